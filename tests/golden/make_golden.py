@@ -1,0 +1,323 @@
+"""Regenerate the golden fixtures in this directory by running the REFERENCE's own code on the CPU.
+
+Run where a checkout of SAI-Lab-NYU/LSVD is available:
+
+    python tests/golden/make_golden.py /path/to/LSVD
+
+It imports the reference's PyTorch quantisers and modules, and executes its Triton
+kernels with Triton's CPU interpreter, on small seeded inputs; inputs and outputs
+are stored as ``.npz`` files next to this script.  The fixtures travel with the
+repository; the reference checkout does not.
+
+Stand-ins needed to import the reference without its optional dependencies:
+  * empty permissive packages for ``llava``, ``accelerate``, ``vlmeval``,
+    ``qwen_vl_utils`` (imported at module scope by the reference, unused here);
+  * ``fast_hadamard_transform.hadamard_transform(x, scale)``: the external CUDA
+    extension is replaced by a Sylvester butterfly that computes in fp32 and returns
+    the input dtype, which is that extension's documented behaviour;
+  * Triton's autotuner is bypassed with one fixed configuration (it needs a GPU
+    driver), and the three ``libdevice.fast_*`` intrinsics of the attention kernel,
+    which the interpreter lacks, are replaced by exp2/log2, cos and sin.
+"""
+import os
+import sys
+import types
+import importlib.abc
+import importlib.machinery
+
+os.environ["TRITON_INTERPRET"] = "1"
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+import numpy as np
+import torch
+import transformers  # noqa: F401  (must be imported before the stub finder is installed)
+
+
+class _Permissive(types.ModuleType):
+    __path__ = []
+
+    def __getattr__(self, k):
+        if k.startswith("__"):
+            raise AttributeError(k)
+        if k.isupper():
+            return -200
+        if k[0].islower():
+            import importlib
+            try:
+                return importlib.import_module(self.__name__ + "." + k)
+            except Exception:
+                pass
+        return type(k, (), {})
+
+
+class _Finder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    ROOTS = ("llava", "accelerate", "vlmeval", "qwen_vl_utils")
+
+    def find_spec(self, name, path, target=None):
+        if name.split(".")[0] in self.ROOTS:
+            return importlib.machinery.ModuleSpec(name, self, is_package=True)
+
+    def create_module(self, spec):
+        return _Permissive(spec.name)
+
+    def exec_module(self, m):
+        pass
+
+
+sys.meta_path.insert(0, _Finder())
+
+fht = types.ModuleType("fast_hadamard_transform")
+
+
+def _hadamard_transform(x, scale=1.0):
+    n = x.shape[-1]
+    assert n & (n - 1) == 0
+    y = x.reshape(-1, n).float().clone()
+    h = 1
+    while h < n:
+        y = y.view(-1, n // (2 * h), 2, h)
+        y = torch.stack((y[:, :, 0] + y[:, :, 1], y[:, :, 0] - y[:, :, 1]), dim=2).reshape(-1, n)
+        h *= 2
+    return (y * float(scale)).reshape(x.shape).to(x.dtype)
+
+
+fht.hadamard_transform = _hadamard_transform
+sys.modules["fast_hadamard_transform"] = fht
+
+
+import triton
+import triton.language as tl
+
+
+@triton.jit
+def _powf(x, y):
+    return tl.exp2(y * tl.log2(x + tl.zeros_like(y)))
+
+
+@triton.jit
+def _cosf(x):
+    return tl.cos(x)
+
+
+@triton.jit
+def _sinf(x):
+    return tl.sin(x)
+
+
+def save(name, **arrs):
+    out = {}
+    for k, v in arrs.items():
+        if isinstance(v, torch.Tensor):
+            v = v.detach().cpu().numpy()
+        out[k] = np.asarray(v)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+    print("wrote", name, {k: (v.shape, str(v.dtype)) for k, v in out.items()})
+
+
+def edge_latents(T, H, R, g):
+    """fp16 latents with the awkward rows in front: zeros, tiny, huge, exact .5 quotients."""
+    x = torch.randn(T, H, R, generator=g).half()
+    x[0] = 0
+    x[1] = 1e-6
+    x[2] = x[2] * 3000
+    x[3, :, 0] = 128.0
+    x[3, :, 1:] = torch.arange(R - 1).half()[None, :] + 0.5
+    x[4] = -x[3]
+    x[5] = x[5] * 1e-3
+    x[6, :, 0] = 65504.0
+    return x
+
+
+# ------------------------------------------------------------------ kernels/ side
+def gen_kernels_side():
+    sys.path.insert(0, os.path.join(REF, "kernels", "layer_bench"))
+    sys.path.insert(0, os.path.join(REF, "kernels", "layer_bench", "fd_kernel"))
+    tl.extra.cuda.libdevice.fast_powf = _powf
+    tl.extra.cuda.libdevice.fast_cosf = _cosf
+    tl.extra.cuda.libdevice.fast_sinf = _sinf
+
+    import benchmark_triton_int8_layer as bench
+    from ffn_kernel import baseline_kernel
+    import destindex_copy_quantize_latent as dcq
+    import flash_int8_latent_per_head_decoding_rope_stage1 as s1
+    import flash_latent_per_head_decoding_stage2 as s2
+
+    g = torch.Generator().manual_seed(0)
+
+    # 1. latent cache quantiser: PyTorch twin (normative) and the Triton append kernel
+    T, H, R = 40, 3, 24
+    x = edge_latents(T, H, R, g)
+    q_t, s_t, _ = bench.quantize_latent_tensor(x, return_dequantized=False)
+    dest = torch.randperm(64, generator=g)[:T].to(torch.int32)
+    cache = torch.zeros(64, H, R, dtype=torch.int8)
+    cache_s = torch.zeros(64, H, dtype=torch.float16)
+    dcq.destindex_copy_quantize_latent(x, dest, cache, cache_s)
+    save("latent_quant", x=x, q_torch=q_t, s_torch=s_t, dest_loc=dest, cache_triton=cache, scale_triton=cache_s)
+
+    # 2. K up-factor quantiser
+    wuk = (torch.randn(16, 96, generator=g) * 0.1).half()
+    wuk[:, 0] = 0
+    wq, ws = baseline_kernel.Int8AttentionBlock._quantize_wuk(None, wuk)
+    save("wuk_quant", wuk=wuk, wuk_q=wq, wuk_scale=ws)
+
+    # 3. decode attention: stage 1 + stage 2 in the interpreter, two fixed block configurations
+    class Fixed:
+        def __init__(self, auto, **cfg):
+            self.fn = auto.fn
+            self.cfg = cfg
+            self.best_config = types.SimpleNamespace(kwargs=cfg)
+
+        def __getitem__(self, grid):
+            gr = grid(self.cfg) if callable(grid) else grid
+            return lambda *a, **k: self.fn[gr](*a, **k, **self.cfg)
+
+    auto = s1._fwd_kernel_flash_int8_latent_decode_rope_stage1
+    B, Hq, Hkv, D, Rk, Rv, S = 3, 4, 2, 32, 16, 32, 300
+    q = torch.randn(B, Hq, D, generator=g).half()
+    lk = torch.randn(B * S, Hkv, Rk, generator=g).half()
+    lv = torch.randn(B * S, Hkv, Rv, generator=g).half()
+    kq, ks, _ = bench.quantize_latent_tensor(lk, return_dequantized=False)
+    vq, vs, _ = bench.quantize_latent_tensor(lv, return_dequantized=False)
+    wukf = (torch.randn(Rk, Hkv * D, generator=g) * 0.1).half()
+    wq, ws = baseline_kernel.Int8AttentionBlock._quantize_wuk(None, wukf)
+    slots = torch.randperm(B * S, generator=g).to(torch.int32).view(B, S)       # non-identity slot map
+    b_req = torch.tensor([2, 0, 1], dtype=torch.int32)
+    b_len = torch.tensor([S, S - 37, 1], dtype=torch.int32)
+    outs = {}
+    for tag, cfg in (("a", dict(BLOCK_N=16, BLOCK_SEQ=256)), ("b", dict(BLOCK_N=32, BLOCK_SEQ=512))):
+        s1._fwd_kernel_flash_int8_latent_decode_rope_stage1 = Fixed(auto, **cfg)
+        BS = 256
+        nblk = (S + BS - 1) // BS
+        mid = torch.zeros(B, Hq, nblk, Rv, dtype=torch.float32)
+        lse = torch.zeros(B, Hq, nblk, dtype=torch.float32)
+        used = s1.flash_int8_latent_per_head_decode_rope_stage1(q, kq, ks, vq, vs, wq, ws, slots, b_req, b_len, S, mid, lse, BS)
+        o = torch.zeros(B, Hq, Rv, dtype=torch.float16)
+        s2.flash_decode_stage2(mid, lse, b_len, o, used)
+        outs["o_" + tag] = o
+    save("attn_rope_recon", q=q, cache_k=kq, scale_k=ks, cache_v=vq, scale_v=vs, wk_q=wq, wk_scale=ws,
+         req_to_token=slots, b_req_idx=b_req, b_seq_len=b_len, **outs)
+
+
+# ------------------------------------------------------------------ fake_quant/ side
+def gen_fake_quant_side():
+    for m in [k for k in sys.modules if k == "utils" or k.startswith("utils.")]:
+        del sys.modules[m]
+    sys.path.insert(0, os.path.join(REF, "fake_quant"))
+    import torch.nn as nn
+    from utils import quant_utils, hadamard_utils
+    from utils.hybrid_ffn_utils import HybridSVDQuantFFN, _make_quant_linear
+    from utils.svd_utils import SVDLinear
+
+    g = torch.Generator().manual_seed(1)
+
+    # 4. activation and weight quantisers
+    xa = torch.randn(9, 64, generator=g).half()
+    xa[0] = 0
+    xa[1, :] = torch.linspace(-3, 3, 64).half()
+    aq = quant_utils.ActQuantizer()
+    aq.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+    aq.find_params(xa)
+    a_codes, a_scale = aq.quantize(xa)
+    a_fake = aq(xa)
+    W = (torch.randn(24, 64, generator=g) * 0.02).half()
+    W[3] = 0
+    wres = {}
+    for tag, mse in (("rtn", False), ("mse", True)):
+        wq = quant_utils.WeightQuantizer()
+        wq.configure(8, perchannel=True, sym=True, mse=mse)
+        wq.find_params(W)
+        fake, codes, scale = wq.fake_quantize(W)
+        wres["w_codes_" + tag], wres["w_scale_" + tag], wres["w_fake_" + tag] = codes, scale, fake
+    save("fq_quantizers", x=xa, a_codes=a_codes, a_scale=a_scale[:, 0], a_fake=a_fake, W=W, **wres)
+
+    # 5. Hadamard: power-of-two and the K = 172, 108 factored forms, plus the factors themselves (bit-packed)
+    res = {}
+    for n in (64, 172 * 4, 108 * 8):
+        hk, K = hadamard_utils.get_hadK(n)
+        xh = torch.randn(5, n, generator=g).half()
+        res[f"x_{n}"] = xh
+        res[f"y_{n}"] = hadamard_utils.matmul_hadU_cuda(xh, hk, K)
+        res[f"K_{n}"] = K
+    for K in (172, 108):
+        hk, _ = hadamard_utils.get_hadK(K * 64)
+        res[f"had{K}_bits"] = np.packbits((hk.numpy() > 0).astype(np.uint8))
+    # input rotation: x @ random_hadamard_matrix(n) with the sign vector recovered from the matrix
+    torch.manual_seed(7)
+    Q = hadamard_utils.random_hadamard_matrix(128, "cpu")                      # float64
+    sign = torch.sign(Q[:, 0]).float()                                        # column 0 of H is all ones
+    xr = torch.randn(6, 128, generator=g).half()
+    res["rot_x"], res["rot_sign"], res["rot_y"] = xr, sign, (xr.double() @ Q).half()
+    save("hadamard", **res)
+
+    # 6. the hybrid FFN module itself, fp16 on the CPU, with every sub-module output captured
+    d_in, d_ffn, r = 128, 172 * 4, 32
+    n_svd = d_ffn // 2
+    n_q = d_ffn - n_svd
+
+    def rtn_(lin):
+        wq = quant_utils.WeightQuantizer()
+        wq.configure(8, perchannel=True, sym=True, mse=False)
+        wq.find_params(lin.weight.data)
+        fake, codes, scale = wq.fake_quantize(lin.weight.data)
+        lin.weight.data = wq.quantize(lin.weight.data).to(lin.weight.dtype)
+        return codes.to(torch.int8), scale.flatten().float()
+
+    def svd_lin():
+        m = SVDLinear.__new__(SVDLinear)
+        nn.Module.__init__(m)
+        m.BLinear = nn.Linear(d_in, r, bias=False)
+        m.ALinear = nn.Linear(r, n_svd, bias=False)
+        m.is_ma_hack = False
+        m.original_linear = None
+        m.is_per_head_svd = False
+        m.BLinear.weight.data = torch.randn(r, d_in, generator=g) * 0.1
+        m.ALinear.weight.data = torch.randn(n_svd, r, generator=g) * 0.1
+        m = m.half()
+        m.BLinear = quant_utils.ActQuantWrapper(m.BLinear)
+        return m
+
+    ref_lin = nn.Linear(d_in, d_ffn, bias=False).half()
+    g_svd, u_svd = svd_lin(), svd_lin()
+    g_q = _make_quant_linear(torch.randn(n_q, d_in, generator=g) * 0.1, d_in, ref_lin)
+    u_q = _make_quant_linear(torch.randn(n_q, d_in, generator=g) * 0.1, d_in, ref_lin)
+    down = quant_utils.ActQuantWrapper(nn.Linear(d_ffn, d_in, bias=False).half())
+    down.module.weight.data = (torch.randn(d_in, d_ffn, generator=g) * 0.05).half()
+    had_K, K = hadamard_utils.get_hadK(d_ffn)
+    ffn = HybridSVDQuantFFN(g_svd, u_svd, g_q, u_q, down, torch.arange(d_ffn), n_svd, had_K=had_K, K=K)
+    wts = {}
+    for name, lin in (("Ug", g_svd.BLinear.module), ("Uu", u_svd.BLinear.module), ("Vg", g_svd.ALinear),
+                      ("Vu", u_svd.ALinear), ("Wg", g_q.module), ("Wu", u_q.module), ("Wd", down.module)):
+        wts[name + "_q"], wts[name + "_s"] = rtn_(lin)
+    for wmod in (g_svd.BLinear, u_svd.BLinear, g_q, u_q, down):
+        wmod.quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+    for wmod in (g_svd.BLinear, u_svd.BLinear):
+        wmod.out_quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+    cap = {}
+
+    def hook(tag):
+        def f(mod, inp, out):
+            cap[tag + "_in"] = inp[0].detach().clone()
+            cap[tag + "_out"] = out.detach().clone()
+        return f
+
+    g_svd.BLinear.register_forward_hook(hook("latg"))
+    u_svd.BLinear.register_forward_hook(hook("latu"))
+    g_svd.register_forward_hook(hook("gsvd"))
+    u_svd.register_forward_hook(hook("usvd"))
+    g_q.register_forward_hook(hook("grtn"))
+    u_q.register_forward_hook(hook("urtn"))
+    down.register_forward_hook(hook("down"))
+    down.module.register_forward_hook(hook("downlin"))
+    x = torch.randn(7, d_in, generator=g).half()
+    with torch.no_grad():
+        y = ffn(x)
+    save("hybrid_ffn", x=x, y=y, K=K, had_bits=np.packbits((had_K.numpy() > 0).astype(np.uint8)),
+         latg=cap["latg_out"], latu=cap["latu_out"], g_svd=cap["gsvd_out"], u_svd=cap["usvd_out"],
+         g_rtn=cap["grtn_out"], u_rtn=cap["urtn_out"], h=cap["down_in"], h_fakeq=cap["downlin_in"], **wts)
+
+
+if __name__ == "__main__":
+    with torch.no_grad():
+        gen_kernels_side()
+        gen_fake_quant_side()
