@@ -1,0 +1,150 @@
+/*
+ * lsvd_b200 -- C ABI of the B200 (sm_100a) kernels for the LSVD decode hot paths.
+ *
+ * Every entry point takes plain device/host pointers, sizes and strides, returns an
+ * int status (0 = success) and never throws.  Kernels are enqueued on the CUDA stream
+ * passed as `stream` (a cudaStream_t cast to void*; NULL = legacy default stream); no
+ * entry point synchronises the device.  Unless an entry point says otherwise the caller
+ * owns every buffer, including the workspace, whose size comes from the matching
+ * *_workspace_bytes query.
+ *
+ * Reference interfaces replaced (paths inside SAI-Lab-NYU/LSVD):
+ *   lsvd_cache_append        kernels/layer_bench/fd_kernel/destindex_copy_quantize_latent.py:36-50
+ *   lsvd_attn_decode         kernels/layer_bench/fd_kernel/flash_decoding.py:3-57
+ *                            (stage 1: flash_int8_latent_per_head_decoding_rope_stage1.py:198-250,
+ *                             stage 2: flash_latent_per_head_decoding_stage2.py:52-69)
+ */
+#ifndef LSVD_B200_H
+#define LSVD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LSVD_ABI_VERSION 1
+#define LSVD_MAX_HEADS 128      /* heads per call (per GPU shard)                     */
+#define LSVD_MAX_RANK 128       /* latent entries per head; ranks are multiples of 16 */
+#define LSVD_MAX_SPLITS 128     /* sequence splits per request in decode attention    */
+
+enum {
+  LSVD_OK = 0,
+  LSVD_ERR_INVALID_ARG = 1,   /* NULL pointer, negative size, misaligned buffer, bad rank table */
+  LSVD_ERR_UNSUPPORTED = 2,   /* a valid request this build has no kernel for                   */
+  LSVD_ERR_WORKSPACE = 3,     /* workspace missing or too small                                 */
+  LSVD_ERR_CUDA = 4,          /* a CUDA runtime call failed; see lsvd_last_cuda_error()         */
+  LSVD_ERR_TIMEOUT = 5,       /* device status word: a bounded wait inside a kernel gave up     */
+  LSVD_ERR_BOUNDS = 6         /* device status word: an index was out of range and was skipped  */
+};
+
+int lsvd_abi_version(void);
+const char* lsvd_status_string(int code);
+/* cudaError_t of the most recent failing CUDA call made by this library on the calling thread. */
+int lsvd_last_cuda_error(void);
+
+/* Rounding used when fp16 latents become int8 cache entries.
+ *   LSVD_ROUND_TORCH  : x/scale evaluated in fp16, round half to even -- the reference's PyTorch quantiser
+ *                       (kernels/layer_bench/benchmark_triton_int8_layer.py:103-113), normative.
+ *   LSVD_ROUND_TRITON : x/scale in fp32, round half away from zero -- the reference's Triton append kernel
+ *                       (kernels/layer_bench/fd_kernel/destindex_copy_quantize_latent.py:26-29).        */
+enum { LSVD_ROUND_TORCH = 0, LSVD_ROUND_TRITON = 1 };
+
+/* ---------------------------------------------------------------------------------------------
+ * Latent KV-cache append / quantise.
+ * Replaces destindex_copy_quantize_latent(latent, dest_loc, cache, cache_scale)
+ * (kernels/layer_bench/fd_kernel/destindex_copy_quantize_latent.py:36-50); one call handles K and V.
+ *
+ * Cache layout: one row per slot; head h of a row occupies bytes rank_off[h] .. rank_off[h+1]-1, so a
+ * uniform rank R gives the reference's [N_slots, H, R] tensor.  Scales: [N_slots, H] fp16.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lsvd_append_tensor {
+  const void* latent;            /* device fp16; element (t, h, i) at latent[t*token_stride + head_off[h] + i]   */
+  int64_t token_stride;          /* elements                                                                       */
+  const int64_t* head_off;       /* HOST array [num_heads] of element offsets, or NULL for rank_off (packed rows) */
+  const int32_t* rank_off;       /* HOST array [num_heads+1], multiples of 16, rank_off[0] = 0                    */
+  int8_t* cache;                 /* device int8                                                                    */
+  int64_t cache_row_stride;      /* bytes between consecutive slots                                                */
+  void* cache_scale;             /* device fp16                                                                    */
+  int64_t scale_row_stride;      /* elements between consecutive slots                                             */
+} lsvd_append_tensor;
+
+typedef struct lsvd_append_args {
+  int32_t num_tokens;
+  int32_t num_heads;
+  int32_t rounding;              /* LSVD_ROUND_*                                                                   */
+  int32_t num_slots;             /* rows in the cache; a dest_loc outside [0, num_slots) is skipped and reported   */
+  const int32_t* dest_loc;       /* device int32 [num_tokens]                                                      */
+  lsvd_append_tensor k;          /* k.latent == NULL skips K                                                       */
+  lsvd_append_tensor v;          /* v.latent == NULL skips V                                                       */
+  int32_t* status_word;          /* device int32 or NULL; receives LSVD_ERR_BOUNDS (never cleared by the library)  */
+} lsvd_append_args;
+
+int lsvd_cache_append(const lsvd_append_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * int8 latent flash-decoding attention, one query token per request ("absorb" form).
+ * Replaces token_decode_attention_flash_int8_latent_per_head_decoding_rope
+ * (kernels/layer_bench/fd_kernel/flash_decoding.py:3-57) for the rotary-free configuration:
+ *   q~   = B_k q                                   query folded into the per-head K up-factor
+ *   s_t  = sm_scale * scale_k[t,h] * (z_k[t,h] . q~_h)
+ *   p    = softmax_t(s)                            split over the sequence, merged by log-sum-exp
+ *   o_lat= sum_t p_t * scale_v[t,h] * z_v[t,h]     (written to out_latent if not NULL)
+ *   o    = B_v^T o_lat                             (written to out if not NULL)
+ * Request b reads the cache rows req_to_token[b_req_idx[b], 0 .. b_seq_len[b]-1].  A request of
+ * length 0 gets zeros (the reference leaves 0/0 there).  num_q_heads == num_kv_heads only.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lsvd_attn_decode_args {
+  int32_t batch;
+  int32_t num_heads;
+  int32_t head_dim;              /* multiple of 8, <= 256                                                          */
+  int32_t max_len_in_batch;      /* upper bound of b_seq_len (sizes the grid, like the reference)                  */
+  float sm_scale;                /* <= 0 selects 1/sqrt(head_dim)                                                  */
+  int32_t num_slots;             /* rows in the cache, for the bounds guard                                        */
+  const void* q;                 /* device fp16; (b, h, d) at q[b*q_stride_b + h*q_stride_h + d]                   */
+  int64_t q_stride_b, q_stride_h;
+  const int32_t* k_off;          /* HOST [num_heads+1] byte offsets of the heads inside a K cache row              */
+  const int32_t* v_off;          /* HOST [num_heads+1]                                                             */
+  const int8_t* cache_k;         /* device; 16-byte aligned, row stride a multiple of 16                           */
+  int64_t cache_k_row_stride;
+  const void* scale_k;           /* device fp16 [N_slots, H]                                                       */
+  int64_t scale_k_row_stride;
+  const int8_t* cache_v;
+  int64_t cache_v_row_stride;
+  const void* scale_v;
+  int64_t scale_v_row_stride;
+  const void* up_k;              /* device fp16 [sum r_k, head_dim]: row k_off[h]+i is latent entry i of head h    */
+  int64_t up_k_row_stride;       /* elements                                                                       */
+  const void* up_v;              /* device fp16 [sum r_v, head_dim]; may be NULL when out is NULL                  */
+  int64_t up_v_row_stride;
+  const int32_t* req_to_token;   /* device int32 [*, req_to_token_stride]                                          */
+  int64_t req_to_token_stride;
+  const int32_t* b_req_idx;      /* device int32 [batch]                                                           */
+  const int32_t* b_seq_len;      /* device int32 [batch]                                                           */
+  void* out;                     /* device fp16 (b, h, d) at out[b*out_stride_b + h*out_stride_h + d], or NULL     */
+  int64_t out_stride_b, out_stride_h;
+  void* out_latent;              /* device fp16 (b, v_off[h]+i) at out_latent[b*out_latent_stride_b + ...], or NULL */
+  int64_t out_latent_stride_b;
+  void* workspace;               /* device, 256-byte aligned                                                       */
+  size_t workspace_bytes;
+  int32_t* status_word;          /* device int32 or NULL                                                           */
+  void* ev_stream_begin;         /* optional cudaEvent_t pair recorded around the streaming kernel alone (the      */
+  void* ev_stream_end;           /* launch that reads the cache), for roofline measurements; NULL = not recorded   */
+} lsvd_attn_decode_args;
+
+/* Bytes of workspace lsvd_attn_decode needs for this problem on the current device. */
+size_t lsvd_attn_decode_workspace_bytes(int32_t batch, int32_t num_heads, int32_t sum_rank_k,
+                                        int32_t sum_rank_v, int32_t max_len_in_batch);
+int lsvd_attn_decode(const lsvd_attn_decode_args* args, void* stream);
+
+/* Launch geometry chosen for a problem (for reports and tests): sequence splits per request, head
+ * groups per request, pipeline stages, thread blocks.  Returns a status. */
+int lsvd_attn_decode_plan(int32_t batch, int32_t num_heads, const int32_t* k_off, const int32_t* v_off,
+                          int32_t max_len_in_batch, int32_t* num_splits, int32_t* num_groups,
+                          int32_t* num_stages, int32_t* num_blocks);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LSVD_B200_H */

@@ -1,0 +1,13 @@
+"""lsvd_b200: B200 (sm_100a) kernels for the LSVD decode hot paths behind the reference's PyTorch API.
+
+Python here is host plumbing only (argument checks, pointers, streams); the work
+is done by hand-written CUDA kernels in ``liblsvd_b200.so``, reached through a
+plain C ABI (``include/lsvd_b200.h``).  There is no CPU or PyTorch fallback.
+"""
+from . import _lib
+from ._lib import LsvdError
+from .attention import (LatentCacheLayout, destindex_copy_quantize_latent, cache_append,
+                        token_decode_attention_int8_latent_absorb, LatentDecodeAttention, InferState)
+
+__all__ = ["LsvdError", "LatentCacheLayout", "destindex_copy_quantize_latent", "cache_append",
+           "token_decode_attention_int8_latent_absorb", "LatentDecodeAttention", "InferState"]

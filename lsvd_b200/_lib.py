@@ -1,0 +1,115 @@
+"""ctypes binding of ``liblsvd_b200.so`` (the C ABI declared in ``include/lsvd_b200.h``).
+
+There is no fallback: if the shared library is missing or does not load, importing
+the kernels raises.  Tensors cross the boundary as raw device pointers, strides
+and the current CUDA stream handle.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liblsvd_b200.so")
+
+LSVD_MAX_HEADS = 128
+LSVD_MAX_RANK = 128
+ROUND_TORCH, ROUND_TRITON = 0, 1
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_BOUNDS = range(7)
+
+
+class LsvdError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"lsvd_b200: {what} (status {code})")
+        self.code = code
+
+
+class AppendTensor(C.Structure):
+    _fields_ = [
+        ("latent", C.c_void_p), ("token_stride", C.c_int64), ("head_off", C.POINTER(C.c_int64)),
+        ("rank_off", C.POINTER(C.c_int32)), ("cache", C.c_void_p), ("cache_row_stride", C.c_int64),
+        ("cache_scale", C.c_void_p), ("scale_row_stride", C.c_int64),
+    ]
+
+
+class AppendArgs(C.Structure):
+    _fields_ = [
+        ("num_tokens", C.c_int32), ("num_heads", C.c_int32), ("rounding", C.c_int32), ("num_slots", C.c_int32),
+        ("dest_loc", C.c_void_p), ("k", AppendTensor), ("v", AppendTensor), ("status_word", C.c_void_p),
+    ]
+
+
+class AttnDecodeArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("max_len_in_batch", C.c_int32),
+        ("sm_scale", C.c_float), ("num_slots", C.c_int32),
+        ("q", C.c_void_p), ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64),
+        ("k_off", C.POINTER(C.c_int32)), ("v_off", C.POINTER(C.c_int32)),
+        ("cache_k", C.c_void_p), ("cache_k_row_stride", C.c_int64),
+        ("scale_k", C.c_void_p), ("scale_k_row_stride", C.c_int64),
+        ("cache_v", C.c_void_p), ("cache_v_row_stride", C.c_int64),
+        ("scale_v", C.c_void_p), ("scale_v_row_stride", C.c_int64),
+        ("up_k", C.c_void_p), ("up_k_row_stride", C.c_int64),
+        ("up_v", C.c_void_p), ("up_v_row_stride", C.c_int64),
+        ("req_to_token", C.c_void_p), ("req_to_token_stride", C.c_int64),
+        ("b_req_idx", C.c_void_p), ("b_seq_len", C.c_void_p),
+        ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
+        ("out_latent", C.c_void_p), ("out_latent_stride_b", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("status_word", C.c_void_p), ("ev_stream_begin", C.c_void_p), ("ev_stream_end", C.c_void_p),
+    ]
+
+
+# Every symbol include/lsvd_b200.h declares, with its ctypes signature.
+SIGNATURES = {
+    "lsvd_abi_version": (C.c_int, []),
+    "lsvd_status_string": (C.c_char_p, [C.c_int]),
+    "lsvd_last_cuda_error": (C.c_int, []),
+    "lsvd_cache_append": (C.c_int, [C.POINTER(AppendArgs), C.c_void_p]),
+    "lsvd_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
+    "lsvd_attn_decode_plan": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
+                                        C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                        C.POINTER(C.c_int32)]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library once; raise if it is absent (there is no CPU path behind it)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise LsvdError(-1, f"{LIB_PATH} not found: build it with `python -m lsvd_b200.build`")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    """Turn a non-zero status into the exception type the reference raises for the same mistake."""
+    if code == OK:
+        return
+    lib = load()
+    what = lib.lsvd_status_string(code).decode()
+    if code == ERR_CUDA:
+        what += f" (cudaError {lib.lsvd_last_cuda_error()})"
+    if code in (ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE):
+        raise ValueError(f"lsvd_b200: {what} (status {code})")
+    raise LsvdError(code, what)
+
+
+def i32_array(values):
+    arr = (C.c_int32 * len(values))(*[int(v) for v in values])
+    return arr
+
+
+def i64_array(values):
+    arr = (C.c_int64 * len(values))(*[int(v) for v in values])
+    return arr

@@ -1,0 +1,177 @@
+// Latent KV-cache append: per (token, head) absmax scale, int8 codes, scatter to the cache row
+// dest_loc[token].  One launch covers K and V and every head.
+//
+// Arithmetic follows the reference exactly (bit-exact codes and scales):
+//   scale = fp16(max(absmax/128, 1e-4))                 destindex_copy_quantize_latent.py:26,
+//                                                       benchmark_triton_int8_layer.py:107-108
+//   torch  rounding: q = clamp(rne(fp16(x / scale)))    benchmark_triton_int8_layer.py:109
+//   triton rounding: q = clamp(trunc(x/scale +- 0.5))   destindex_copy_quantize_latent.py:27-29
+//
+// Mapping: one warp per (token, head, K|V).  A lane owns 4 consecutive latent entries (ranks are
+// multiples of 16, at most 128), loads them with one 8-byte access and stores 4 codes with one
+// 4-byte access, so a warp moves a head with one coalesced load and one coalesced store.
+#include "common.cuh"
+
+namespace lsvd {
+
+struct AppendSide {
+  const __half* latent;
+  int64_t token_stride;
+  int8_t* cache;
+  int64_t cache_row_stride;
+  __half* scale;
+  int64_t scale_row_stride;
+  int64_t head_off[LSVD_MAX_HEADS];   // element offset of each head inside a token's latent
+  int32_t rank_off[LSVD_MAX_HEADS + 1];
+};
+
+struct AppendParams {
+  AppendSide side[2];
+  const int32_t* dest_loc;
+  int32_t* status_word;
+  int32_t num_tokens, num_heads, num_slots, rounding;
+  int32_t side_mask;                   // bit 0: K present, bit 1: V present
+};
+
+template <int kRounding>
+__device__ __forceinline__ int quantise_one(float x, float s) {
+  if (kRounding == LSVD_ROUND_TORCH) {
+    // fp16 division = exact quotient rounded once to fp16; then round half to even.
+    float y = __half2float(__float2half_rn(__fdiv_rn(x, s)));
+    y = rintf(y);
+    return static_cast<int>(fminf(fmaxf(y, -128.f), 127.f));
+  } else {
+    float y = __fdiv_rn(x, s);
+    int r = static_cast<int>(y >= 0.f ? y + 0.5f : y - 0.5f);   // conversion truncates toward zero
+    return min(max(r, -128), 127);
+  }
+}
+
+template <int kRounding>
+__global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant__ AppendParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t per_side = static_cast<int64_t>(p.num_tokens) * p.num_heads;
+  int side = 0;
+  int64_t u = unit;
+  if ((p.side_mask & 1) == 0) {
+    side = 1;
+  } else if (u >= per_side) {
+    side = 1;
+    u -= per_side;
+  }
+  if (u >= per_side || ((p.side_mask >> side) & 1) == 0) return;
+  const int t = static_cast<int>(u / p.num_heads);
+  const int h = static_cast<int>(u - static_cast<int64_t>(t) * p.num_heads);
+  const AppendSide& s = p.side[side];
+
+  const int r0 = s.rank_off[h];
+  const int rank = s.rank_off[h + 1] - r0;
+  const int i0 = lane * 4;
+  const bool active = i0 < rank;
+
+  float x[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const __half* src = s.latent + static_cast<int64_t>(t) * s.token_stride + s.head_off[h] + i0;
+    if ((reinterpret_cast<uintptr_t>(src) & 7) == 0) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(src);
+      const __half2 a = *reinterpret_cast<const __half2*>(&raw.x);
+      const __half2 b = *reinterpret_cast<const __half2*>(&raw.y);
+      x[0] = __low2float(a); x[1] = __high2float(a); x[2] = __low2float(b); x[3] = __high2float(b);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[j] = __half2float(src[j]);
+    }
+  }
+  float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+  amax = warp_max(amax);
+  // absmax is an fp16 value; /128 in fp16 is one rounding of the exact quotient.
+  __half s16 = __float2half_rn(amax * 0.0078125f);
+  const __half floor16 = __float2half_rn(1e-4f);
+  if (__half2float(s16) < __half2float(floor16)) s16 = floor16;
+  const float sf = __half2float(s16);
+
+  const int dest = p.dest_loc[t];
+  if (dest < 0 || dest >= p.num_slots) {
+    if (lane == 0) report_status(p.status_word, LSVD_ERR_BOUNDS);
+    return;
+  }
+  if (active) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int q = quantise_one<kRounding>(x[j], sf);
+      packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * j);
+    }
+    int8_t* dst = s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0 + i0;
+    *reinterpret_cast<uint32_t*>(dst) = packed;
+  }
+  if (lane == 0) s.scale[static_cast<int64_t>(dest) * s.scale_row_stride + h] = s16;
+}
+
+static int fill_side(AppendSide& dst, const lsvd_append_tensor& src, int num_heads) {
+  if (src.rank_off == nullptr || src.cache == nullptr || src.cache_scale == nullptr) return LSVD_ERR_INVALID_ARG;
+  if (src.rank_off[0] != 0) return LSVD_ERR_INVALID_ARG;
+  for (int h = 0; h < num_heads; ++h) {
+    const int r = src.rank_off[h + 1] - src.rank_off[h];
+    if (r <= 0 || r > LSVD_MAX_RANK || (r % 16) != 0) return LSVD_ERR_INVALID_ARG;
+    dst.rank_off[h] = src.rank_off[h];
+    dst.head_off[h] = src.head_off ? src.head_off[h] : src.rank_off[h];
+  }
+  dst.rank_off[num_heads] = src.rank_off[num_heads];
+  if (src.cache_row_stride < src.rank_off[num_heads] || (src.cache_row_stride % 4) != 0) return LSVD_ERR_INVALID_ARG;
+  if (!aligned(src.cache, 4) || !aligned(src.latent, 2) || !aligned(src.cache_scale, 2)) return LSVD_ERR_INVALID_ARG;
+  if (src.scale_row_stride < num_heads) return LSVD_ERR_INVALID_ARG;
+  dst.latent = static_cast<const __half*>(src.latent);
+  dst.token_stride = src.token_stride;
+  dst.cache = src.cache;
+  dst.cache_row_stride = src.cache_row_stride;
+  dst.scale = static_cast<__half*>(src.cache_scale);
+  dst.scale_row_stride = src.scale_row_stride;
+  return LSVD_OK;
+}
+
+}  // namespace lsvd
+
+extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
+  using namespace lsvd;
+  if (a == nullptr) return LSVD_ERR_INVALID_ARG;
+  if (a->num_tokens < 0 || a->num_heads <= 0 || a->num_heads > LSVD_MAX_HEADS || a->num_slots <= 0)
+    return LSVD_ERR_INVALID_ARG;
+  if (a->rounding != LSVD_ROUND_TORCH && a->rounding != LSVD_ROUND_TRITON) return LSVD_ERR_INVALID_ARG;
+  if (a->num_tokens == 0) return LSVD_OK;
+  if (a->dest_loc == nullptr) return LSVD_ERR_INVALID_ARG;
+
+  AppendParams p{};
+  p.dest_loc = a->dest_loc;
+  p.status_word = a->status_word;
+  p.num_tokens = a->num_tokens;
+  p.num_heads = a->num_heads;
+  p.num_slots = a->num_slots;
+  p.rounding = a->rounding;
+  p.side_mask = 0;
+  if (a->k.latent != nullptr) {
+    int rc = fill_side(p.side[0], a->k, a->num_heads);
+    if (rc != LSVD_OK) return rc;
+    p.side_mask |= 1;
+  }
+  if (a->v.latent != nullptr) {
+    int rc = fill_side(p.side[1], a->v, a->num_heads);
+    if (rc != LSVD_OK) return rc;
+    p.side_mask |= 2;
+  }
+  if (p.side_mask == 0) return LSVD_OK;
+
+  const int sides = (p.side_mask == 3) ? 2 : 1;
+  const int64_t warps = static_cast<int64_t>(a->num_tokens) * a->num_heads * sides;
+  const int warps_per_block = 4;
+  const int64_t blocks = (warps + warps_per_block - 1) / warps_per_block;
+  if (blocks > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->rounding == LSVD_ROUND_TORCH)
+    cache_append_kernel<LSVD_ROUND_TORCH><<<static_cast<unsigned>(blocks), warps_per_block * 32, 0, st>>>(p);
+  else
+    cache_append_kernel<LSVD_ROUND_TRITON><<<static_cast<unsigned>(blocks), warps_per_block * 32, 0, st>>>(p);
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}

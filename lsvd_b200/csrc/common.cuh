@@ -1,0 +1,136 @@
+// Shared device/host helpers for the sm_100a kernels: status plumbing, mbarrier and bulk-copy
+// (TMA) wrappers with bounded waits, warp reductions.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lsvd_b200.h"
+
+namespace lsvd {
+
+// ---- host side -------------------------------------------------------------------------------
+void set_last_cuda_error(cudaError_t e);
+
+#define LSVD_CUDA_TRY(expr)                      \
+  do {                                           \
+    cudaError_t _e = (expr);                     \
+    if (_e != cudaSuccess) {                     \
+      ::lsvd::set_last_cuda_error(_e);           \
+      return LSVD_ERR_CUDA;                      \
+    }                                            \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int device_sm_count();           // SM count of the current device (cached per device)
+int device_max_smem_optin();     // opt-in shared memory per block of the current device
+// Raise a kernel's dynamic shared memory limit on the current device (remembered, so repeated calls are free).
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
+
+// ---- device side -----------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// Record the first error code seen by a kernel; later codes do not overwrite it.
+__device__ __forceinline__ void report_status(int32_t* status_word, int code) {
+  if (status_word != nullptr) atomicCAS(status_word, 0, code);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Wait for a phase of an mbarrier for at most kMbarTimeoutNs of wall time (and a hard cap on polls, in
+// case the timer does not advance).  Returns false when the limit ran out; the caller must then stop
+// using the pipeline and report LSVD_ERR_TIMEOUT.
+constexpr uint64_t kMbarTimeoutNs = 2000000000ull;   // 2 s
+constexpr uint32_t kMbarMaxPolls = 1u << 26;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 0; i < kMbarMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kMbarTimeoutNs) return false;
+  }
+  return false;
+}
+
+// One-dimensional bulk copy global -> shared (TMA, no tensor map): 16-byte aligned addresses,
+// size a multiple of 16; completion is counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Warp maximum of finite-or-minus-infinity floats through the integer redux unit: the key is
+// monotonic in the float value.
+__device__ __forceinline__ float warp_max_redux(float v) {
+  int i = __float_as_int(v);
+  int key = i ^ ((i >> 31) & 0x7fffffff);
+  key = __reduce_max_sync(0xffffffffu, key);
+  return __int_as_float(key ^ ((key >> 31) & 0x7fffffff));
+}
+
+// Sign-extended byte `idx` of a 32-bit word as a float, without the narrow integer conversions:
+// one byte-permute with sign replication, one int32 -> fp32 conversion.
+template <int kIdx>
+__device__ __forceinline__ float s8_to_f32(uint32_t w) {
+  constexpr uint32_t sel = (kIdx) | ((8u | kIdx) << 4) | ((8u | kIdx) << 8) | ((8u | kIdx) << 12);
+  int v;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(w), "r"(0u), "r"(sel));   // selector bit 3: replicate the sign
+  return __int2float_rn(v);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace lsvd
