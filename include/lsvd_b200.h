@@ -27,7 +27,6 @@ extern "C" {
 #define LSVD_ABI_VERSION 1
 #define LSVD_MAX_HEADS 128      /* heads per call (per GPU shard)                     */
 #define LSVD_MAX_RANK 128       /* latent entries per head; ranks are multiples of 16 */
-#define LSVD_MAX_SPLITS 128     /* sequence splits per request in decode attention    */
 
 enum {
   LSVD_OK = 0,
@@ -138,11 +137,11 @@ size_t lsvd_attn_decode_workspace_bytes(int32_t batch, int32_t num_heads, int32_
                                         int32_t sum_rank_v, int32_t max_len_in_batch);
 int lsvd_attn_decode(const lsvd_attn_decode_args* args, void* stream);
 
-/* Launch geometry chosen for a problem (for reports and tests): sequence splits per request, head
- * groups per request, pipeline stages, thread blocks.  Returns a status. */
+/* Launch geometry chosen for a problem (for reports and tests): work items per request, the byte size
+ * an item aims for, thread blocks.  Returns a status. */
 int lsvd_attn_decode_plan(int32_t batch, int32_t num_heads, const int32_t* k_off, const int32_t* v_off,
-                          int32_t max_len_in_batch, int32_t* num_splits, int32_t* num_groups,
-                          int32_t* num_stages, int32_t* num_blocks);
+                          int32_t max_len_in_batch, int32_t* items_per_request, int32_t* item_bytes,
+                          int32_t* num_blocks);
 
 #ifdef __cplusplus
 }

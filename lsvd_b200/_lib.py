@@ -69,8 +69,7 @@ SIGNATURES = {
     "lsvd_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_plan": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
-                                        C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
-                                        C.POINTER(C.c_int32)]),
+                                        C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
 }
 
 _lib = None

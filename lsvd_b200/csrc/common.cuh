@@ -87,6 +87,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   for (uint32_t i = 0; i < kMbarMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() - t0 > kMbarTimeoutNs) return false;
+    __nanosleep(40);      // keep the issue slots for the warps that have work
   }
   return false;
 }
