@@ -143,6 +143,70 @@ int lsvd_attn_decode_plan(int32_t batch, int32_t num_heads, const int32_t* k_off
                           int32_t max_len_in_batch, int32_t* items_per_request, int32_t* item_bytes,
                           int32_t* num_blocks);
 
+/* ---------------------------------------------------------------------------------------------
+ * Hybrid SVD/RTN FFN, decode (1..64 tokens): building blocks and the fused chain.
+ * Semantics follow fake_quant/utils/hybrid_ffn_utils.py:956-984 (HybridSVDQuantFFN.forward) with real
+ * int8 codes: activations are quantised per token (fake_quant/utils/quant_utils.py:201-212,30-33),
+ * weights per output channel (quant_utils.py:436-498), every matrix product is an exact
+ * int8 x int8 -> int32 contraction, and fp16 roundings sit where the reference's fp16 tensors are.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Per-token symmetric int8 quantisation of fp16 rows, optionally after a Hadamard rotation of the row:
+ *   sign != NULL : x <- FWHT(x * sign) / sqrt(cols)   (x @ random_hadamard_matrix, fake_quant/utils/hadamard_utils.py:99-104)
+ *   fwht  != 0   : x <- FWHT(x) / sqrt(cols)          (matmul_hadU_cuda with K == 1, hadamard_utils.py:106-109)
+ * then scale = absmax / 127 (1 for a zero row), q = clamp(rne(x / scale), -128, 127).  cols <= 16384; a
+ * rotation needs cols to be a power of two.  Replaces ActQuantizer.find_params + quantize. */
+typedef struct lsvd_act_quant_args {
+  int32_t rows, cols;
+  const void* x;                 /* device fp16 [rows, cols]                                        */
+  int64_t x_row_stride;          /* elements                                                        */
+  const void* sign;              /* device fp16 [cols] of +-1, or NULL                              */
+  int32_t fwht;                  /* rotate without signs                                            */
+  int8_t* q;                     /* device int8 [rows, cols]                                        */
+  int64_t q_row_stride;
+  float* scale;                  /* device fp32 [rows]                                              */
+  void* x_rot;                   /* optional device fp16 [rows, cols] (contiguous): the rotated row */
+} lsvd_act_quant_args;
+int lsvd_act_quant(const lsvd_act_quant_args* args, void* stream);
+
+/* Online Hadamard of the FFN hidden vector followed by per-token int8 quantisation:
+ *   y = (H_K kron H_{cols/K}) x / sqrt(cols), rounded to fp16 after the power-of-two part and after the
+ *   had_K product (matmul_hadU_cuda, fake_quant/utils/hadamard_utils.py:106-113), then quantised as above.
+ * K > 1, K <= 256, cols / K a power of two in [8, 128]. */
+typedef struct lsvd_hadamard_quant_args {
+  int32_t rows, cols, K;
+  const void* x;                 /* device fp16 [rows, cols]                                        */
+  int64_t x_row_stride;
+  const void* had_K;             /* device fp16 [K, K] row-major                                    */
+  int8_t* q;
+  int64_t q_row_stride;
+  float* scale;                  /* device fp32 [rows]                                              */
+  void* y;                       /* optional device fp16 [rows, cols] (contiguous): the rotated row */
+} lsvd_hadamard_quant_args;
+int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* args, void* stream);
+
+/* Weight-streaming W8A8 product for 1..64 tokens: acc[m, n] = sum_k a[m, k] * w[n, k] (int32, exact),
+ * optionally for a second weight matrix w2 (with its own activations a2, or the same ones) in the same pass.
+ *   epilogue 0: out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n])              (a quantised Linear)
+ *   epilogue 1: g = that for (w, a), u = that for (w2, a2); out = fp16(fp16(silu(g)) * u) (gate/up pair)
+ * n a multiple of 16, k a multiple of 64, rows 16-byte aligned.  Replaces the reference's fp16 Linear on
+ * fake-quantised tensors (ActQuantWrapper.forward, fake_quant/utils/quant_utils.py:319-333) and, on the kernel
+ * side, the w8a8 matmul + dequant kernels of kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:968-1021,1292-1338. */
+typedef struct lsvd_gemv_args {
+  int32_t m, n, k;
+  const int8_t* w;  int64_t w_row_stride;  const float* w_scale;
+  const int8_t* w2; int64_t w2_row_stride; const float* w2_scale;     /* w2 == NULL: single product        */
+  const int8_t* a;  int64_t a_row_stride;  const float* a_scale;  int64_t a_scale_stride;
+  const int8_t* a2; int64_t a2_row_stride; const float* a2_scale; int64_t a2_scale_stride;   /* a2 == NULL: use a */
+  int32_t epilogue;
+  void* out;                     /* device fp16                                                      */
+  int64_t out_row_stride;
+  int32_t out_col;
+  int32_t* acc_out;              /* optional device int32 [m, n] raw accumulators of (w, a)          */
+  int32_t* acc2_out;             /* optional, of (w2, a2)                                            */
+} lsvd_gemv_args;
+int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,33 @@ class AttnDecodeArgs(C.Structure):
     ]
 
 
+class ActQuantArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("cols", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
+        ("sign", C.c_void_p), ("fwht", C.c_int32), ("q", C.c_void_p), ("q_row_stride", C.c_int64),
+        ("scale", C.c_void_p), ("x_rot", C.c_void_p),
+    ]
+
+
+class HadamardQuantArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("cols", C.c_int32), ("K", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
+        ("had_K", C.c_void_p), ("q", C.c_void_p), ("q_row_stride", C.c_int64), ("scale", C.c_void_p), ("y", C.c_void_p),
+    ]
+
+
+class GemvArgs(C.Structure):
+    _fields_ = [
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("w", C.c_void_p), ("w_row_stride", C.c_int64), ("w_scale", C.c_void_p),
+        ("w2", C.c_void_p), ("w2_row_stride", C.c_int64), ("w2_scale", C.c_void_p),
+        ("a", C.c_void_p), ("a_row_stride", C.c_int64), ("a_scale", C.c_void_p), ("a_scale_stride", C.c_int64),
+        ("a2", C.c_void_p), ("a2_row_stride", C.c_int64), ("a2_scale", C.c_void_p), ("a2_scale_stride", C.c_int64),
+        ("epilogue", C.c_int32), ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("out_col", C.c_int32),
+        ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p),
+    ]
+
+
 # Every symbol include/lsvd_b200.h declares, with its ctypes signature.
 SIGNATURES = {
     "lsvd_abi_version": (C.c_int, []),
@@ -68,6 +95,9 @@ SIGNATURES = {
     "lsvd_cache_append": (C.c_int, [C.POINTER(AppendArgs), C.c_void_p]),
     "lsvd_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
+    "lsvd_act_quant": (C.c_int, [C.POINTER(ActQuantArgs), C.c_void_p]),
+    "lsvd_hadamard_quant": (C.c_int, [C.POINTER(HadamardQuantArgs), C.c_void_p]),
+    "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),
     "lsvd_attn_decode_plan": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
                                         C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
 }

@@ -142,6 +142,14 @@ __device__ __forceinline__ void mma_s8_16x8x32(int (&d)[4], uint32_t a0, uint32_
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Same with a zero accumulator on input (no registers to clear first).
+__device__ __forceinline__ void mma_s8_16x8x32_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                    uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 __device__ __forceinline__ uint4 ldg128(const int8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint2 ldg64(const int8_t* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
 
@@ -256,9 +264,10 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     float sc[4];                     // score of token g + 8j, in lanes t = 0, 1 of the quad
 #pragma unroll
     for (int rt = 0; rt < 2; ++rt) {
-      int d[4] = {0, 0, 0, 0};
+      int d[4];
+      mma_s8_16x8x32_zero(d, ka[2 * rt][0].x, ka[2 * rt + 1][0].x, ka[2 * rt][0].y, ka[2 * rt + 1][0].y, limb_b0[0], limb_b1[0]);
 #pragma unroll
-      for (int kb = 0; kb < 4; ++kb) {
+      for (int kb = 1; kb < 4; ++kb) {
         if (kb < nkb)
           mma_s8_16x8x32(d, ka[2 * rt][kb].x, ka[2 * rt + 1][kb].x, ka[2 * rt][kb].y, ka[2 * rt + 1][kb].y,
                          limb_b0[kb], limb_b1[kb]);
@@ -328,8 +337,8 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
         }
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          int d[4] = {0, 0, 0, 0};
-          mma_s8_16x8x32(d, x0[r], y0[r], x1[r], y1[r], wb0, wb1);
+          int d[4];
+          mma_s8_16x8x32_zero(d, x0[r], y0[r], x1[r], y1[r], wb0, wb1);
           float lo, hi;
           if (t4 == 0) {
             lo = fmaf(128.f, static_cast<float>(d[1]), static_cast<float>(d[0]));

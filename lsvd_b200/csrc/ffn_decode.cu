@@ -1,0 +1,442 @@
+// Hybrid SVD/RTN FFN for decode batches (1..64 tokens): per-token int8 quantisation (with the input and
+// the d_ffn Hadamard rotations), and the weight-streaming W8A8 products.
+//
+// The products are HBM streams of int8 weights: 100 MB per FFN call at the 7B shape whatever the batch.
+// A block owns 16 output channels (of one matrix, or of a gate/up pair); its eight warps split K, each
+// lane loads 16 contiguous weight bytes per instruction straight into the A fragments of exact int8
+// tensor-core MMAs (m16n8k32, int32 accumulators) whose B fragments are the tokens' int8 activations
+// (L1/L2 resident), and the warps' partial sums meet in shared memory for the dequantising epilogue.
+//
+// Reference semantics: fake_quant/utils/hybrid_ffn_utils.py:956-984 (module forward),
+// fake_quant/utils/quant_utils.py:201-212,30-33 (activation quantiser), :319-338 (wrapped Linear),
+// fake_quant/utils/hadamard_utils.py:99-113 (rotations).
+#include <cmath>
+
+#include "common.cuh"
+
+namespace lsvd {
+
+// ----------------------------------------------------------------------------------------------
+// per-token quantisation, optional power-of-two rotation
+// ----------------------------------------------------------------------------------------------
+struct ActQuantParams {
+  const __half* x;
+  int64_t x_row_stride;
+  const __half* sign;
+  int8_t* q;
+  int64_t q_row_stride;
+  float* scale;
+  __half* x_rot;
+  int32_t rows, cols, rotate;
+  float rot_scale;           // 1 / sqrt(cols)
+};
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < (blockDim.x >> 5)) ? red[lane] : 0.f;
+  r = warp_max(r);
+  return r;
+}
+
+// scale = absmax / 127 (1 for a zero row), both divisions IEEE: the codes must match the reference bit for bit.
+__device__ __forceinline__ float act_scale_of(float amax) { return amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f; }
+
+__device__ __forceinline__ int8_t act_code(float x, float s) {
+  const float y = rintf(__fdiv_rn(x, s));
+  return static_cast<int8_t>(fminf(fmaxf(y, -128.f), 127.f));
+}
+
+__global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ ActQuantParams p) {
+  extern __shared__ float row[];          // cols floats
+  __shared__ float red[8];
+  const int r = blockIdx.x;
+  const __half* x = p.x + r * p.x_row_stride;
+  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+    float v = __half2float(x[i]);
+    if (p.sign != nullptr) v *= __half2float(p.sign[i]);
+    row[i] = v;
+  }
+  __syncthreads();
+  if (p.rotate) {
+    // Sylvester butterflies in fp32, stride 1 first: the same additions in the same order as the
+    // reference's butterfly loop, so the rotated row is bit-identical.
+    for (int h = 1; h < p.cols; h <<= 1) {
+      for (int i = threadIdx.x; i < (p.cols >> 1); i += blockDim.x) {
+        const int j = ((i / h) * 2 * h) + (i % h);
+        const float a = row[j], b = row[j + h];
+        row[j] = a + b;
+        row[j + h] = a - b;
+      }
+      __syncthreads();
+    }
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+      const __half hv = __float2half_rn(row[i] * p.rot_scale);
+      row[i] = __half2float(hv);
+      if (p.x_rot != nullptr) p.x_rot[static_cast<int64_t>(r) * p.cols + i] = hv;
+    }
+    __syncthreads();
+  }
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+  amax = block_max(amax, red);
+  const float s = act_scale_of(amax);
+  if (threadIdx.x == 0) p.scale[r] = s;
+  int8_t* q = p.q + r * p.q_row_stride;
+  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) q[i] = act_code(row[i], s);
+}
+
+// ----------------------------------------------------------------------------------------------
+// (H_K kron H_nb) rotation + per-token quantisation, one block per token
+// ----------------------------------------------------------------------------------------------
+struct HadQuantParams {
+  const __half* x;
+  int64_t x_row_stride;
+  const __half* had_K;       // [K, K]
+  int8_t* q;
+  int64_t q_row_stride;
+  float* scale;
+  __half* y;
+  int32_t rows, cols, K, nb; // nb = cols / K, a power of two in [8, 128]
+  int32_t Kp, ld;            // K rounded up to 16, leading dimension (halves) of the staged matrices
+  float rot_scale;           // 1 / sqrt(cols)
+};
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col).  Lane (g, t):
+//   a0: row g, k 2t..2t+1   a1: row g+8, k 2t..   a2: row g, k 2t+8..   a3: row g+8, k 2t+8..
+//   b0: k 2t..2t+1, col g   b1: k 2t+8.., col g   d0,d1: row g, cols 2t,2t+1   d2,d3: row g+8
+__device__ __forceinline__ void mma_f16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_constant__ HadQuantParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half* Hs = reinterpret_cast<__half*>(smem_raw);                 // [Kp][ld]   had_K, zero padded
+  __half* Tt = Hs + p.Kp * p.ld;                                    // [nb][ld]   rotated blocks, transposed
+  __half* Ys = Tt + p.nb * p.ld;                                    // [K][nb]    result
+  __shared__ float red[8];
+  const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = p.K, Kp = p.Kp, nb = p.nb, ld = p.ld;
+
+  for (int i = threadIdx.x; i < Kp * ld; i += blockDim.x) {
+    const int a = i / ld, c = i - a * ld;
+    Hs[i] = (a < K && c < K) ? p.had_K[a * K + c] : __float2half_rn(0.f);
+  }
+  for (int i = threadIdx.x; i < nb * ld; i += blockDim.x) Tt[i] = __float2half_rn(0.f);
+  __syncthreads();
+
+  // ---- power-of-two part: each warp rotates whole blocks of nb entries; a lane holds entries lane + 32 i ----
+  const __half* x = p.x + r * p.x_row_stride;
+  const int per = nb >= 32 ? (nb >> 5) : 1;         // 1, 2 or 4 entries per lane (lanes >= nb idle when nb < 32)
+  const bool lane_on = lane < nb;
+  for (int k = warp; k < K; k += (blockDim.x >> 5)) {
+    float e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = (i < per && lane_on) ? __half2float(x[k * nb + i * 32 + lane]) : 0.f;
+    // strides 1..16 cross lanes; the entry with the stride bit clear gets a + b, the other a - b
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+      if (h >= nb) break;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (i < per) {
+          const float o = __shfl_xor_sync(0xffffffffu, e[i], h);
+          e[i] = (lane & h) ? o - e[i] : e[i] + o;
+        }
+      }
+    }
+    if (per >= 2) {                        // stride 32
+      const float a0 = e[0], a1 = e[1];
+      e[0] = a0 + a1; e[1] = a0 - a1;
+      if (per == 4) { const float b0 = e[2], b1 = e[3]; e[2] = b0 + b1; e[3] = b0 - b1; }
+    }
+    if (per == 4) {                        // stride 64
+      const float a0 = e[0], a2 = e[2], a1 = e[1], a3 = e[3];
+      e[0] = a0 + a2; e[2] = a0 - a2; e[1] = a1 + a3; e[3] = a1 - a3;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (i < per && lane_on) Tt[(i * 32 + lane) * ld + k] = __float2half_rn(e[i] * p.rot_scale);
+  }
+  __syncthreads();
+
+  // ---- had_K part on the tensor cores: Y[k', j] = sum_k Hs[k', k] * Tt[j, k] ----
+  const int g = lane >> 2, t = lane & 3;
+  const int mtiles = Kp >> 4, ntiles = nb >> 3, ktiles = Kp >> 4;
+  for (int tile = warp; tile < mtiles * ntiles; tile += (blockDim.x >> 5)) {
+    const int mt = tile / ntiles, nt = tile - mt * ntiles;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    const __half* arow0 = Hs + (mt * 16 + g) * ld + 2 * t;
+    const __half* arow1 = arow0 + 8 * ld;
+    const __half* brow = Tt + (nt * 8 + g) * ld + 2 * t;
+    for (int kt = 0; kt < ktiles; ++kt) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(arow0 + kt * 16);
+      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(arow1 + kt * 16);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(arow0 + kt * 16 + 8);
+      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(arow1 + kt * 16 + 8);
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + kt * 16);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + kt * 16 + 8);
+      mma_f16_16x8x16(d, a0, a1, a2, a3, b0, b1);
+    }
+    const int row0 = mt * 16 + g, col = nt * 8 + 2 * t;
+    if (row0 < K) {
+      Ys[row0 * nb + col] = __float2half_rn(d[0]);
+      Ys[row0 * nb + col + 1] = __float2half_rn(d[1]);
+    }
+    if (row0 + 8 < K) {
+      Ys[(row0 + 8) * nb + col] = __float2half_rn(d[2]);
+      Ys[(row0 + 8) * nb + col + 1] = __float2half_rn(d[3]);
+    }
+  }
+  __syncthreads();
+
+  // ---- per-token quantisation ----
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) amax = fmaxf(amax, fabsf(__half2float(Ys[i])));
+  amax = block_max(amax, red);
+  const float s = act_scale_of(amax);
+  if (threadIdx.x == 0) p.scale[r] = s;
+  int8_t* q = p.q + r * p.q_row_stride;
+  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+    const __half hv = Ys[i];
+    q[i] = act_code(__half2float(hv), s);
+    if (p.y != nullptr) p.y[static_cast<int64_t>(r) * p.cols + i] = hv;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// weight-streaming W8A8 product
+// ----------------------------------------------------------------------------------------------
+struct GemvParams {
+  const int8_t* w;  int64_t w_row_stride;  const float* w_scale;
+  const int8_t* w2; int64_t w2_row_stride; const float* w2_scale;
+  const int8_t* a;  int64_t a_row_stride;  const float* a_scale;  int64_t a_scale_stride;
+  const int8_t* a2; int64_t a2_row_stride; const float* a2_scale; int64_t a2_scale_stride;
+  __half* out; int64_t out_row_stride; int32_t out_col;
+  int32_t* acc_out; int32_t* acc2_out;
+  int32_t m, n, k, epilogue;
+};
+
+constexpr int kGemvWarps = 8;
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_u4(const int8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// NT = token tiles of 8 (tokens beyond m read as zero); DUAL = a gate/up pair of matrices in one pass;
+// SPLIT_B = the second matrix has its own activations.
+template <int NT, bool DUAL, bool SPLIT_B>
+__global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid_constant__ GemvParams p) {
+  extern __shared__ __align__(16) int red[];      // [warp][matrix][NT][4][32]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  constexpr int NMAT = DUAL ? 2 : 1;
+
+  int acc[NMAT][NT][4];
+#pragma unroll
+  for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0;
+
+  // this warp's share of K, in spans of 64 (a lane's 16 bytes per row cover two 32-wide MMA steps)
+  const int spans = p.k >> 6;
+  const int s_begin = (warp * spans) / kGemvWarps, s_end = ((warp + 1) * spans) / kGemvWarps;
+  const int8_t* wr0 = p.w + (row0 + g) * p.w_row_stride + 16 * t;
+  const int8_t* wr1 = wr0 + 8 * p.w_row_stride;
+  const int8_t* w2r0 = DUAL ? p.w2 + (row0 + g) * p.w2_row_stride + 16 * t : nullptr;
+  const int8_t* w2r1 = DUAL ? w2r0 + 8 * p.w2_row_stride : nullptr;
+
+  for (int s = s_begin; s < s_end; ++s) {
+    const int ko = s * 64;
+    const uint4 x0 = ldg_u4(wr0 + ko), x1 = ldg_u4(wr1 + ko);
+    uint4 y0, y1;
+    if (DUAL) {
+      y0 = ldg_u4(w2r0 + ko);
+      y1 = ldg_u4(w2r1 + ko);
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const int tok = j * 8 + g;
+      uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+      if (tok < p.m) bv = ldg_u4(p.a + tok * p.a_row_stride + ko + 16 * t);
+      // the MMA's k index is a permutation of the 32 columns that A and B share: k 4t..4t+3 <-> the first
+      // four of a lane's bytes, k 16+4t.. <-> the next four
+      mma_s8(acc[0][j], x0.x, x1.x, x0.y, x1.y, bv.x, bv.y);
+      mma_s8(acc[0][j], x0.z, x1.z, x0.w, x1.w, bv.z, bv.w);
+      if (DUAL) {
+        uint4 bw = bv;
+        if (SPLIT_B) {
+          bw = make_uint4(0u, 0u, 0u, 0u);
+          if (tok < p.m) bw = ldg_u4(p.a2 + tok * p.a2_row_stride + ko + 16 * t);
+        }
+        mma_s8(acc[NMAT - 1][j], y0.x, y1.x, y0.y, y1.y, bw.x, bw.y);
+        mma_s8(acc[NMAT - 1][j], y0.z, y1.z, y0.w, y1.w, bw.z, bw.w);
+      }
+    }
+  }
+
+  // ---- sum the warps' shares ----
+  int* mine = red + warp * (NMAT * NT * 4 * 32);
+#pragma unroll
+  for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) mine[((mtx * NT + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
+  __syncthreads();
+
+  // element e of a matrix: (j, c, lane) -> row = g + 8 (c >> 1), token = 8 j + 2 t + (c & 1)
+  for (int e = threadIdx.x; e < NT * 4 * 32; e += blockDim.x) {
+    const int el = e & 31, c = (e >> 5) & 3, j = e >> 7;
+    const int row = row0 + (el >> 2) + 8 * (c >> 1);
+    const int tok = j * 8 + 2 * (el & 3) + (c & 1);
+    int sum0 = 0, sum1 = 0;
+#pragma unroll
+    for (int wi = 0; wi < kGemvWarps; ++wi) {
+      sum0 += red[wi * (NMAT * NT * 4 * 32) + e];
+      if (DUAL) sum1 += red[wi * (NMAT * NT * 4 * 32) + NT * 4 * 32 + e];
+    }
+    if (tok >= p.m) continue;
+    if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = sum0;
+    if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = sum1;
+    if (p.out == nullptr) continue;
+    const float sa = p.a_scale[tok * p.a_scale_stride];
+    const __half v0 = __float2half_rn((static_cast<float>(sum0) * sa) * p.w_scale[row]);
+    __half res = v0;
+    if (DUAL) {
+      const float sb = SPLIT_B ? p.a2_scale[tok * p.a2_scale_stride] : sa;
+      const __half u = __float2half_rn((static_cast<float>(sum1) * sb) * p.w2_scale[row]);
+      // silu in fp32 rounded to fp16, then an fp16 product: how PyTorch evaluates F.silu(g) * u on fp16 tensors
+      const __half sg = __float2half_rn(silu_f(__half2float(v0)));
+      res = __float2half_rn(__half2float(sg) * __half2float(u));
+    }
+    p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = res;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// host
+// ----------------------------------------------------------------------------------------------
+static bool is_pow2(int n) { return n > 0 && (n & (n - 1)) == 0; }
+
+template <int NT, bool DUAL, bool SPLIT_B>
+static int launch_gemv(const GemvParams& p, cudaStream_t st) {
+  const int smem = kGemvWarps * (DUAL ? 2 : 1) * NT * 4 * 32 * 4;
+  auto kern = w8a8_gemv_kernel<NT, DUAL, SPLIT_B>;
+  if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
+  kern<<<p.n / 16, kGemvWarps * 32, smem, st>>>(p);
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}
+
+template <int NT>
+static int launch_gemv_nt(const GemvParams& p, bool dual, bool split, cudaStream_t st) {
+  if (!dual) return launch_gemv<NT, false, false>(p, st);
+  if (split) return launch_gemv<NT, true, true>(p, st);
+  return launch_gemv<NT, true, false>(p, st);
+}
+
+}  // namespace lsvd
+
+extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
+  using namespace lsvd;
+  if (a == nullptr || a->rows < 0 || a->cols <= 0 || a->cols > 16384) return LSVD_ERR_INVALID_ARG;
+  if (a->rows == 0) return LSVD_OK;
+  if (!a->x || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
+  const bool rotate = a->sign != nullptr || a->fwht != 0;
+  if (rotate && !is_pow2(a->cols)) return LSVD_ERR_INVALID_ARG;
+  ActQuantParams p{};
+  p.x = static_cast<const __half*>(a->x);
+  p.x_row_stride = a->x_row_stride;
+  p.sign = static_cast<const __half*>(a->sign);
+  p.q = a->q;
+  p.q_row_stride = a->q_row_stride;
+  p.scale = a->scale;
+  p.x_rot = static_cast<__half*>(a->x_rot);
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.rotate = rotate ? 1 : 0;
+  p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
+  const int smem = a->cols * 4;
+  if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(act_quant_kernel), smem));
+  act_quant_kernel<<<a->rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}
+
+extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stream) {
+  using namespace lsvd;
+  if (a == nullptr || a->rows < 0 || a->cols <= 0 || a->K <= 1 || a->K > 256) return LSVD_ERR_INVALID_ARG;
+  if (a->rows == 0) return LSVD_OK;
+  if (!a->x || !a->had_K || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
+  if (a->cols % a->K) return LSVD_ERR_INVALID_ARG;
+  const int nb = a->cols / a->K;
+  if (!is_pow2(nb) || nb < 8 || nb > 128) return LSVD_ERR_UNSUPPORTED;
+  HadQuantParams p{};
+  p.x = static_cast<const __half*>(a->x);
+  p.x_row_stride = a->x_row_stride;
+  p.had_K = static_cast<const __half*>(a->had_K);
+  p.q = a->q;
+  p.q_row_stride = a->q_row_stride;
+  p.scale = a->scale;
+  p.y = static_cast<__half*>(a->y);
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.K = a->K;
+  p.nb = nb;
+  p.Kp = (a->K + 15) / 16 * 16;
+  p.ld = p.Kp + 8;
+  p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
+  const int smem = (p.Kp * p.ld + nb * p.ld + a->K * nb) * 2;
+  if (smem > device_max_smem_optin()) return LSVD_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(hadamard_quant_kernel), smem));
+  hadamard_quant_kernel<<<a->rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}
+
+extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
+  using namespace lsvd;
+  if (a == nullptr || a->m <= 0 || a->m > 64 || a->n <= 0 || (a->n % 16) || a->k <= 0 || (a->k % 64))
+    return LSVD_ERR_INVALID_ARG;
+  if (!a->w || !a->a) return LSVD_ERR_INVALID_ARG;
+  if (a->out != nullptr && (!a->w_scale || !a->a_scale)) return LSVD_ERR_INVALID_ARG;
+  const bool dual = a->w2 != nullptr;
+  if (dual != (a->epilogue == 1)) return LSVD_ERR_INVALID_ARG;
+  if (dual && a->out != nullptr && !a->w2_scale) return LSVD_ERR_INVALID_ARG;
+  const bool split = dual && a->a2 != nullptr;
+  if (split && a->out != nullptr && !a->a2_scale) return LSVD_ERR_INVALID_ARG;
+  if (!aligned(a->w, 16) || (a->w_row_stride % 16) || !aligned(a->a, 16) || (a->a_row_stride % 16)) return LSVD_ERR_INVALID_ARG;
+  if (dual && (!aligned(a->w2, 16) || (a->w2_row_stride % 16))) return LSVD_ERR_INVALID_ARG;
+  if (split && (!aligned(a->a2, 16) || (a->a2_row_stride % 16))) return LSVD_ERR_INVALID_ARG;
+  GemvParams p{};
+  p.w = a->w; p.w_row_stride = a->w_row_stride; p.w_scale = a->w_scale;
+  p.w2 = a->w2; p.w2_row_stride = a->w2_row_stride; p.w2_scale = a->w2_scale;
+  p.a = a->a; p.a_row_stride = a->a_row_stride; p.a_scale = a->a_scale; p.a_scale_stride = a->a_scale_stride;
+  p.a2 = a->a2; p.a2_row_stride = a->a2_row_stride; p.a2_scale = a->a2_scale; p.a2_scale_stride = a->a2_scale_stride;
+  p.out = static_cast<__half*>(a->out); p.out_row_stride = a->out_row_stride; p.out_col = a->out_col;
+  p.acc_out = a->acc_out; p.acc2_out = a->acc2_out;
+  p.m = a->m; p.n = a->n; p.k = a->k; p.epilogue = a->epilogue;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->m <= 8) return launch_gemv_nt<1>(p, dual, split, st);
+  if (a->m <= 16) return launch_gemv_nt<2>(p, dual, split, st);
+  if (a->m <= 32) return launch_gemv_nt<4>(p, dual, split, st);
+  return launch_gemv_nt<8>(p, dual, split, st);
+}

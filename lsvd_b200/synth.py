@@ -52,3 +52,31 @@ def attention_inputs(batch: int, num_heads: int, head_dim: int, k_ranks, v_ranks
         b_req = torch.arange(batch, dtype=torch.int32)
     return dict(latent_k=lat_k, latent_v=lat_v, up_k=up_k, up_v=up_v, q=q, req_to_token=r2t, b_req_idx=b_req,
                 b_seq_len=torch.tensor(list(seq_lens), dtype=torch.int32), max_len=max_len, n_slots=n_slots)
+
+
+def sign_matrix(K: int, seed: int = 0):
+    """A seeded +-1 matrix [K, K] standing in for the non-power-of-two Hadamard factor of d_ffn when the
+    reference's literal matrices are not at hand.  The kernels treat ``had_K`` as an arbitrary input matrix, so
+    timings and parity against the CPU checker do not depend on it being orthogonal."""
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, 2, (K, K), generator=g) * 2 - 1).to(torch.float16)
+
+
+def ffn_weights(d_in: int, d_ffn: int, rank: int, n_svd: int, seed: int = 0, std: float = 0.02, had_K=None,
+                K: int = 1, input_had: bool = True, mse: bool = False) -> dict:
+    """Seeded hybrid-FFN weights on the CPU: N(0, std) draws, int8 RTN per output channel.
+
+    A seeded ``randperm(d_ffn)[:n_svd]`` picks the SVD channel group; the weights being random, the permutation
+    only fixes the input-column order [SVD | RTN] of the down projection, which is the order they are drawn in.
+    Returns the dict ``HybridFFN`` and the CPU checker both take.
+    """
+    from .ffn import quantize_weight_rtn
+    g = torch.Generator().manual_seed(seed)
+    n_q = d_ffn - n_svd
+    w = {"K": K, "had_K": had_K, "online_had": True}
+    for name, shape in (("U", (2 * rank, d_in)), ("Vg", (n_svd, rank)), ("Vu", (n_svd, rank)),
+                        ("Wg", (n_q, d_in)), ("Wu", (n_q, d_in)), ("Wd", (d_in, d_ffn))):
+        w[name + "_q"], w[name + "_s"] = quantize_weight_rtn(torch.randn(*shape, generator=g) * std, mse)
+    w["perm"] = torch.randperm(d_ffn, generator=g)
+    w["had_sign"] = (torch.randint(0, 2, (d_in,), generator=g).float() * 2 - 1).to(torch.float16) if input_had else None
+    return w
