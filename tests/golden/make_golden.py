@@ -251,7 +251,7 @@ def gen_fake_quant_side():
     save("hadamard", **res)
 
     # 6. the hybrid FFN module itself, fp16 on the CPU, with every sub-module output captured
-    d_in, d_ffn, r = 128, 172 * 8, 64
+    d_in, d_ffn, r = 128, 172 * 16, 64
     n_svd = d_ffn // 2
     n_q = d_ffn - n_svd
 

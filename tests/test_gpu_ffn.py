@@ -58,7 +58,7 @@ def test_input_rotation_bit_exact():
     assert torch.equal(rot2.cpu(), offn.hadamard_full(x, None, 1))
 
 
-@pytest.mark.parametrize("K,nb", [(172, 64), (108, 128), (172, 8)])
+@pytest.mark.parametrize("K,nb", [(172, 64), (108, 128), (172, 8), (172, 16)])
 def test_hadamard_quant_against_oracle(K, nb):
     g = load_golden("hadamard")
     hk = unpack_had(g[f"had{K}_bits"], K)
