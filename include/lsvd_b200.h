@@ -143,6 +143,25 @@ int lsvd_attn_decode_plan(int32_t batch, int32_t num_heads, const int32_t* k_off
                           int32_t max_len_in_batch, int32_t* items_per_request, int32_t* item_bytes,
                           int32_t* num_blocks);
 
+/* Decode attention without a caller workspace (no counterpart in the reference; added for hosts that cannot
+ * allocate device memory on the decode path: servers whose memory pool owns the whole GPU, plugins inside another
+ * runtime's budget, steps recorded while allocation is off limits).  Same arguments and results as
+ * lsvd_attn_decode; `workspace` and `workspace_bytes` are ignored.  The scratch is a fixed array of
+ * LSVD_STATIC_SCRATCH_BYTES inside the library's device image: every GPU that loads the library holds it until
+ * the process exits, and every call on that GPU uses the same bytes.
+ *   - A problem whose scratch need exceeds the array returns LSVD_ERR_WORKSPACE and launches nothing
+ *     (the need grows with batch x (heads + context / item size); batch 16 x context 4096 at the 7B shape takes ~3 MB).
+ *   - The call makes no cudaMalloc / cudaFree and uses no allocating library routine.  The first call on a
+ *     device looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
+ *     stream capture.
+ *   - The array keeps what the last call left in it; the one word that must start at zero (the work counter)
+ *     is cleared on the stream by the first kernel of each call.  Two calls that overlap on the GPU (different
+ *     streams, no ordering) race on the scratch: order them, or give one of them lsvd_attn_decode with its own
+ *     workspace. */
+#define LSVD_STATIC_SCRATCH_BYTES (8u << 20)
+size_t lsvd_attn_decode_static_scratch_bytes(void);
+int lsvd_attn_decode_static(const lsvd_attn_decode_args* args, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Hybrid SVD/RTN FFN, decode (1..64 tokens): building blocks and the fused chain.
  * Semantics follow fake_quant/utils/hybrid_ffn_utils.py:956-984 (HybridSVDQuantFFN.forward) with real

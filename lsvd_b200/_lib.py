@@ -95,6 +95,8 @@ SIGNATURES = {
     "lsvd_cache_append": (C.c_int, [C.POINTER(AppendArgs), C.c_void_p]),
     "lsvd_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
+    "lsvd_attn_decode_static_scratch_bytes": (C.c_size_t, []),
+    "lsvd_attn_decode_static": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_act_quant": (C.c_int, [C.POINTER(ActQuantArgs), C.c_void_p]),
     "lsvd_hadamard_quant": (C.c_int, [C.POINTER(HadamardQuantArgs), C.c_void_p]),
     "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),

@@ -27,6 +27,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -676,4 +677,62 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
   merge_up_kernel<<<dim3(a->num_heads, a->batch), 128, 0, st>>>(mp);
   LSVD_CUDA_TRY(cudaGetLastError());
   return LSVD_OK;
+}
+
+// ----------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory
+// ----------------------------------------------------------------------------------------------
+// Some hosts of this library may not call cudaMalloc on the path that runs a decode step: an inference
+// server that has handed all of its device memory to a paged KV-cache pool at start-up, a plugin that
+// runs inside another runtime's memory budget, or a step that is being recorded into a CUDA graph, where
+// allocation calls are not allowed.  lsvd_attn_decode leaves the workspace to the caller; this variant
+// brings its own: a fixed array in the library's device image, present on every GPU that loads the
+// library from load time until the process exits.
+namespace lsvd {
+
+static __device__ __align__(256) unsigned char g_static_scratch[LSVD_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {nullptr};     // device address of the array, per device
+static std::mutex g_static_scratch_mu;
+
+// The array's name is only a host-side handle here; the device address has to be asked for, once per
+// device, with that device current.
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  LSVD_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return LSVD_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    LSVD_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) return LSVD_ERR_CUDA;
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return LSVD_OK;
+}
+
+}  // namespace lsvd
+
+extern "C" size_t lsvd_attn_decode_static_scratch_bytes(void) { return LSVD_STATIC_SCRATCH_BYTES; }
+
+extern "C" int lsvd_attn_decode_static(const lsvd_attn_decode_args* a, void* stream) {
+  using namespace lsvd;
+  if (a == nullptr || a->k_off == nullptr || a->v_off == nullptr || a->num_heads <= 0 || a->num_heads > LSVD_MAX_HEADS)
+    return LSVD_ERR_INVALID_ARG;
+  // Size check first, against the exact need of this problem: too large a batch or context is refused, not truncated.
+  HostPlan hp;
+  const int rc = make_plan(a->batch, a->num_heads, a->k_off, a->v_off, a->max_len_in_batch, &hp);
+  if (rc != LSVD_OK) return rc;
+  const WorkspaceLayout wl =
+      workspace_layout(a->batch, a->num_heads, a->k_off[a->num_heads], hp.items_per_request, hp.acc_per_request);
+  if (wl.total > LSVD_STATIC_SCRATCH_BYTES) return LSVD_ERR_WORKSPACE;
+  void* scratch = nullptr;
+  const int rc2 = static_scratch_address(&scratch);
+  if (rc2 != LSVD_OK) return rc2;
+  lsvd_attn_decode_args b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = LSVD_STATIC_SCRATCH_BYTES;
+  return lsvd_attn_decode(&b, stream);
 }
