@@ -3,11 +3,12 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-A "step" is one decode step of one decoder-layer's hot path over one batch of synthetic
-requests: append this step's K/V latents to the int8 latent cache, then int8 latent
-flash-decoding attention over the whole context.  The default workload is the attention
-block of BASELINE config 3 (LLaVA-Next-7B layer shape, batch 16, context 4096, ragged
-per-head ranks with mean 64); the metric is decode tokens/s for that layer step.
+A "step" is one decode step of one decoder layer's hot path over one batch of synthetic
+requests.  Default workload `c3_layer` (BASELINE config 3 shape): append this step's K/V
+latents to the int8 latent cache, int8 latent flash-decoding attention over the whole
+context (batch 16, context 4096, ragged per-head ranks, mean 64), then the hybrid SVD/RTN
+FFN (4096/11008) on the 16 tokens.  Metric: decode tokens/s of that layer step.  Other
+workloads: `c2_ffn` (--tokens 1/8/64), `c3_attention`, `c1_attention`.
 
 N > 1 (launched by torch.distributed.run): requests are independent, so each rank serves
 its own batch of the same size with no data-path collective (weak scaling).
@@ -32,6 +33,13 @@ sys.path.insert(0, ROOT)
 import torch
 
 WORKLOADS = {
+    "c3_layer": dict(batch=16, heads=32, head_dim=128, context=4096, ragged=True, ffn=True,
+                     desc="BASELINE config 3 decode hot path of one LLaVA-Next-7B-shape layer: batch 16, context 4096, "
+                          "ragged per-head K/V ranks (multiples of 16 in [16,128], mean 64); hybrid FFN 4096/11008, "
+                          "rank 512, 50 % SVD channels, Hadamard 64 x 172"),
+    "c2_ffn": dict(batch=8, heads=0, head_dim=0, context=0, ragged=False, ffn=True, ffn_only=True,
+                   desc="BASELINE config 2: hybrid FFN decode block 4096/11008, rank 512, 50 % SVD channels, input "
+                        "rotation + Hadamard 64 x 172, batch of --tokens tokens (1/8/64)"),
     # name: batch, heads, head_dim, context, ragged?
     "c3_attention": dict(batch=16, heads=32, head_dim=128, context=4096, ragged=True,
                          desc="BASELINE config 3 attention block: LLaVA-Next-7B layer shape, batch 16, "
@@ -138,6 +146,24 @@ def algorithmic_bytes(wl):
     return cache + scales + slots
 
 
+FFN_SHAPE = dict(d_in=4096, d_ffn=11008, rank=512, n_svd=5504, K=172)
+FFN_BYTES = 2 * 4096 * 512 + 2 * 512 * 5504 + 2 * 5504 * 4096 + 11008 * 4096      # int8 weights of one FFN
+FFN_RTN_PAIR_BYTES = 2 * 5504 * 4096                                               # its largest launch
+
+
+def make_ffn(device, seed, copies):
+    """`copies` hybrid FFNs with different seeded weights (cycled so that weights never sit in L2 between steps)."""
+    from lsvd_b200 import synth
+    from lsvd_b200.ffn import HybridFFN
+    hk = synth.sign_matrix(FFN_SHAPE["K"], seed=0)
+    out = []
+    for c in range(copies):
+        w = synth.ffn_weights(FFN_SHAPE["d_in"], FFN_SHAPE["d_ffn"], FFN_SHAPE["rank"], FFN_SHAPE["n_svd"],
+                              seed=seed + c, had_K=hk, K=FFN_SHAPE["K"])
+        out.append(HybridFFN({k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}))
+    return out
+
+
 def run_ours(args, rank, world, local):
     from lsvd_b200 import _lib, cache_append, token_decode_attention_int8_latent_absorb
     from lsvd_b200.attention import attn_decode_workspace_bytes
@@ -147,31 +173,53 @@ def run_ours(args, rank, world, local):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    w = WORKLOADS[args.workload]
-    wl = make_workload(w, dev, seed=1000 + rank)
-    lay, st, B, H, D = wl["layout"], wl["state"], wl["B"], wl["H"], wl["D"]
-    ws = torch.empty(attn_decode_workspace_bytes(B, lay, wl["seq"]), dtype=torch.uint8, device=dev)
-    out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    # per-step inputs: this step's query and K/V latents.  Host copies live in pinned memory for the e2e leg.
+    w = dict(WORKLOADS[args.workload])
+    has_attn = not w.get("ffn_only", False)
+    has_ffn = w.get("ffn", False)
+    if w.get("ffn_only"):
+        w["batch"] = args.tokens
+    B = w["batch"]
     g = torch.Generator().manual_seed(7 + rank)
     n_in = 8
-    host_q = [torch.randn(B, H, D, generator=g).half().pin_memory() for _ in range(n_in)]
-    host_lk = [torch.randn(B, lay.sum_k, generator=g).half().pin_memory() for _ in range(n_in)]
-    host_lv = [torch.randn(B, lay.sum_v, generator=g).half().pin_memory() for _ in range(n_in)]
-    dev_q = [t.to(dev) for t in host_q]
-    dev_lk = [t.to(dev) for t in host_lk]
-    dev_lv = [t.to(dev) for t in host_lv]
-    q_in = torch.empty_like(dev_q[0])
-    lk_in = torch.empty_like(dev_lk[0])
-    lv_in = torch.empty_like(dev_lv[0])
-    host_out = torch.empty(B, H, D, dtype=torch.float16).pin_memory()
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    host_in, dev_in, stage_in = [], [], []
+    launches = 0
 
-    def step(q, lk, lv, ev=None):
-        cache_append(lay, lk, lv, st.mem_index, wl["ck"], wl["sk"], wl["cv"], wl["sv"])
-        token_decode_attention_int8_latent_absorb(q, st, H, D, wl["ck"], wl["sk"], wl["cv"], wl["sv"], wl["up_k"],
-                                                  wl["up_v"], layout=lay, out=out, workspace=ws, status_word=status,
-                                                  timing_events=ev)
+    if has_attn:
+        wl = make_workload(w, dev, seed=1000 + rank)
+        lay, st, H, D = wl["layout"], wl["state"], wl["H"], wl["D"]
+        ws = torch.empty(attn_decode_workspace_bytes(B, lay, wl["seq"]), dtype=torch.uint8, device=dev)
+        attn_out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+        shapes = [(B, H, D), (B, lay.sum_k), (B, lay.sum_v)]
+        launches += 4
+    else:
+        shapes = [(B, FFN_SHAPE["d_in"])]
+    if has_ffn:
+        ffns = make_ffn(dev, seed=50 + rank, copies=1 if has_attn else 3)
+        ffn_out = torch.empty(B, FFN_SHAPE["d_in"], dtype=torch.float16, device=dev)
+        launches += 7
+    # per-step inputs; host copies live in pinned memory for the end-to-end leg
+    for shp in shapes:
+        host_in.append([torch.randn(*shp, generator=g).half().pin_memory() for _ in range(n_in)])
+        dev_in.append([t.to(dev) for t in host_in[-1]])
+        stage_in.append(torch.empty_like(dev_in[-1][0]))
+    result = ffn_out if has_ffn else attn_out
+    host_out = torch.empty(result.shape, dtype=torch.float16).pin_memory()
+
+    def step(inputs, i, ev=None):
+        """One decode step of the layer's hot path.  The FFN takes the attention output's heads flattened
+        (hidden = heads x head_dim) as its input: the data dependency of the layer without the projections."""
+        if has_attn:
+            q, lk, lv = inputs
+            cache_append(lay, lk, lv, st.mem_index, wl["ck"], wl["sk"], wl["cv"], wl["sv"])
+            token_decode_attention_int8_latent_absorb(q, st, H, D, wl["ck"], wl["sk"], wl["cv"], wl["sv"], wl["up_k"],
+                                                      wl["up_v"], layout=lay, out=attn_out, workspace=ws,
+                                                      status_word=status, timing_events=ev)
+            x = attn_out.view(B, H * D)
+        else:
+            x = inputs[0]
+        if has_ffn:
+            ffns[i % len(ffns)](x, out=ffn_out)
 
     def barrier():
         if world > 1:
@@ -179,43 +227,89 @@ def run_ours(args, rank, world, local):
             dist.barrier()
         torch.cuda.synchronize()
 
+    pick = lambda pool, i: [p[i % n_in] for p in pool]
     for i in range(max(args.warmup, 3)):
-        step(dev_q[i % n_in], dev_lk[i % n_in], dev_lv[i % n_in])
+        step(pick(dev_in, i), i)
     torch.cuda.synchronize()
 
-    # ---- device-resident leg (value) with the streaming kernel timed on its own by event pairs ----
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for a, b in kev:
-        a.record()
-        b.record()
+    # CUDA graphs of the step, as the reference's harness replays its layer (kernels/layer_bench/ffn_kernel/utils.py:687-706):
+    # one graph per FFN weight copy, all reading the staging inputs.
+    graphs = []
+    side = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(side):
+        for c in range(len(ffns) if has_ffn else 1):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                step(stage_in, c)
+            graphs.append(gr)
     torch.cuda.synchronize()
+
+    def load_inputs(i, from_host):
+        src = host_in if from_host else dev_in
+        for dst, pool in zip(stage_in, src):
+            dst.copy_(pool[i % n_in], non_blocking=True)
+
+    for i in range(3):
+        load_inputs(i, False)
+        graphs[i % len(graphs)].replay()
+    torch.cuda.synchronize()
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    # ---- device-resident leg (value): inputs already in HBM, graph replays ----
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for i in range(args.steps):
-        step(dev_q[i % n_in], dev_lk[i % n_in], dev_lv[i % n_in], kev[i])
+        load_inputs(i, False)                       # device-to-device refresh of this step's inputs (a few hundred KB)
+        graphs[i % len(graphs)].replay()
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)
-    kernel_ms = [a.elapsed_time(b) for a, b in kev]
-
-    # ---- end-to-end leg: host inputs from pinned memory, result read back, every step ----
+    # ---- end-to-end leg: this step's inputs from pinned host memory, the result read back, every step ----
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     f0.record()
     for i in range(args.steps):
-        q_in.copy_(host_q[i % n_in], non_blocking=True)
-        lk_in.copy_(host_lk[i % n_in], non_blocking=True)
-        lv_in.copy_(host_lv[i % n_in], non_blocking=True)
-        step(q_in, lk_in, lv_in)
-        host_out.copy_(out, non_blocking=True)
+        load_inputs(i, True)
+        graphs[i % len(graphs)].replay()
+        host_out.copy_(result, non_blocking=True)
     f1.record()
     barrier()
     ms_e2e = f0.elapsed_time(f1)
+    # ---- the dominant kernel on its own, timed by event pairs on the launching stream (eager steps) ----
+    kernel_ms = []
+    if has_attn:
+        kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in kev:
+            a.record()
+            b.record()
+        torch.cuda.synchronize()
+        for i in range(args.steps):
+            step(pick(dev_in, i), i, kev[i])
+        torch.cuda.synchronize()
+        kernel_ms = [a.elapsed_time(b) for a, b in kev]
+    else:
+        # the RTN gate/up pair (45 MB of weights) of the FFN: the plan's fifth launch, other copies' weights in between
+        x = dev_in[0][0]
+        for f in ffns:
+            f(x, out=ffn_out)
+        kev = []
+        for i in range(args.steps):
+            f = ffns[i % len(ffns)]
+            _, calls = f._plan(B, dev)
+            fn, a = calls[4]
+            import ctypes
+            s_ptr = torch.cuda.current_stream().cuda_stream
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            fn(ctypes.byref(a), s_ptr)
+            a1.record()
+            kev.append((a0, a1))
+        torch.cuda.synchronize()
+        kernel_ms = [a.elapsed_time(b) for a, b in kev]
     clocks = sampler.stop() if rank == 0 else None
     if status.item() != 0:
         raise RuntimeError(f"device status word = {status.item()}")
@@ -235,55 +329,79 @@ def run_ours(args, rank, world, local):
     except Exception:
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
-    abytes = algorithmic_bytes(wl)
     k_ms = statistics.mean(kernel_ms)
+    if has_attn:
+        abytes, kname = algorithmic_bytes(wl), "latent_stream_kernel"
+    else:
+        abytes, kname = FFN_RTN_PAIR_BYTES + B * 4096 + 2 * 5504 * 4, "w8a8_gemv_kernel (RTN gate/up pair)"
     achieved = abytes / (k_ms * 1e-3) / 1e9
-    h2d = sum(t.numel() * t.element_size() for t in (host_q[0], host_lk[0], host_lv[0]))
+    step_bytes = (algorithmic_bytes(wl) if has_attn else 0) + (FFN_BYTES if has_ffn else 0)
+    h2d = sum(p[0].numel() * p[0].element_size() for p in host_in)
     d2h = host_out.numel() * host_out.element_size()
+    what = []
+    if has_attn:
+        what.append("cache append (K+V) + int8 latent decode attention (absorb) + V up-projection")
+    if has_ffn:
+        what.append("hybrid SVD/RTN FFN (input rotation, A8 quantisers, SVD and RTN gate/up, Hadamard 64x172, down)")
     line = {
         "metric": "decode_tokens_per_s", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8 latents, fp32 softmax/accumulate, fp16 out",
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax, fp16 out",
         "data": "synthetic",
-        "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B, "context": wl["L"],
-                   "layers": 1, "step": "cache append (K+V) + int8 latent decode attention (absorb) + V up-projection",
-                   "l2": "inputs larger than L2: the cache read by every step is %.0f MB" % (abytes / 1e6)},
+        "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B, "layers": 1, "step": " + ".join(what),
+                   "launch": "CUDA graph replay of the step",
+                   "l2": "inputs larger than L2: every step streams %.0f MB of cache/weights%s"
+                         % (step_bytes / 1e6, "" if has_attn else " (three weight copies cycled, 300 MB)")},
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": 4 * args.steps,
-        "roofline": {"kernel": "latent_stream_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "of": "measured" if "hbm_gbs" in peaks else "fallback",
-                     "traffic": None, "algorithmic_bytes_per_launch": abytes, "kernel_us": k_ms * 1e3,
-                     "frac_of_8TBs": achieved / 8000.0},
-        "parts": {"latent_decode_us_per_step": k_ms * 1e3, "latent_decode_hbm_gbs": achieved,
-                  "step_us": ms_step * 1e3},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "of": "measured" if "hbm_gbs" in peaks else "fallback", "traffic": None,
+                     "algorithmic_bytes_per_launch": abytes, "kernel_us": k_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
+        "parts": {"step_us": ms_step * 1e3, "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                  "step_algorithmic_bytes": step_bytes, "dominant_kernel_us": k_ms * 1e3},
         "clocks": clocks,
     }
     return line
 
 
-def cpu_baseline(w, seconds_hint=15.0, threads=None):
-    """The oracle (a CPU port of the reference's algorithm) timed on the host cores on a bounded sample:
-    a slice of the batch of the same workload."""
-    from oracle import attention as oattn, quant
+def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
+    """The oracle (a CPU port of the reference's algorithm: the reference has no CPU implementation of latent
+    attention, and its FFN module is fake-quant fp16 GPU code) timed on the host cores on a bounded sample of
+    the same workload: a slice of the batch for attention, the full FFN on its tokens."""
+    from oracle import attention as oattn, ffn as offn, quant
     from lsvd_b200 import synth
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
-    B, H, D, L = w["batch"], w["heads"], w["head_dim"], w["context"]
-    kr = synth.ragged_ranks(H, 64, seed=0) if w["ragged"] else [64] * H
-    vr = synth.ragged_ranks(H, 64, seed=1) if w["ragged"] else [64] * H
+    w = dict(WORKLOADS[workload])
+    if w.get("ffn_only"):
+        w["batch"] = tokens
+    B = w["batch"]
+    has_attn, has_ffn = not w.get("ffn_only", False), w.get("ffn", False)
     bs = min(B, 4)
-    c = synth.attention_inputs(bs, H, D, kr, vr, [L + 1] * bs, seed=0)
-    ko, vo = [0], [0]
-    for a, b in zip(kr, vr):
-        ko.append(ko[-1] + a)
-        vo.append(vo[-1] + b)
-    ck, sk = quant.latent_quant_ragged(c["latent_k"], ko)
-    cv, sv = quant.latent_quant_ragged(c["latent_v"], vo)
+    fns = []
+    if has_attn:
+        H, D, L = w["heads"], w["head_dim"], w["context"]
+        kr = synth.ragged_ranks(H, 64, seed=0) if w["ragged"] else [64] * H
+        vr = synth.ragged_ranks(H, 64, seed=1) if w["ragged"] else [64] * H
+        c = synth.attention_inputs(bs, H, D, kr, vr, [L + 1] * bs, seed=0)
+        ko, vo = [0], [0]
+        for a, b in zip(kr, vr):
+            ko.append(ko[-1] + a)
+            vo.append(vo[-1] + b)
+        ck, sk = quant.latent_quant_ragged(c["latent_k"], ko)
+        cv, sv = quant.latent_quant_ragged(c["latent_v"], vo)
+        fns.append(lambda: oattn.decode_absorb(c["q"], ck, sk, cv, sv, c["up_k"], c["up_v"], ko, vo, c["req_to_token"],
+                                               c["b_req_idx"], c["b_seq_len"], dtype=torch.float32))
+    if has_ffn:
+        fw = synth.ffn_weights(FFN_SHAPE["d_in"], FFN_SHAPE["d_ffn"], FFN_SHAPE["rank"], FFN_SHAPE["n_svd"], seed=0,
+                               had_K=synth.sign_matrix(FFN_SHAPE["K"]).float(), K=FFN_SHAPE["K"])
+        x = torch.randn(bs, FFN_SHAPE["d_in"], generator=torch.Generator().manual_seed(1)).half()
+        fns.append(lambda: offn.hybrid_ffn_stages(x, fw))
 
     def once():
-        return oattn.decode_absorb(c["q"], ck, sk, cv, sv, c["up_k"], c["up_v"], ko, vo, c["req_to_token"],
-                                   c["b_req_idx"], c["b_seq_len"], dtype=torch.float32)
+        for f in fns:
+            f()
     once()
     n, t0 = 0, time.perf_counter()
     while True:
@@ -293,19 +411,20 @@ def cpu_baseline(w, seconds_hint=15.0, threads=None):
         if dt > seconds_hint or n >= 20:
             break
     return {"value": bs * n / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"{bs} of {B} requests of the same workload, {n} steps, fp32 torch on {threads} threads "
-                      f"(attention only; the cache is pre-quantised)"}
+            "sample": f"{bs} of {B} requests/tokens of the same workload, {n} steps, torch on {threads} threads "
+                      f"(int8 products evaluated in float64 for exactness, attention in fp32; the cache is pre-quantised)"}
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return None
     w = WORKLOADS[args.workload]
-    cb = cpu_baseline(w, seconds_hint=max(5.0, 3.0 * args.steps))
+    B = args.tokens if w.get("ffn_only") else w["batch"]
+    cb = cpu_baseline(args.workload, args.tokens, seconds_hint=max(5.0, 3.0 * args.steps))
     return {"impl": "reference", "metric": "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * w["batch"] / cb["value"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
-            "config": {"workload": args.workload, "what": w["desc"]}, "cpu_baseline": cb,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * B / cb["value"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32/fp64 (CPU)", "data": "synthetic",
+            "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B}, "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
@@ -315,7 +434,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_attention", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3_layer", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=8, help="tokens per step of the c2_ffn workload (1..64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank, world, local = dist_env()
@@ -327,7 +447,7 @@ def main():
     line = run_ours(args, rank, world, local)
     if line is not None:
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(WORKLOADS[args.workload])
+            line["cpu_baseline"] = cpu_baseline(args.workload, args.tokens)
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

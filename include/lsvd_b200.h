@@ -196,13 +196,18 @@ typedef struct lsvd_hadamard_quant_args {
   int32_t rows, cols, K;
   const void* x;                 /* device fp16 [rows, cols]                                        */
   int64_t x_row_stride;
-  const void* had_K;             /* device fp16 [K, K] row-major                                    */
+  const void* had_K_packed;      /* device buffer made by lsvd_hadamard_pack from had_K [K, K]      */
   int8_t* q;
   int64_t q_row_stride;
   float* scale;                  /* device fp32 [rows]                                              */
   void* y;                       /* optional device fp16 [rows, cols] (contiguous): the rotated row */
 } lsvd_hadamard_quant_args;
 int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* args, void* stream);
+/* One-time preparation of the K x K factor (device fp16, row-major, the `had_K` buffer of the reference's
+ * modules, fake_quant/utils/hadamard_utils.py:7-69) into the tensor-core fragment order the kernel reads:
+ * lsvd_hadamard_packed_bytes(K) bytes, 16-byte aligned. */
+size_t lsvd_hadamard_packed_bytes(int32_t K);
+int lsvd_hadamard_pack(const void* had_K, int32_t K, void* packed, void* stream);
 
 /* Weight-streaming W8A8 product for 1..64 tokens: acc[m, n] = sum_k a[m, k] * w[n, k] (int32, exact),
  * optionally for a second weight matrix w2 (with its own activations a2, or the same ones) in the same pass.

@@ -71,7 +71,7 @@ class ActQuantArgs(C.Structure):
 class HadamardQuantArgs(C.Structure):
     _fields_ = [
         ("rows", C.c_int32), ("cols", C.c_int32), ("K", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
-        ("had_K", C.c_void_p), ("q", C.c_void_p), ("q_row_stride", C.c_int64), ("scale", C.c_void_p), ("y", C.c_void_p),
+        ("had_K_packed", C.c_void_p), ("q", C.c_void_p), ("q_row_stride", C.c_int64), ("scale", C.c_void_p), ("y", C.c_void_p),
     ]
 
 
@@ -99,6 +99,8 @@ SIGNATURES = {
     "lsvd_attn_decode_static": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_act_quant": (C.c_int, [C.POINTER(ActQuantArgs), C.c_void_p]),
     "lsvd_hadamard_quant": (C.c_int, [C.POINTER(HadamardQuantArgs), C.c_void_p]),
+    "lsvd_hadamard_packed_bytes": (C.c_size_t, [C.c_int32]),
+    "lsvd_hadamard_pack": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),
     "lsvd_attn_decode_plan": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
                                         C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),

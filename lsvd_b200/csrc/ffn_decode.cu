@@ -90,18 +90,25 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ 
 }
 
 // ----------------------------------------------------------------------------------------------
-// (H_K kron H_nb) rotation + per-token quantisation, one block per token
+// (H_K kron H_nb) rotation + per-token quantisation: a thread-block cluster per token
 // ----------------------------------------------------------------------------------------------
+// y[k', j] = sum_k had_K[k', k] * fwht(x[k, :])[j] / sqrt(cols).  The blocks of a cluster split the nb
+// columns j (8 per MMA tile); each block rotates all K power-of-two blocks with warp shuffles (cheap),
+// keeps the columns it owns, multiplies by had_K on the fp16 tensor cores (A fragments come pre-packed in
+// fragment order, so a lane loads 16 bytes per MMA and every had_K element is read once per block), and
+// the row's absmax is exchanged through distributed shared memory between two cluster barriers.
 struct HadQuantParams {
   const __half* x;
   int64_t x_row_stride;
-  const __half* had_K;       // [K, K]
+  const uint4* packed;       // had_K in MMA A-fragment order: [m tile][k tile][lane] x {a0, a1, a2, a3}
   int8_t* q;
   int64_t q_row_stride;
   float* scale;
   __half* y;
   int32_t rows, cols, K, nb; // nb = cols / K, a power of two in [8, 128]
-  int32_t Kp, ld;            // K rounded up to 16, leading dimension (halves) of the staged matrices
+  int32_t Kp, ld;            // K rounded up to 16; leading dimension (halves) of the staged columns
+  int32_t cluster, ntile_per;   // blocks per token, 8-column tiles per block
+  int32_t x_vec16;              // rows of x are 16-byte aligned
   float rot_scale;           // 1 / sqrt(cols)
 };
 
@@ -115,25 +122,68 @@ __device__ __forceinline__ void mma_f16_16x8x16(float (&d)[4], uint32_t a0, uint
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Pack had_K [K, K] (fp16, row-major) into A-fragment order, zero padded to multiples of 16.
+__global__ void hadamard_pack_kernel(const __half* had_K, int K, int Kp, uint4* out) {
+  const int tiles = Kp >> 4;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tiles * tiles * 32) return;
+  const int lane = idx & 31, kt = (idx >> 5) % tiles, mt = (idx >> 5) / tiles;
+  const int g = lane >> 2, t = lane & 3;
+  auto at = [&](int r, int c) -> uint32_t {
+    const __half lo = (r < K && c < K) ? had_K[r * K + c] : __float2half_rn(0.f);
+    const __half hi = (r < K && c + 1 < K) ? had_K[r * K + c + 1] : __float2half_rn(0.f);
+    return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+  };
+  const int r0 = mt * 16 + g, c0 = kt * 16 + 2 * t;
+  out[idx] = make_uint4(at(r0, c0), at(r0 + 8, c0), at(r0, c0 + 8), at(r0 + 8, c0 + 8));
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Read a float from the same shared-memory offset in block `rank` of the cluster.
+__device__ __forceinline__ float cluster_peer_float(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+constexpr int kHadMaxTilesPerWarp = 2;     // m tiles a warp keeps in registers: Kp <= 256 with 8 warps
+constexpr int kHadMaxNtilePer = 2;         // 8-column tiles per block: nb <= 128 with a cluster of 8
+
 __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_constant__ HadQuantParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __half* Hs = reinterpret_cast<__half*>(smem_raw);                 // [Kp][ld]   had_K, zero padded
-  __half* Tt = Hs + p.Kp * p.ld;                                    // [nb][ld]   rotated blocks, transposed
-  __half* Ys = Tt + p.nb * p.ld;                                    // [K][nb]    result
+  __half* Tt = reinterpret_cast<__half*>(smem_raw);          // [ntile_per * 8][ld]: my columns of the rotated blocks
+  __half* xs = Tt + p.ntile_per * 8 * p.ld;                  // [cols]: the token's row, staged with wide loads
   __shared__ float red[8];
-  const int r = blockIdx.x;
+  __shared__ float my_max;
+  const int crank = static_cast<int>(cluster_rank());
+  const int r = blockIdx.x / p.cluster;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int K = p.K, Kp = p.Kp, nb = p.nb, ld = p.ld;
+  const int K = p.K, nb = p.nb, ld = p.ld;
+  const int col0 = crank * p.ntile_per * 8, ncols = p.ntile_per * 8;     // columns [col0, col0 + ncols) are mine
 
-  for (int i = threadIdx.x; i < Kp * ld; i += blockDim.x) {
-    const int a = i / ld, c = i - a * ld;
-    Hs[i] = (a < K && c < K) ? p.had_K[a * K + c] : __float2half_rn(0.f);
+  for (int i = threadIdx.x; i < ncols * ld; i += blockDim.x) Tt[i] = __float2half_rn(0.f);
+  {
+    const __half* xg = p.x + r * p.x_row_stride;
+    if (p.x_vec16) {
+      for (int i = threadIdx.x; i < (p.cols >> 3); i += blockDim.x)
+        reinterpret_cast<uint4*>(xs)[i] = __ldg(reinterpret_cast<const uint4*>(xg) + i);
+    } else {
+      for (int i = threadIdx.x; i < p.cols; i += blockDim.x) xs[i] = xg[i];
+    }
   }
-  for (int i = threadIdx.x; i < nb * ld; i += blockDim.x) Tt[i] = __float2half_rn(0.f);
   __syncthreads();
 
   // ---- power-of-two part: each warp rotates whole blocks of nb entries; a lane holds entries lane + 32 i ----
-  const __half* x = p.x + r * p.x_row_stride;
+  const __half* x = xs;
   const int per = nb >= 32 ? (nb >> 5) : 1;         // 1, 2 or 4 entries per lane (lanes >= nb idle when nb < 32)
   const bool lane_on = lane < nb;
   for (int k = warp; k < K; k += (blockDim.x >> 5)) {
@@ -162,52 +212,90 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
       e[0] = a0 + a2; e[2] = a0 - a2; e[1] = a1 + a3; e[3] = a1 - a3;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-      if (i < per && lane_on) Tt[(i * 32 + lane) * ld + k] = __float2half_rn(e[i] * p.rot_scale);
+    for (int i = 0; i < 4; ++i) {
+      const int j = i * 32 + lane;
+      if (i < per && lane_on && j >= col0 && j < col0 + ncols) Tt[(j - col0) * ld + k] = __float2half_rn(e[i] * p.rot_scale);
+    }
   }
   __syncthreads();
 
-  // ---- had_K part on the tensor cores: Y[k', j] = sum_k Hs[k', k] * Tt[j, k] ----
+  // ---- had_K part on the tensor cores: warp w owns m tiles w, w + 8; results stay in registers ----
   const int g = lane >> 2, t = lane & 3;
-  const int mtiles = Kp >> 4, ntiles = nb >> 3, ktiles = Kp >> 4;
-  for (int tile = warp; tile < mtiles * ntiles; tile += (blockDim.x >> 5)) {
-    const int mt = tile / ntiles, nt = tile - mt * ntiles;
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
-    const __half* arow0 = Hs + (mt * 16 + g) * ld + 2 * t;
-    const __half* arow1 = arow0 + 8 * ld;
-    const __half* brow = Tt + (nt * 8 + g) * ld + 2 * t;
-    for (int kt = 0; kt < ktiles; ++kt) {
-      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(arow0 + kt * 16);
-      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(arow1 + kt * 16);
-      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(arow0 + kt * 16 + 8);
-      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(arow1 + kt * 16 + 8);
-      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + kt * 16);
-      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + kt * 16 + 8);
-      mma_f16_16x8x16(d, a0, a1, a2, a3, b0, b1);
-    }
-    const int row0 = mt * 16 + g, col = nt * 8 + 2 * t;
-    if (row0 < K) {
-      Ys[row0 * nb + col] = __float2half_rn(d[0]);
-      Ys[row0 * nb + col + 1] = __float2half_rn(d[1]);
-    }
-    if (row0 + 8 < K) {
-      Ys[(row0 + 8) * nb + col] = __float2half_rn(d[2]);
-      Ys[(row0 + 8) * nb + col + 1] = __float2half_rn(d[3]);
+  const int tiles = p.Kp >> 4;
+  float d[kHadMaxTilesPerWarp][kHadMaxNtilePer][4];
+  float amax = 0.f;
+#pragma unroll
+  for (int mi = 0; mi < kHadMaxTilesPerWarp; ++mi) {
+    const int mt = warp + mi * 8;
+#pragma unroll
+    for (int ni = 0; ni < kHadMaxNtilePer; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) d[mi][ni][c] = 0.f;
+    if (mt < tiles) {
+      const uint4* ap = p.packed + (static_cast<int64_t>(mt) * tiles) * 32 + lane;
+      for (int kt0 = 0; kt0 < tiles; kt0 += 4) {          // four k tiles of A in flight at a time
+        uint4 a[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = (kt0 + i < tiles) ? __ldg(ap + (kt0 + i) * 32) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kt = kt0 + i;
+          if (kt >= tiles) break;
+#pragma unroll
+          for (int ni = 0; ni < kHadMaxNtilePer; ++ni) {
+            if (ni < p.ntile_per) {
+              const __half* brow = Tt + (ni * 8 + g) * ld + kt * 16 + 2 * t;
+              const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow);
+              const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 8);
+              mma_f16_16x8x16(d[mi][ni], a[i].x, a[i].y, a[i].z, a[i].w, b0, b1);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int ni = 0; ni < kHadMaxNtilePer; ++ni)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          d[mi][ni][c] = __half2float(__float2half_rn(d[mi][ni][c]));        // the reference's fp16 result
+          const int row = mt * 16 + g + 8 * (c >> 1);
+          if (ni < p.ntile_per && row < K) amax = fmaxf(amax, fabsf(d[mi][ni][c]));
+        }
     }
   }
-  __syncthreads();
-
-  // ---- per-token quantisation ----
-  float amax = 0.f;
-  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) amax = fmaxf(amax, fabsf(__half2float(Ys[i])));
   amax = block_max(amax, red);
-  const float s = act_scale_of(amax);
-  if (threadIdx.x == 0) p.scale[r] = s;
+  if (threadIdx.x == 0) my_max = amax;
+  cluster_barrier();
+  float row_max = 0.f;
+  for (int c = 0; c < p.cluster; ++c) row_max = fmaxf(row_max, cluster_peer_float(&my_max, c));
+  cluster_barrier();                        // nobody leaves while a peer may still read its my_max
+  const float s = act_scale_of(row_max);
+  if (crank == 0 && threadIdx.x == 0) p.scale[r] = s;
+
+  // ---- quantise and store my columns ----
   int8_t* q = p.q + r * p.q_row_stride;
-  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
-    const __half hv = Ys[i];
-    q[i] = act_code(__half2float(hv), s);
-    if (p.y != nullptr) p.y[static_cast<int64_t>(r) * p.cols + i] = hv;
+#pragma unroll
+  for (int mi = 0; mi < kHadMaxTilesPerWarp; ++mi) {
+    const int mt = warp + mi * 8;
+    if (mt >= tiles) continue;
+#pragma unroll
+    for (int ni = 0; ni < kHadMaxNtilePer; ++ni) {
+      if (ni >= p.ntile_per) continue;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int row = mt * 16 + g + 8 * hf;
+        if (row >= K) continue;
+        const int col = col0 + ni * 8 + 2 * t;
+        const float v0 = d[mi][ni][2 * hf], v1 = d[mi][ni][2 * hf + 1];
+        const int64_t o = static_cast<int64_t>(row) * nb + col;
+        const uint16_t packed = static_cast<uint16_t>(static_cast<uint8_t>(act_code(v0, s))) |
+                                (static_cast<uint16_t>(static_cast<uint8_t>(act_code(v1, s))) << 8);
+        *reinterpret_cast<uint16_t*>(q + o) = packed;
+        if (p.y != nullptr) {
+          __half* yo = p.y + static_cast<int64_t>(r) * p.cols + o;
+          *reinterpret_cast<__half2*>(yo) = __floats2half2_rn(v0, v1);
+        }
+      }
+    }
   }
 }
 
@@ -263,6 +351,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
   const int8_t* w2r0 = DUAL ? p.w2 + (row0 + g) * p.w2_row_stride + 16 * t : nullptr;
   const int8_t* w2r1 = DUAL ? w2r0 + 8 * p.w2_row_stride : nullptr;
 
+  constexpr int kUnroll = NT <= 2 ? 4 : (NT == 4 ? 2 : 1);     // spans whose loads are issued together
+#pragma unroll kUnroll
   for (int s = s_begin; s < s_end; ++s) {
     const int ko = s * 64;
     const uint4 x0 = ldg_u4(wr0 + ko), x1 = ldg_u4(wr1 + ko);
@@ -381,18 +471,36 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   return LSVD_OK;
 }
 
+extern "C" size_t lsvd_hadamard_packed_bytes(int32_t K) {
+  if (K <= 1 || K > 256) return 0;
+  const size_t tiles = (static_cast<size_t>(K) + 15) / 16;
+  return tiles * tiles * 32 * 16;
+}
+
+extern "C" int lsvd_hadamard_pack(const void* had_K, int32_t K, void* packed, void* stream) {
+  using namespace lsvd;
+  if (had_K == nullptr || packed == nullptr || K <= 1 || K > 256 || !aligned(packed, 16)) return LSVD_ERR_INVALID_ARG;
+  const int Kp = (K + 15) / 16 * 16;
+  const int n = (Kp / 16) * (Kp / 16) * 32;
+  hadamard_pack_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(had_K), K, Kp, static_cast<uint4*>(packed));
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}
+
 extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stream) {
   using namespace lsvd;
   if (a == nullptr || a->rows < 0 || a->cols <= 0 || a->K <= 1 || a->K > 256) return LSVD_ERR_INVALID_ARG;
   if (a->rows == 0) return LSVD_OK;
-  if (!a->x || !a->had_K || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
+  if (!a->x || !a->had_K_packed || !a->q || !a->scale || !aligned(a->had_K_packed, 16)) return LSVD_ERR_INVALID_ARG;
   if (a->cols % a->K) return LSVD_ERR_INVALID_ARG;
   const int nb = a->cols / a->K;
   if (!is_pow2(nb) || nb < 8 || nb > 128) return LSVD_ERR_UNSUPPORTED;
+  if ((a->q_row_stride % 2) || !aligned(a->q, 2) || (a->y && !aligned(a->y, 4))) return LSVD_ERR_INVALID_ARG;
   HadQuantParams p{};
   p.x = static_cast<const __half*>(a->x);
   p.x_row_stride = a->x_row_stride;
-  p.had_K = static_cast<const __half*>(a->had_K);
+  p.packed = static_cast<const uint4*>(a->had_K_packed);
   p.q = a->q;
   p.q_row_stride = a->q_row_stride;
   p.scale = a->scale;
@@ -403,12 +511,26 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
   p.nb = nb;
   p.Kp = (a->K + 15) / 16 * 16;
   p.ld = p.Kp + 8;
+  const int ntiles = nb / 8;
+  p.cluster = ntiles < 8 ? ntiles : 8;
+  p.ntile_per = ntiles / p.cluster;
   p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
-  const int smem = (p.Kp * p.ld + nb * p.ld + a->K * nb) * 2;
-  if (smem > device_max_smem_optin()) return LSVD_ERR_UNSUPPORTED;
+  const int smem = (p.ntile_per * 8 * p.ld + a->cols) * 2;
+  p.x_vec16 = (aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && (a->cols % 8) == 0) ? 1 : 0;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(hadamard_quant_kernel), smem));
-  hadamard_quant_kernel<<<a->rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
-  LSVD_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(a->rows * p.cluster));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  LSVD_CUDA_TRY(cudaLaunchKernelEx(&cfg, hadamard_quant_kernel, p));
   return LSVD_OK;
 }
 

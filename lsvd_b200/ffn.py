@@ -76,11 +76,23 @@ def act_quant(x: torch.Tensor, sign: Optional[torch.Tensor] = None, fwht: bool =
     return q, scale, rot
 
 
-def hadamard_quant(x: torch.Tensor, had_K: torch.Tensor, K: int, want_rotated: bool = False):
-    """(H_K kron H_{cols/K}) rotation of fp16 rows followed by per-token int8 quantisation."""
-    _require_cuda(x, had_K)
-    if x.dtype != torch.float16 or had_K.dtype != torch.float16 or not had_K.is_contiguous():
-        raise ValueError("x and had_K must be fp16 (had_K contiguous)")
+def hadamard_pack(had_K: torch.Tensor) -> torch.Tensor:
+    """One-time conversion of the K x K Hadamard factor into the layout ``hadamard_quant`` reads."""
+    _require_cuda(had_K)
+    had_K = had_K.to(torch.float16).contiguous()
+    K = had_K.shape[0]
+    lib = _lib.load()
+    packed = torch.empty(int(lib.lsvd_hadamard_packed_bytes(K)), dtype=torch.uint8, device=had_K.device)
+    _lib.check(lib.lsvd_hadamard_pack(had_K.data_ptr(), K, packed.data_ptr(), _stream_ptr(had_K)))
+    return packed
+
+
+def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rotated: bool = False):
+    """(H_K kron H_{cols/K}) rotation of fp16 rows followed by per-token int8 quantisation.
+    ``had_K_packed`` comes from ``hadamard_pack(had_K)``."""
+    _require_cuda(x, had_K_packed)
+    if x.dtype != torch.float16 or had_K_packed.dtype != torch.uint8:
+        raise ValueError("x must be fp16 and had_K_packed the buffer made by hadamard_pack")
     rows, cols = x.shape
     q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
     scale = torch.empty(rows, dtype=torch.float32, device=x.device)
@@ -88,7 +100,7 @@ def hadamard_quant(x: torch.Tensor, had_K: torch.Tensor, K: int, want_rotated: b
     a = _lib.HadamardQuantArgs()
     a.rows, a.cols, a.K = rows, cols, K
     a.x, a.x_row_stride = x.data_ptr(), x.stride(0)
-    a.had_K = had_K.data_ptr()
+    a.had_K_packed = had_K_packed.data_ptr()
     a.q, a.q_row_stride = q.data_ptr(), q.stride(0)
     a.scale = scale.data_ptr()
     a.y = _ptr(y)
@@ -149,6 +161,9 @@ class HybridFFN(nn.Module):
         self.register_buffer("had_sign", None if hs is None else hs.to(torch.float16).contiguous())
         hk = weights.get("had_K")
         self.register_buffer("had_K", None if hk is None else hk.to(torch.float16).contiguous())
+        self.register_buffer("had_K_packed", None if (hk is None or self.K == 1 or not hk.is_cuda)
+                             else hadamard_pack(self.had_K))
+        self._plans = {}
         self.rank = self.U_q.shape[0] // 2
         self.n_svd = self.Vg_q.shape[0]
         self.n_q = self.Wg_q.shape[0]
@@ -195,12 +210,93 @@ class HybridFFN(nn.Module):
         elif self.K == 1:
             h_q, h_s, h_rot = act_quant(h16, fwht=True, want_rotated=True)
         else:
-            h_q, h_s, h_rot = hadamard_quant(h16, self.had_K, self.K, want_rotated=True)
+            if self.had_K_packed is None:
+                self.had_K_packed = hadamard_pack(self.had_K)
+            h_q, h_s, h_rot = hadamard_quant(h16, self.had_K_packed, self.K, want_rotated=True)
         st.update(h_q=h_q, h_s=h_s, h_rot=h_rot)
         out, out_acc, _ = w8a8_gemv(h_q, h_s, self.Wd_q, self.Wd_s, want_acc=want_acc)
         st.update(out_acc=out_acc, out=out.view(*shape[:-1], self.d_out))
         return st
 
+    # ---- the decode path proper: preallocated buffers and argument blocks per batch size, seven launches ----
+    def _plan(self, m: int, device):
+        key = (m, str(device))
+        plan = self._plans.get(key)
+        if plan is not None:
+            return plan
+        r, dev = self.rank, device
+        b = {
+            "x_q": torch.empty(m, self.d_in, dtype=torch.int8, device=dev), "x_s": torch.empty(m, dtype=torch.float32, device=dev),
+            "lat16": torch.empty(m, 2 * r, dtype=torch.float16, device=dev),
+            "z_q": torch.empty(m, 2 * r, dtype=torch.int8, device=dev), "z_s": torch.empty(m, 2, dtype=torch.float32, device=dev),
+            "h16": torch.empty(m, self.d_ffn, dtype=torch.float16, device=dev),
+            "h_q": torch.empty(m, self.d_ffn, dtype=torch.int8, device=dev), "h_s": torch.empty(m, dtype=torch.float32, device=dev),
+        }
+        calls = []
+        lib = _lib.load()
+
+        def actq(x_ptr, x_stride, rows, cols, sign, fwht, q, scale):
+            a = _lib.ActQuantArgs()
+            a.rows, a.cols, a.x, a.x_row_stride = rows, cols, x_ptr, x_stride
+            a.sign, a.fwht = _ptr(sign), 1 if fwht else 0
+            a.q, a.q_row_stride, a.scale = q.data_ptr(), cols if q.dim() == 1 else q.stride(0), scale.data_ptr()
+            return (lib.lsvd_act_quant, a)
+
+        def gemv(a_q, a_stride, a_s, a_s_stride, k, w, ws, out, out_stride, out_col=0, w2=None, w2s=None,
+                 a2=None, a2_s=None):
+            g = _lib.GemvArgs()
+            g.m, g.n, g.k = m, w.shape[0], k
+            g.w, g.w_row_stride, g.w_scale = w.data_ptr(), w.stride(0), ws.data_ptr()
+            if w2 is not None:
+                g.w2, g.w2_row_stride, g.w2_scale, g.epilogue = w2.data_ptr(), w2.stride(0), w2s.data_ptr(), 1
+            g.a, g.a_row_stride, g.a_scale, g.a_scale_stride = a_q, a_stride, a_s, a_s_stride
+            if a2 is not None:
+                g.a2, g.a2_row_stride, g.a2_scale, g.a2_scale_stride = a2, a_stride, a2_s, a_s_stride
+            g.out, g.out_row_stride, g.out_col = out, out_stride, out_col
+            return (lib.lsvd_w8a8_gemv, g)
+
+        calls.append(actq(0, self.d_in, m, self.d_in, self.had_sign, False, b["x_q"], b["x_s"]))            # [0]: x set per call
+        calls.append(gemv(b["x_q"].data_ptr(), self.d_in, b["x_s"].data_ptr(), 1, self.d_in, self.U_q, self.U_s,
+                          b["lat16"].data_ptr(), 2 * r))
+        calls.append(actq(b["lat16"].data_ptr(), r, 2 * m, r, None, False, b["z_q"].view(-1, r), b["z_s"].view(-1)))
+        zq, zs = b["z_q"].data_ptr(), b["z_s"].data_ptr()
+        calls.append(gemv(zq, 2 * r, zs, 2, r, self.Vg_q, self.Vg_s, b["h16"].data_ptr(), self.d_ffn, 0, self.Vu_q, self.Vu_s,
+                          a2=zq + r, a2_s=zs + 4))
+        calls.append(gemv(b["x_q"].data_ptr(), self.d_in, b["x_s"].data_ptr(), 1, self.d_in, self.Wg_q, self.Wg_s,
+                          b["h16"].data_ptr(), self.d_ffn, self.n_svd, self.Wu_q, self.Wu_s))
+        if self.online_had and self.K > 1:
+            if self.had_K_packed is None:
+                self.had_K_packed = hadamard_pack(self.had_K)
+            h = _lib.HadamardQuantArgs()
+            h.rows, h.cols, h.K = m, self.d_ffn, self.K
+            h.x, h.x_row_stride, h.had_K_packed = b["h16"].data_ptr(), self.d_ffn, self.had_K_packed.data_ptr()
+            h.q, h.q_row_stride, h.scale = b["h_q"].data_ptr(), self.d_ffn, b["h_s"].data_ptr()
+            calls.append((lib.lsvd_hadamard_quant, h))
+        else:
+            calls.append(actq(b["h16"].data_ptr(), self.d_ffn, m, self.d_ffn, None, self.online_had, b["h_q"], b["h_s"]))
+        calls.append(gemv(b["h_q"].data_ptr(), self.d_ffn, b["h_s"].data_ptr(), 1, self.d_ffn, self.Wd_q, self.Wd_s, 0, self.d_out))
+        plan = (b, calls)
+        self._plans[key] = plan
+        return plan
+
     @torch.no_grad()
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.forward_stages(x)["out"]
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [..., d_in] fp16 (at most 64 tokens) -> [..., d_out] fp16.  Intermediate buffers are kept per batch size,
+        so apart from the result (unless ``out`` is passed) a call allocates nothing and can be captured in a CUDA graph."""
+        _require_cuda(x)
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        m = x2.shape[0]
+        if m > 64 or m < 1:
+            raise ValueError("the decode FFN takes 1..64 tokens per call")
+        if x2.dtype != torch.float16 or x2.stride(1) != 1 or shape[-1] != self.d_in:
+            raise ValueError("x must be fp16 [..., d_in] with unit inner stride")
+        if out is None:
+            out = torch.empty(m, self.d_out, dtype=torch.float16, device=x.device)
+        _, calls = self._plan(m, x.device)
+        calls[0][1].x, calls[0][1].x_row_stride = x2.data_ptr(), x2.stride(0)
+        calls[-1][1].out = out.data_ptr()
+        stream = _stream_ptr(x)
+        for fn, args in calls:
+            _lib.check(fn(C.byref(args), stream))
+        return out.view(*shape[:-1], self.d_out)

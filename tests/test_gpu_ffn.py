@@ -10,7 +10,7 @@ import torch
 from conftest import load_golden, unpack_had, rel_to_norm
 from oracle import ffn as offn, quant
 from lsvd_b200 import synth
-from lsvd_b200.ffn import HybridFFN, act_quant, hadamard_quant, w8a8_gemv, quantize_weight_rtn
+from lsvd_b200.ffn import HybridFFN, act_quant, hadamard_quant, hadamard_pack, w8a8_gemv, quantize_weight_rtn
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-3
@@ -64,7 +64,7 @@ def test_hadamard_quant_against_oracle(K, nb):
     hk = unpack_had(g[f"had{K}_bits"], K)
     gen = torch.Generator().manual_seed(K + nb)
     x = torch.randn(4, K * nb, generator=gen).half()
-    q, s, y = hadamard_quant(x.cuda(), hk.half().cuda(), K, want_rotated=True)
+    q, s, y = hadamard_quant(x.cuda(), hadamard_pack(hk.half().cuda()), K, want_rotated=True)
     y_ref = offn.hadamard_full(x, hk, K)
     d = (y.cpu().float() - y_ref.float()).abs()
     assert d.max() <= 2 ** -10 * y_ref.float().abs().max()          # at most one fp16 ulp of the largest entry
@@ -81,7 +81,7 @@ def test_hadamard_quant_reference_fixture():
     # (H_172 kron H_8) on [x, 0] interleaved is not the same transform; use the 1376-wide FFN fixture instead
     f = load_golden("hybrid_ffn")
     st = offn.hybrid_ffn_stages(f["x"], _golden_weights(f))
-    q, s, y = hadamard_quant(st["h16"].cuda(), hk.half().cuda(), 172, want_rotated=True)
+    q, s, y = hadamard_quant(st["h16"].cuda(), hadamard_pack(hk.half().cuda()), 172, want_rotated=True)
     assert rel_to_norm(y.cpu().float(), f["h"].float()) < 2e-3      # the reference module's rotated hidden vector
     assert x.shape[1] == 688
 
@@ -169,6 +169,8 @@ def test_config2_chain_stage_by_stage(m):
     acc_ref = offn._i32_matmul(st["h_q"], w["Wd_q"])
     assert torch.equal(st["out_acc"], acc_ref)
     assert torch.equal(st["out"], offn._dequant16(acc_ref, st["h_s"], w["Wd_s"]))
+    # the allocation-free decode path runs the same kernels
+    assert torch.equal(ffn(x.cuda()).cpu(), st["out"])
     # end to end
     err = rel_to_norm(st["out"].float(), ref["out"].float())
     assert err < TOL, err
