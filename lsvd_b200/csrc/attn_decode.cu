@@ -83,6 +83,7 @@ struct AbsorbParams {
   int32_t* queue;          // work counter of the stream kernel that follows: reset here
   float score_scale;       // sm_scale * log2(e)
   int32_t num_heads, head_dim, sum_rk;
+  int32_t up_k_vec16;      // rows of up_k are 16-byte aligned
   int32_t k_off[LSVD_MAX_HEADS + 1];
 };
 
@@ -97,12 +98,35 @@ __global__ void __launch_bounds__(128) absorb_query_kernel(const __grid_constant
   const __half* qp = p.q + b * p.q_stride_b + h * p.q_stride_h;
   for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) qs[d] = __half2float(qp[d]);
   __syncthreads();
-  for (int i = warp; i < r; i += 4) {
-    const __half* row = p.up_k + static_cast<int64_t>(r0 + i) * p.up_k_row_stride;
+  // one thread per latent entry: its up-factor row is head_dim contiguous fp16 values, read with 16-byte
+  // loads that are all in flight together
+  if (threadIdx.x < r) {
+    const __half* row = p.up_k + static_cast<int64_t>(r0 + threadIdx.x) * p.up_k_row_stride;
     float acc = 0.f;
-    for (int d = lane; d < p.head_dim; d += 32) acc = fmaf(__half2float(row[d]), qs[d], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) qt[i] = acc;
+    if (p.up_k_vec16) {
+      const uint4* rv = reinterpret_cast<const uint4*>(row);
+      for (int c0 = 0; c0 < (p.head_dim >> 3); c0 += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = (c0 + c < (p.head_dim >> 3)) ? __ldg(rv + c0 + c) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          if (c0 + c < (p.head_dim >> 3)) {
+            const __half2* h2 = reinterpret_cast<const __half2*>(&v[c]);
+            const float* qv = qs + (c0 + c) * 8;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __half22float2(h2[e]);
+              acc = fmaf(f.x, qv[2 * e], acc);
+              acc = fmaf(f.y, qv[2 * e + 1], acc);
+            }
+          }
+        }
+      }
+    } else {
+      for (int d = 0; d < p.head_dim; ++d) acc = fmaf(__half2float(row[d]), qs[d], acc);
+    }
+    qt[threadIdx.x] = acc;
   }
   __syncthreads();
   float a = (threadIdx.x < r) ? fabsf(qt[threadIdx.x]) : 0.f;
@@ -151,6 +175,14 @@ __device__ __forceinline__ void mma_s8_16x8x32_zero(int (&d)[4], uint32_t a0, ui
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// A signed (latents), B unsigned (softmax weights), zero accumulator on input.
+__device__ __forceinline__ void mma_s8u8_16x8x32_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                      uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 __device__ __forceinline__ uint4 ldg128(const int8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint2 ldg64(const int8_t* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
 
@@ -174,8 +206,8 @@ __device__ __forceinline__ void transpose4x4_bytes(uint32_t x0, uint32_t x1, uin
 //   values   A = V latents transposed, rows = ranks, k = the 32 tokens; lane (g, t) loads the 8 bytes at ranks
 //            8g..8g+7 of a 64-rank group for tokens 8t..8t+7 and transposes 4 x 4 byte blocks in registers, which
 //            feeds four MMAs (row g <-> rank 8g+r, row g+8 <-> rank 8g+4+r); B = the softmax weights
-//            p * scale_v of the 32 tokens, quantised per step to three int8 limbs against the step's largest
-//            weight (21 bits), columns 0..2.  The int32 results are scaled back and added to fp32 accumulators.
+//            p * scale_v of the 32 tokens, quantised per step to two unsigned base-256 limbs against the step's
+//            largest weight (16 bits), columns 0..1.  The int32 results are scaled back into fp32 accumulators.
 __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPlan& H, int b, int h, int rem, int k,
                                             int len, int t0, int t1, uint4* scratch, uint8_t* wlimb, int lane) {
   const int nk = H.nk, nv = H.nv;
@@ -298,24 +330,19 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     const float pr = exp2f(s - mx);
     l = fmaf(l, corr, pr);
     const float w = valid ? pr * vs : 0.f;
-    // ---- weights of the 32 tokens as three int8 limbs against the step's largest weight ----
+    // ---- weights of the 32 tokens as two unsigned base-256 limbs against the step's largest weight (16 bits) ----
     const float wmax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(w)));   // w >= 0
-    const float winv = wmax > 0.f ? static_cast<float>(kLimbMax) / wmax : 0.f;
-    const float wsc = wmax * (1.0f / static_cast<float>(kLimbMax));
+    const float winv = wmax > 0.f ? 65535.f / wmax : 0.f;
+    const float wsc = wmax * (1.0f / 65535.f);
     {
-      const int Q = min(kLimbMax, __float2int_rn(w * winv));
-      int c0 = Q & 127; if (c0 >= 64) c0 -= 128;
-      const int Q1 = (Q - c0) >> 7;
-      int c1 = Q1 & 127; if (c1 >= 64) c1 -= 128;
-      const int c2 = (Q1 - c1) >> 7;
+      const uint32_t Q = static_cast<uint32_t>(min(65535, __float2int_rn(w * winv)));
       __syncwarp();
-      wlimb[lane] = static_cast<uint8_t>(c0);
-      wlimb[32 + lane] = static_cast<uint8_t>(c1);
-      wlimb[64 + lane] = static_cast<uint8_t>(c2);
+      wlimb[lane] = static_cast<uint8_t>(Q & 255u);
+      wlimb[32 + lane] = static_cast<uint8_t>(Q >> 8);
       __syncwarp();
     }
     uint32_t wb0 = 0u, wb1 = 0u;     // B operand: k 4t..4t+3 <-> tokens 8t..8t+3, k 16+4t.. <-> tokens 8t+4..8t+7
-    if (g < 3) {
+    if (g < 2) {                     // column 0: low limb, column 1: high limb; both land in lane t = 0 of a quad
       const uint32_t* wl = reinterpret_cast<const uint32_t*>(wlimb + g * 32 + t4 * 8);
       wb0 = wl[0];
       wb1 = wl[1];
@@ -339,15 +366,9 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           int d[4];
-          mma_s8_16x8x32_zero(d, x0[r], y0[r], x1[r], y1[r], wb0, wb1);
-          float lo, hi;
-          if (t4 == 0) {
-            lo = fmaf(128.f, static_cast<float>(d[1]), static_cast<float>(d[0]));
-            hi = fmaf(128.f, static_cast<float>(d[3]), static_cast<float>(d[2]));
-          } else {
-            lo = 16384.f * static_cast<float>(d[0]);     // lanes t = 2, 3 hold zero columns
-            hi = 16384.f * static_cast<float>(d[2]);
-          }
+          mma_s8u8_16x8x32_zero(d, x0[r], y0[r], x1[r], y1[r], wb0, wb1);
+          // lane t = 0 holds both limb columns; the other lanes of the quad compute on zero columns
+          const float lo = static_cast<float>(d[0] + d[1] * 256), hi = static_cast<float>(d[2] + d[3] * 256);
           acc[gi][r][0] = fmaf(acc[gi][r][0], corr, wsc * lo);
           acc[gi][r][1] = fmaf(acc[gi][r][1], corr, wsc * hi);
         }
@@ -369,9 +390,8 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     float v[8];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      // limbs 0, 1 were summed in lane t = 0 and limb 2 in lane t = 1
-      v[r] = acc[gi][r][0] + __shfl_xor_sync(0xffffffffu, acc[gi][r][0], 1);
-      v[4 + r] = acc[gi][r][1] + __shfl_xor_sync(0xffffffffu, acc[gi][r][1], 1);
+      v[r] = acc[gi][r][0];            // complete in lane t = 0 of each quad
+      v[4 + r] = acc[gi][r][1];
     }
     if (t4 == 0 && gi * 64 + g * 8 < nv * 16) {
       float4* dst = reinterpret_cast<float4*>(pa + gi * 64 + g * 8);     // ranks 8g .. 8g+7 of the group
@@ -422,6 +442,7 @@ struct MergeParams {
   __half* out_latent;
   int64_t out_latent_stride_b;
   int32_t batch, num_heads, head_dim, items_per_request, acc_per_request;
+  int32_t up_v_vec16;        // rows of up_v are 16-byte aligned: stage the head's block in shared memory
   int32_t v_off[LSVD_MAX_HEADS + 1];
   int32_t part_off[LSVD_MAX_HEADS];
   int32_t acc_off[LSVD_MAX_HEADS];
@@ -429,34 +450,80 @@ struct MergeParams {
   int16_t parts[LSVD_MAX_HEADS];
 };
 
+constexpr int kMergeMaxParts = 512;     // part weights kept in shared memory; further parts are recomputed
+
 __global__ void __launch_bounds__(128) merge_up_kernel(const __grid_constant__ MergeParams p) {
+  extern __shared__ __align__(16) uint8_t merge_smem[];      // [rv][head_dim] fp16: this head's V up-factor
+  __half* upv_s = reinterpret_cast<__half*>(merge_smem);
   __shared__ float olat[LSVD_MAX_RANK];
   const int h = blockIdx.x, b = blockIdx.y;
-  const int v0 = p.v_off[h], rv = p.v_off[h + 1] - v0;
+  const int v0_col = p.v_off[h], rv = p.v_off[h + 1] - v0_col;
+  // The up-factor does not depend on the partial results: fetch it first, with wide loads, so that its
+  // latency overlaps the merge.
+  if (p.out != nullptr && p.up_v_vec16) {
+    const int per_row = p.head_dim >> 3;
+    for (int i = threadIdx.x; i < rv * per_row; i += blockDim.x) {
+      const int r = i / per_row, c = i - r * per_row;
+      reinterpret_cast<uint4*>(upv_s)[i] =
+          __ldg(reinterpret_cast<const uint4*>(p.up_v + static_cast<int64_t>(v0_col + r) * p.up_v_row_stride) + c);
+    }
+  }
   // Items of (b, h) that held tokens: the same arithmetic as the stream kernel.
   const int ntiles = tiles_of(p.b_seq_len[b]);
   int nparts = (ntiles + p.chunk_tiles[h] - 1) / p.chunk_tiles[h];
   if (nparts > p.parts[h]) nparts = p.parts[h];
   const float* ml = p.part_ml + (static_cast<int64_t>(b) * p.items_per_request + p.part_off[h]) * 2;
+  // weights of the parts: w_k = 2^(m_k - M) / sum_k l_k 2^(m_k - M), computed once by the block
+  __shared__ float wpart[kMergeMaxParts];
+  __shared__ float red_a[4], red_b[4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float M = -INFINITY;
-  for (int k = 0; k < nparts; ++k) M = fmaxf(M, ml[k * 2]);
+  for (int k = threadIdx.x; k < nparts; k += blockDim.x) M = fmaxf(M, ml[k * 2]);
+  M = warp_max(M);
+  if (lane == 0) red_a[warp] = M;
+  __syncthreads();
+  M = fmaxf(fmaxf(red_a[0], red_a[1]), fmaxf(red_a[2], red_a[3]));
   float denom = 0.f;
-  for (int k = 0; k < nparts; ++k) denom += ml[k * 2 + 1] * exp2f(ml[k * 2] - M);
+  for (int k = threadIdx.x; k < nparts; k += blockDim.x) {
+    const float e = exp2f(ml[k * 2] - M);
+    if (k < kMergeMaxParts) wpart[k] = e;
+    denom += ml[k * 2 + 1] * e;
+  }
+  denom = warp_sum(denom);
+  if (lane == 0) red_b[warp] = denom;
+  __syncthreads();
+  denom = red_b[0] + red_b[1] + red_b[2] + red_b[3];
   const int i = threadIdx.x;
   if (i < rv) {
     float num = 0.f;
     const float* pa = p.part_acc + static_cast<int64_t>(b) * p.acc_per_request + p.acc_off[h] + i;
-    for (int k = 0; k < nparts; ++k) num += pa[static_cast<int64_t>(k) * rv] * exp2f(ml[k * 2] - M);
+    const int fast = min(nparts, kMergeMaxParts);
+    int k = 0;
+    for (; k + 8 <= fast; k += 8) {           // eight loads in flight
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = pa[static_cast<int64_t>(k + u) * rv];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) num = fmaf(v[u], wpart[k + u], num);
+    }
+    for (; k < fast; ++k) num = fmaf(pa[static_cast<int64_t>(k) * rv], wpart[k], num);
+    for (; k < nparts; ++k) num = fmaf(pa[static_cast<int64_t>(k) * rv], exp2f(ml[k * 2] - M), num);
     const float o = nparts > 0 ? num / denom : 0.f;
     olat[i] = o;
-    if (p.out_latent != nullptr) p.out_latent[b * p.out_latent_stride_b + v0 + i] = __float2half_rn(o);
+    if (p.out_latent != nullptr) p.out_latent[b * p.out_latent_stride_b + v0_col + i] = __float2half_rn(o);
   }
   __syncthreads();
   if (p.out != nullptr) {
     for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) {
       float acc = 0.f;
-      const __half* col = p.up_v + static_cast<int64_t>(v0) * p.up_v_row_stride + d;
-      for (int r = 0; r < rv; ++r) acc = fmaf(olat[r], __half2float(col[static_cast<int64_t>(r) * p.up_v_row_stride]), acc);
+      if (p.up_v_vec16) {
+#pragma unroll 8
+        for (int r = 0; r < rv; ++r) acc = fmaf(olat[r], __half2float(upv_s[r * p.head_dim + d]), acc);
+      } else {
+        const __half* col = p.up_v + static_cast<int64_t>(v0_col) * p.up_v_row_stride + d;
+#pragma unroll 8
+        for (int r = 0; r < rv; ++r) acc = fmaf(olat[r], __half2float(col[static_cast<int64_t>(r) * p.up_v_row_stride]), acc);
+      }
       p.out[b * p.out_stride_b + h * p.out_stride_h + d] = __float2half_rn(acc);
     }
   }
@@ -613,6 +680,7 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
   ap.num_heads = a->num_heads;
   ap.head_dim = a->head_dim;
   ap.sum_rk = sum_rk;
+  ap.up_k_vec16 = (aligned(a->up_k, 16) && (a->up_k_row_stride % 8) == 0) ? 1 : 0;
   std::memcpy(ap.k_off, a->k_off, sizeof(int32_t) * (a->num_heads + 1));
   absorb_query_kernel<<<dim3(a->num_heads, a->batch), 128, 0, st>>>(ap);
   LSVD_CUDA_TRY(cudaGetLastError());
@@ -674,7 +742,12 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
     mp.chunk_tiles[h] = hp.head[h].chunk_tiles;
     mp.parts[h] = hp.head[h].parts;
   }
-  merge_up_kernel<<<dim3(a->num_heads, a->batch), 128, 0, st>>>(mp);
+  mp.up_v_vec16 = (a->up_v != nullptr && aligned(a->up_v, 16) && (a->up_v_row_stride % 8) == 0 && (a->head_dim % 8) == 0) ? 1 : 0;
+  int max_rv = 0;
+  for (int h = 0; h < a->num_heads; ++h) max_rv = std::max(max_rv, a->v_off[h + 1] - a->v_off[h]);
+  const int merge_smem = (a->out != nullptr && mp.up_v_vec16) ? max_rv * a->head_dim * 2 : 0;
+  if (merge_smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(merge_up_kernel), merge_smem));
+  merge_up_kernel<<<dim3(a->num_heads, a->batch), 128, merge_smem, st>>>(mp);
   LSVD_CUDA_TRY(cudaGetLastError());
   return LSVD_OK;
 }

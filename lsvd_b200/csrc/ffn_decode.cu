@@ -28,6 +28,7 @@ struct ActQuantParams {
   float* scale;
   __half* x_rot;
   int32_t rows, cols, rotate;
+  int32_t vec8;              // rows of x, sign and q allow 16 / 8-byte accesses
   float rot_scale;           // 1 / sqrt(cols)
 };
 
@@ -55,18 +56,54 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ 
   __shared__ float red[8];
   const int r = blockIdx.x;
   const __half* x = p.x + r * p.x_row_stride;
-  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
-    float v = __half2float(x[i]);
-    if (p.sign != nullptr) v *= __half2float(p.sign[i]);
-    row[i] = v;
+  if (p.vec8) {
+    // 16-byte loads, all of a thread's chunks in flight before the first use
+    const int chunks = p.cols >> 3;
+    for (int c0 = threadIdx.x; c0 < chunks; c0 += 4 * blockDim.x) {
+      uint4 xv[4], sv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < chunks) {
+          xv[u] = __ldg(reinterpret_cast<const uint4*>(x) + c);
+          if (p.sign != nullptr) sv[u] = __ldg(reinterpret_cast<const uint4*>(p.sign) + c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < chunks) {
+          const __half2* xh = reinterpret_cast<const __half2*>(&xv[u]);
+          const __half2* sh = reinterpret_cast<const __half2*>(&sv[u]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = __half22float2(xh[e]);
+            if (p.sign != nullptr) {
+              const float2 g2 = __half22float2(sh[e]);
+              f.x *= g2.x;
+              f.y *= g2.y;
+            }
+            row[c * 8 + 2 * e] = f.x;
+            row[c * 8 + 2 * e + 1] = f.y;
+          }
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+      float v = __half2float(x[i]);
+      if (p.sign != nullptr) v *= __half2float(p.sign[i]);
+      row[i] = v;
+    }
   }
   __syncthreads();
   if (p.rotate) {
     // Sylvester butterflies in fp32, stride 1 first: the same additions in the same order as the
     // reference's butterfly loop, so the rotated row is bit-identical.
-    for (int h = 1; h < p.cols; h <<= 1) {
+    int lg = 0;
+    for (int h = 1; h < p.cols; h <<= 1, ++lg) {
       for (int i = threadIdx.x; i < (p.cols >> 1); i += blockDim.x) {
-        const int j = ((i / h) * 2 * h) + (i % h);
+        const int j = ((i >> lg) << (lg + 1)) + (i & (h - 1));
         const float a = row[j], b = row[j + h];
         row[j] = a + b;
         row[j + h] = a - b;
@@ -86,7 +123,19 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ 
   const float s = act_scale_of(amax);
   if (threadIdx.x == 0) p.scale[r] = s;
   int8_t* q = p.q + r * p.q_row_stride;
-  for (int i = threadIdx.x; i < p.cols; i += blockDim.x) q[i] = act_code(row[i], s);
+  if (p.vec8) {
+    for (int c = threadIdx.x; c < (p.cols >> 3); c += blockDim.x) {
+      uint32_t lo = 0u, hi = 0u;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        lo |= static_cast<uint32_t>(static_cast<uint8_t>(act_code(row[c * 8 + e], s))) << (8 * e);
+        hi |= static_cast<uint32_t>(static_cast<uint8_t>(act_code(row[c * 8 + 4 + e], s))) << (8 * e);
+      }
+      *reinterpret_cast<uint2*>(q + c * 8) = make_uint2(lo, hi);
+    }
+  } else {
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) q[i] = act_code(row[i], s);
+  }
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -174,19 +223,26 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
   {
     const __half* xg = p.x + r * p.x_row_stride;
     if (p.x_vec16) {
-      for (int i = threadIdx.x; i < (p.cols >> 3); i += blockDim.x)
-        reinterpret_cast<uint4*>(xs)[i] = __ldg(reinterpret_cast<const uint4*>(xg) + i);
+      // only the blocks this cluster member rotates: k = crank, crank + cluster, ...
+      const int per_blk = nb >> 3, nmine = (K - crank + p.cluster - 1) / p.cluster;
+      for (int i = threadIdx.x; i < nmine * per_blk; i += blockDim.x) {
+        const int kb = i / per_blk, c = i - kb * per_blk;
+        const int o = (((crank + kb * p.cluster) * nb) >> 3) + c;
+        reinterpret_cast<uint4*>(xs)[o] = __ldg(reinterpret_cast<const uint4*>(xg) + o);
+      }
     } else {
       for (int i = threadIdx.x; i < p.cols; i += blockDim.x) xs[i] = xg[i];
     }
   }
-  __syncthreads();
+  cluster_barrier();        // every block's Tt is cleared before any peer writes into it
 
   // ---- power-of-two part: each warp rotates whole blocks of nb entries; a lane holds entries lane + 32 i ----
   const __half* x = xs;
   const int per = nb >= 32 ? (nb >> 5) : 1;         // 1, 2 or 4 entries per lane (lanes >= nb idle when nb < 32)
   const bool lane_on = lane < nb;
-  for (int k = warp; k < K; k += (blockDim.x >> 5)) {
+  // Block c of the cluster rotates the blocks k = c, c + cluster, ... and sends each peer the columns it owns
+  // (distributed shared memory); a cluster barrier then makes every block's Tt complete.
+  for (int k = crank + warp * p.cluster; k < K; k += (blockDim.x >> 5) * p.cluster) {
     float e[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) e[i] = (i < per && lane_on) ? __half2float(x[k * nb + i * 32 + lane]) : 0.f;
@@ -214,10 +270,16 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int j = i * 32 + lane;
-      if (i < per && lane_on && j >= col0 && j < col0 + ncols) Tt[(j - col0) * ld + k] = __float2half_rn(e[i] * p.rot_scale);
+      if (i < per && lane_on) {
+        const int owner = j / ncols, local = j - owner * ncols;
+        const __half hv = __float2half_rn(e[i] * p.rot_scale);
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(Tt + local * ld + k)), "r"(owner));
+        asm volatile("st.shared::cluster.b16 [%0], %1;" ::"r"(remote), "h"(__half_as_ushort(hv)) : "memory");
+      }
     }
   }
-  __syncthreads();
+  cluster_barrier();
 
   // ---- had_K part on the tensor cores: warp w owns m tiles w, w + 8; results stay in registers ----
   const int g = lane >> 2, t = lane & 3;
@@ -233,21 +295,19 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
       for (int c = 0; c < 4; ++c) d[mi][ni][c] = 0.f;
     if (mt < tiles) {
       const uint4* ap = p.packed + (static_cast<int64_t>(mt) * tiles) * 32 + lane;
-      for (int kt0 = 0; kt0 < tiles; kt0 += 4) {          // four k tiles of A in flight at a time
-        uint4 a[4];
+      uint4 a[16];                                         // every k tile of this m tile, loaded together
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = (kt0 + i < tiles) ? __ldg(ap + (kt0 + i) * 32) : make_uint4(0u, 0u, 0u, 0u);
+      for (int kt = 0; kt < 16; ++kt) a[kt] = kt < tiles ? __ldg(ap + kt * 32) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int kt = kt0 + i;
-          if (kt >= tiles) break;
+      for (int kt = 0; kt < 16; ++kt) {
+        if (kt < tiles) {
 #pragma unroll
           for (int ni = 0; ni < kHadMaxNtilePer; ++ni) {
             if (ni < p.ntile_per) {
               const __half* brow = Tt + (ni * 8 + g) * ld + kt * 16 + 2 * t;
               const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow);
               const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 8);
-              mma_f16_16x8x16(d[mi][ni], a[i].x, a[i].y, a[i].z, a[i].w, b0, b1);
+              mma_f16_16x8x16(d[mi][ni], a[kt].x, a[kt].y, a[kt].z, a[kt].w, b0, b1);
             }
           }
         }
@@ -464,6 +524,8 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   p.cols = a->cols;
   p.rotate = rotate ? 1 : 0;
   p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
+  p.vec8 = ((a->cols % 8) == 0 && aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && aligned(a->q, 8) &&
+            (a->q_row_stride % 8) == 0 && (a->sign == nullptr || aligned(a->sign, 16))) ? 1 : 0;
   const int smem = a->cols * 4;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(act_quant_kernel), smem));
   act_quant_kernel<<<a->rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
