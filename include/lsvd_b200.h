@@ -184,7 +184,11 @@ typedef struct lsvd_act_quant_args {
   int8_t* q;                     /* device int8 [rows, cols]                                        */
   int64_t q_row_stride;
   float* scale;                  /* device fp32 [rows]                                              */
-  void* x_rot;                   /* optional device fp16 [rows, cols] (contiguous): the rotated row */
+  void* x_rot;                   /* optional device fp16 [rows, cols] (contiguous): the row as quantised
+                                    (after the rotation or the normalisation)                        */
+  const void* norm_weight;       /* device fp16 [cols] or NULL: RMSNorm(x) * weight first, fp32 statistics and fp16
+                                    products as kernels/layer_bench/ffn_kernel/utils.py:560-565 (not with `sign`) */
+  float norm_eps;
 } lsvd_act_quant_args;
 int lsvd_act_quant(const lsvd_act_quant_args* args, void* stream);
 
@@ -228,6 +232,8 @@ typedef struct lsvd_gemv_args {
   int32_t out_col;
   int32_t* acc_out;              /* optional device int32 [m, n] raw accumulators of (w, a)          */
   int32_t* acc2_out;             /* optional, of (w2, a2)                                            */
+  const void* residual;          /* optional device fp16 [m, n] added to the fp16 result (fp16 add)  */
+  int64_t residual_row_stride;
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 

@@ -64,7 +64,7 @@ class ActQuantArgs(C.Structure):
     _fields_ = [
         ("rows", C.c_int32), ("cols", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
         ("sign", C.c_void_p), ("fwht", C.c_int32), ("q", C.c_void_p), ("q_row_stride", C.c_int64),
-        ("scale", C.c_void_p), ("x_rot", C.c_void_p),
+        ("scale", C.c_void_p), ("x_rot", C.c_void_p), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float),
     ]
 
 
@@ -83,7 +83,7 @@ class GemvArgs(C.Structure):
         ("a", C.c_void_p), ("a_row_stride", C.c_int64), ("a_scale", C.c_void_p), ("a_scale_stride", C.c_int64),
         ("a2", C.c_void_p), ("a2_row_stride", C.c_int64), ("a2_scale", C.c_void_p), ("a2_scale_stride", C.c_int64),
         ("epilogue", C.c_int32), ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("out_col", C.c_int32),
-        ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p),
+        ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
     ]
 
 

@@ -23,6 +23,8 @@ struct ActQuantParams {
   const __half* x;
   int64_t x_row_stride;
   const __half* sign;
+  const __half* norm_weight;   // RMSNorm weight [cols] or NULL
+  float norm_eps;
   int8_t* q;
   int64_t q_row_stride;
   float* scale;
@@ -97,6 +99,26 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ 
     }
   }
   __syncthreads();
+  if (p.norm_weight != nullptr) {
+    // RMSNorm as kernels/layer_bench/ffn_kernel/utils.py:560-565: fp32 statistics, the normalised value
+    // rounded to fp16, then an fp16 product with the weight.
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+    ss = warp_sum(ss);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int wi = 0; wi < (blockDim.x >> 5); ++wi) tot += red[wi];
+    const float inv = rsqrtf(tot / static_cast<float>(p.cols) + p.norm_eps);
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+      const __half xn = __float2half_rn(row[i] * inv);
+      const __half hv = __float2half_rn(__half2float(xn) * __half2float(p.norm_weight[i]));
+      row[i] = __half2float(hv);
+      if (p.x_rot != nullptr) p.x_rot[static_cast<int64_t>(r) * p.cols + i] = hv;
+    }
+    __syncthreads();
+  }
   if (p.rotate) {
     // Sylvester butterflies in fp32, stride 1 first: the same additions in the same order as the
     // reference's butterfly loop, so the rotated row is bit-identical.
@@ -368,6 +390,7 @@ struct GemvParams {
   const int8_t* a;  int64_t a_row_stride;  const float* a_scale;  int64_t a_scale_stride;
   const int8_t* a2; int64_t a2_row_stride; const float* a2_scale; int64_t a2_scale_stride;
   __half* out; int64_t out_row_stride; int32_t out_col;
+  const __half* residual; int64_t residual_row_stride;
   int32_t* acc_out; int32_t* acc2_out;
   int32_t m, n, k, epilogue;
 };
@@ -477,6 +500,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
       const __half sg = __float2half_rn(silu_f(__half2float(v0)));
       res = __float2half_rn(__half2float(sg) * __half2float(u));
     }
+    if (p.residual != nullptr)       // fp16 add of the fp16 result and the residual, as the reference's `x @ W + residual`
+      res = __float2half_rn(__half2float(res) + __half2float(p.residual[static_cast<int64_t>(tok) * p.residual_row_stride + row]));
     p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = res;
   }
 }
@@ -516,6 +541,9 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   p.x = static_cast<const __half*>(a->x);
   p.x_row_stride = a->x_row_stride;
   p.sign = static_cast<const __half*>(a->sign);
+  p.norm_weight = static_cast<const __half*>(a->norm_weight);
+  p.norm_eps = a->norm_eps;
+  if (p.norm_weight != nullptr && a->sign != nullptr) return LSVD_ERR_UNSUPPORTED;
   p.q = a->q;
   p.q_row_stride = a->q_row_stride;
   p.scale = a->scale;
@@ -616,6 +644,7 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   p.a = a->a; p.a_row_stride = a->a_row_stride; p.a_scale = a->a_scale; p.a_scale_stride = a->a_scale_stride;
   p.a2 = a->a2; p.a2_row_stride = a->a2_row_stride; p.a2_scale = a->a2_scale; p.a2_scale_stride = a->a2_scale_stride;
   p.out = static_cast<__half*>(a->out); p.out_row_stride = a->out_row_stride; p.out_col = a->out_col;
+  p.residual = static_cast<const __half*>(a->residual); p.residual_row_stride = a->residual_row_stride;
   p.acc_out = a->acc_out; p.acc2_out = a->acc2_out;
   p.m = a->m; p.n = a->n; p.k = a->k; p.epilogue = a->epilogue;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

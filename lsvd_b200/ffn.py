@@ -54,7 +54,8 @@ def _ptr(t):
     return t.data_ptr() if t is not None else None
 
 
-def act_quant(x: torch.Tensor, sign: Optional[torch.Tensor] = None, fwht: bool = False, want_rotated: bool = False):
+def act_quant(x: torch.Tensor, sign: Optional[torch.Tensor] = None, fwht: bool = False, want_rotated: bool = False,
+              norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5):
     """Per-token int8 quantisation of fp16 rows ``[rows, cols]`` (optionally after a Hadamard rotation).
     Returns (codes int8, scale fp32 [rows], rotated fp16 or None)."""
     _require_cuda(x)
@@ -72,6 +73,7 @@ def act_quant(x: torch.Tensor, sign: Optional[torch.Tensor] = None, fwht: bool =
     a.q, a.q_row_stride = q.data_ptr(), q.stride(0)
     a.scale = scale.data_ptr()
     a.x_rot = _ptr(rot)
+    a.norm_weight, a.norm_eps = _ptr(norm_weight), norm_eps
     _lib.check(_lib.load().lsvd_act_quant(C.byref(a), _stream_ptr(x)))
     return q, scale, rot
 
@@ -109,7 +111,7 @@ def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rot
 
 
 def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a2_scale=None, out=None, out_col=0,
-              want_acc=False, want_out=True):
+              want_acc=False, want_out=True, residual=None):
     """acc = a_q @ w_q^T (int32, exact) for 1..64 tokens, dequantised to fp16; with (w2, a2) a gate/up pair whose
     result is silu(gate) * up.  Returns (out fp16 [m, n] or the passed tensor, acc int32 or None, acc2 or None)."""
     _require_cuda(a_q, w_q)
@@ -135,6 +137,8 @@ def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a
     if out is not None:
         g.out, g.out_row_stride, g.out_col = out.data_ptr(), out.stride(0), out_col
     g.acc_out, g.acc2_out = _ptr(acc), _ptr(acc2)
+    if residual is not None:
+        g.residual, g.residual_row_stride = residual.data_ptr(), residual.stride(0)
     _lib.check(_lib.load().lsvd_w8a8_gemv(C.byref(g), _stream_ptr(a_q)))
     return out, acc, acc2
 
@@ -280,9 +284,12 @@ class HybridFFN(nn.Module):
         return plan
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                norm_eps: float = 1e-6, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x [..., d_in] fp16 (at most 64 tokens) -> [..., d_out] fp16.  Intermediate buffers are kept per batch size,
-        so apart from the result (unless ``out`` is passed) a call allocates nothing and can be captured in a CUDA graph."""
+        so apart from the result (unless ``out`` is passed) a call allocates nothing and can be captured in a CUDA graph.
+        ``norm_weight`` applies RMSNorm(x) * weight inside the first quantiser (for modules without an input rotation);
+        ``residual [tokens, d_out]`` is added to the result in the down projection's epilogue."""
         _require_cuda(x)
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
@@ -295,7 +302,10 @@ class HybridFFN(nn.Module):
             out = torch.empty(m, self.d_out, dtype=torch.float16, device=x.device)
         _, calls = self._plan(m, x.device)
         calls[0][1].x, calls[0][1].x_row_stride = x2.data_ptr(), x2.stride(0)
+        calls[0][1].norm_weight, calls[0][1].norm_eps = _ptr(norm_weight), norm_eps
         calls[-1][1].out = out.data_ptr()
+        calls[-1][1].residual = _ptr(residual)
+        calls[-1][1].residual_row_stride = residual.stride(0) if residual is not None else 0
         stream = _stream_ptr(x)
         for fn, args in calls:
             _lib.check(fn(C.byref(args), stream))

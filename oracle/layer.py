@@ -1,0 +1,46 @@
+"""The W8A8 decoder layer composed from the oracle's stage functions (test infrastructure).
+
+Mirrors lsvd_b200/layer.py stage by stage; every stage is one of the pinned oracle functions, plus the
+reference's RMSNorm (kernels/layer_bench/ffn_kernel/utils.py:560-565).
+"""
+import math
+
+import torch
+
+from . import quant, attention, ffn
+
+
+def rms_norm(x16, w16, eps):
+    """fp32 statistics, normalised value rounded to fp16, fp16 product with the weight."""
+    xf = x16.float()
+    xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).half()
+    return (xn.float() * w16.float()).half()
+
+
+def linear_a8w8(x16, w_q, w_s, residual=None):
+    q, s = quant.act_quant(x16)
+    y = ffn._dequant16(ffn._i32_matmul(q, w_q), s, w_s)
+    if residual is not None:
+        y = (y.float() + residual.float()).half()
+    return y
+
+
+def decoder_layer(x16, w, ffn_w, k_off, v_off, num_heads, head_dim, rank_q, cache_k, scale_k, cache_v, scale_v,
+                  req_to_token, b_req_idx, b_seq_len, mem_index):
+    """Returns (out fp16, stages).  Mutates the cache like the reference block does."""
+    Rq = num_heads * rank_q
+    xn = rms_norm(x16, w["ln1"], 1e-5)
+    lat = linear_a8w8(xn, w["W_lat_q"], w["W_lat_s"])
+    attention.cache_append(lat[:, Rq:Rq + k_off[-1]].contiguous(), mem_index, k_off, cache_k, scale_k)
+    attention.cache_append(lat[:, Rq + k_off[-1]:].contiguous(), mem_index, v_off, cache_v, scale_v)
+    q = lat[:, :Rq].reshape(-1, num_heads, rank_q)
+    ident = torch.zeros(v_off[-1], 1, dtype=torch.float16)          # the V up-projection is folded into W_uvo
+    _, o_lat = attention.decode_absorb(q, cache_k, scale_k, cache_v, scale_v, w["C"], ident, k_off, v_off,
+                                       req_to_token, b_req_idx, b_seq_len, sm_scale=1.0 / math.sqrt(head_dim),
+                                       dtype=torch.float32)
+    o16 = o_lat.half()
+    y1 = linear_a8w8(o16, w["W_uvo_q"], w["W_uvo_s"], residual=xn)
+    x2 = rms_norm(y1, w["ln2"], 1e-6)
+    st = ffn.hybrid_ffn_stages(x2, ffn_w)
+    out = (st["out"].float() + y1.float()).half()
+    return out, dict(xn=xn, lat=lat, o_lat=o16, y1=y1, out=out)
