@@ -217,7 +217,7 @@ int lsvd_hadamard_pack(const void* had_K, int32_t K, void* packed, void* stream)
  * optionally for a second weight matrix w2 (with its own activations a2, or the same ones) in the same pass.
  *   epilogue 0: out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n])              (a quantised Linear)
  *   epilogue 1: g = that for (w, a), u = that for (w2, a2); out = fp16(fp16(silu(g)) * u) (gate/up pair)
- * n a multiple of 16, k a multiple of 64, rows 16-byte aligned.  Replaces the reference's fp16 Linear on
+ * n and k multiples of 16, rows 16-byte aligned.  Replaces the reference's fp16 Linear on
  * fake-quantised tensors (ActQuantWrapper.forward, fake_quant/utils/quant_utils.py:319-333) and, on the kernel
  * side, the w8a8 matmul + dequant kernels of kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:968-1021,1292-1338. */
 typedef struct lsvd_gemv_args {

@@ -435,20 +435,22 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
   const int8_t* w2r1 = DUAL ? w2r0 + 8 * p.w2_row_stride : nullptr;
 
   constexpr int kUnroll = NT <= 2 ? 4 : (NT == 4 ? 2 : 1);     // spans whose loads are issued together
-#pragma unroll kUnroll
-  for (int s = s_begin; s < s_end; ++s) {
-    const int ko = s * 64;
-    const uint4 x0 = ldg_u4(wr0 + ko), x1 = ldg_u4(wr1 + ko);
-    uint4 y0, y1;
-    if (DUAL) {
-      y0 = ldg_u4(w2r0 + ko);
-      y1 = ldg_u4(w2r1 + ko);
+  auto span = [&](int ko, bool on) {
+    // `on` is false only for the lanes past the end of a last, partial span (K a multiple of 16, not of 64)
+    uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0, y0 = x0, y1 = x0;
+    if (on) {
+      x0 = ldg_u4(wr0 + ko);
+      x1 = ldg_u4(wr1 + ko);
+      if (DUAL) {
+        y0 = ldg_u4(w2r0 + ko);
+        y1 = ldg_u4(w2r1 + ko);
+      }
     }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       const int tok = j * 8 + g;
       uint4 bv = make_uint4(0u, 0u, 0u, 0u);
-      if (tok < p.m) bv = ldg_u4(p.a + tok * p.a_row_stride + ko + 16 * t);
+      if (on && tok < p.m) bv = ldg_u4(p.a + tok * p.a_row_stride + ko + 16 * t);
       // the MMA's k index is a permutation of the 32 columns that A and B share: k 4t..4t+3 <-> the first
       // four of a lane's bytes, k 16+4t.. <-> the next four
       mma_s8(acc[0][j], x0.x, x1.x, x0.y, x1.y, bv.x, bv.y);
@@ -457,13 +459,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
         uint4 bw = bv;
         if (SPLIT_B) {
           bw = make_uint4(0u, 0u, 0u, 0u);
-          if (tok < p.m) bw = ldg_u4(p.a2 + tok * p.a2_row_stride + ko + 16 * t);
+          if (on && tok < p.m) bw = ldg_u4(p.a2 + tok * p.a2_row_stride + ko + 16 * t);
         }
         mma_s8(acc[NMAT - 1][j], y0.x, y1.x, y0.y, y1.y, bw.x, bw.y);
         mma_s8(acc[NMAT - 1][j], y0.z, y1.z, y0.w, y1.w, bw.z, bw.w);
       }
     }
-  }
+  };
+#pragma unroll kUnroll
+  for (int s = s_begin; s < s_end; ++s) span(s * 64, true);
+  if ((p.k & 63) != 0 && warp == kGemvWarps - 1) span(spans * 64, 16 * t < (p.k & 63));
 
   // ---- sum the warps' shares ----
   int* mine = red + warp * (NMAT * NT * 4 * 32);
@@ -626,7 +631,7 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
 
 extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   using namespace lsvd;
-  if (a == nullptr || a->m <= 0 || a->m > 64 || a->n <= 0 || (a->n % 16) || a->k <= 0 || (a->k % 64))
+  if (a == nullptr || a->m <= 0 || a->m > 64 || a->n <= 0 || (a->n % 16) || a->k <= 0 || (a->k % 16))
     return LSVD_ERR_INVALID_ARG;
   if (!a->w || !a->a) return LSVD_ERR_INVALID_ARG;
   if (a->out != nullptr && (!a->w_scale || !a->a_scale)) return LSVD_ERR_INVALID_ARG;

@@ -174,8 +174,8 @@ class HybridFFN(nn.Module):
         self.d_in = self.U_q.shape[1]
         self.d_ffn = self.n_svd + self.n_q
         self.d_out = self.Wd_q.shape[0]
-        if self.n_svd % 16 or self.n_q % 16 or self.d_out % 16 or self.rank % 64 or self.d_in % 64 or self.d_ffn % 64:
-            raise ValueError("channel groups must be multiples of 16 and reduction sizes multiples of 64")
+        if self.n_svd % 16 or self.n_q % 16 or self.d_out % 16 or self.rank % 16 or self.d_in % 16:
+            raise ValueError("channel groups and reduction sizes must be multiples of 16")
 
     @classmethod
     def from_float(cls, U, Vg, Vu, Wg, Wu, Wd, had_sign=None, had_K=None, K=1, mse=False, online_had=True):

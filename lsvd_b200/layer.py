@@ -85,3 +85,78 @@ def make_layer_weights(hidden: int, num_heads: int, head_dim: int, rank_q: int, 
     w["W_lat_q"], w["W_lat_s"] = quantize_weight_rtn(W_lat)
     w["W_uvo_q"], w["W_uvo_s"] = quantize_weight_rtn(W_uvo)
     return w
+
+
+class TPDecoderLayer(nn.Module):
+    """The decoder layer of one tensor-parallel rank (see lsvd_b200/parallel.py for the sharding).
+
+    Built from that rank's local weights; ``forward`` takes the replicated hidden state and the rank's own cache
+    columns, and issues one all-reduce in the attention block, one all-gather and one all-reduce in the FFN block.
+    """
+
+    def __init__(self, lw: dict, fw: dict, info: dict, head_dim: int, rank_q: int, world: int, group=None):
+        super().__init__()
+        self.info, self.head_dim, self.rank_q, self.world, self.group = info, head_dim, rank_q, world, group
+        self.layout = LatentCacheLayout(info["k_ranks"], info["v_ranks"])
+        for name in ("ln1", "ln2", "W_lat_q", "W_lat_s", "C", "W_uvo_q", "W_uvo_s"):
+            self.register_buffer(name, lw[name].contiguous())
+        for name in ("U_q", "U_s", "Vg_q", "Vg_s", "Vu_q", "Vu_s", "Wg_q", "Wg_s", "Wu_q", "Wu_s", "Wd_svd_q", "Wd_rtn_q", "Wd_s"):
+            self.register_buffer("f_" + name, fw[name].contiguous())
+        self.K = int(fw.get("K", 1))
+        hk = fw.get("had_K")
+        self.register_buffer("had_K", None if hk is None else hk.to(torch.float16).contiguous())
+        self.had_K_packed = None
+        self.Rq = self.layout.num_heads * rank_q
+        self._ws = None
+
+    @torch.no_grad()
+    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages=None):
+        import torch.distributed as dist
+        from .ffn import hadamard_pack, hadamard_quant
+        from .parallel import gather_hidden
+        lay, Hl, B, dev = self.layout, self.layout.num_heads, x.shape[0], x.device
+        xq, xs, xn = act_quant(x, want_rotated=True, norm_weight=self.ln1, norm_eps=1e-5)
+        lat, _, _ = w8a8_gemv(xq, xs, self.W_lat_q, self.W_lat_s)
+        cache_append(lay, lat[:, self.Rq:self.Rq + lay.sum_k], lat[:, self.Rq + lay.sum_k:], infer_state.mem_index,
+                     cache_k, scale_k, cache_v, scale_v)
+        need = attn_decode_workspace_bytes(B, lay, infer_state.max_len_in_batch)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        o_lat = torch.empty(B, lay.sum_v, dtype=torch.float16, device=dev)
+        token_decode_attention_int8_latent_absorb(lat[:, :self.Rq].unflatten(1, (Hl, self.rank_q)), infer_state, Hl,
+                                                  self.rank_q, cache_k, scale_k, cache_v, scale_v, self.C, None,
+                                                  layout=lay, out_latent=o_lat, workspace=self._ws,
+                                                  sm_scale=1.0 / math.sqrt(self.head_dim))
+        # row-parallel output projection: dequantised partial sums in fp32, ONE all-reduce, then the residual
+        oq, os_, _ = act_quant(o_lat)
+        _, acc, _ = w8a8_gemv(oq, os_, self.W_uvo_q, None, want_acc=True, want_out=False)
+        part = (acc.float() * os_[:, None]) * self.W_uvo_s[None, :]
+        dist.all_reduce(part, group=self.group)
+        y1 = (part + xn.float()).half()
+        # FFN: replicated latents, column-parallel gate/up, gathered hidden vector, row-parallel int32 down projection
+        r = self.f_U_q.shape[0] // 2
+        x2q, x2s, _ = act_quant(y1, norm_weight=self.ln2, norm_eps=1e-6)
+        lat2, _, _ = w8a8_gemv(x2q, x2s, self.f_U_q, self.f_U_s)
+        zq, zs, _ = act_quant(lat2.view(-1, r))
+        zq, zs = zq.view(-1, 2 * r), zs.view(-1, 2)
+        ns, nq = self.f_Vg_q.shape[0], self.f_Wg_q.shape[0]
+        h_local = torch.empty(B, ns + nq, dtype=torch.float16, device=dev)
+        w8a8_gemv(zq[:, :r], zs[:, 0], self.f_Vg_q, self.f_Vg_s, self.f_Vu_q, self.f_Vu_s, a2_q=zq[:, r:], a2_scale=zs[:, 1],
+                  out=h_local, out_col=0)
+        w8a8_gemv(x2q, x2s, self.f_Wg_q, self.f_Wg_s, self.f_Wu_q, self.f_Wu_s, out=h_local, out_col=ns)
+        h = gather_hidden(h_local, self.info, self.world, self.group)
+        if self.had_K_packed is None:
+            self.had_K_packed = hadamard_pack(self.had_K)
+        hq, hs, _ = hadamard_quant(h, self.had_K_packed, self.K)
+        s0, s1 = self.info["svd"]
+        q0, q1 = self.info["rtn"]
+        n_svd = self.info["n_svd"]
+        _, a1, _ = w8a8_gemv(hq[:, s0:s1], hs, self.f_Wd_svd_q, None, want_acc=True, want_out=False)
+        _, a2, _ = w8a8_gemv(hq[:, n_svd + q0:n_svd + q1], hs, self.f_Wd_rtn_q, None, want_acc=True, want_out=False)
+        acc = a1 + a2
+        dist.all_reduce(acc, group=self.group)
+        down = ((acc.float() * hs[:, None]) * self.f_Wd_s[None, :]).half()
+        out = (down.float() + y1.float()).half()
+        if stages is not None:
+            stages.update(xn=xn, o_lat=o_lat, y1=y1, h_q=hq, down_acc=acc, out=out)
+        return out

@@ -44,3 +44,52 @@ def decoder_layer(x16, w, ffn_w, k_off, v_off, num_heads, head_dim, rank_q, cach
     st = ffn.hybrid_ffn_stages(x2, ffn_w)
     out = (st["out"].float() + y1.float()).half()
     return out, dict(xn=xn, lat=lat, o_lat=o16, y1=y1, out=out)
+
+
+def decoder_layer_tp_rank(x16, lw, fw, info, head_dim, rank_q, world, cache_k, scale_k, cache_v, scale_v,
+                          req_to_token, b_req_idx, b_seq_len, mem_index, group=None):
+    """One tensor-parallel rank of the layer on the CPU (gloo collectives): the same algebra as
+    lsvd_b200.layer.TPDecoderLayer with the oracle's stage functions.  ``cache_*`` hold this rank's columns."""
+    import torch.distributed as dist
+    from lsvd_b200.parallel import gather_hidden
+    kr, vr = info["k_ranks"], info["v_ranks"]
+    k_off, v_off = [0], [0]
+    for a, b in zip(kr, vr):
+        k_off.append(k_off[-1] + a)
+        v_off.append(v_off[-1] + b)
+    Hl = len(kr)
+    Rq = Hl * rank_q
+    xn = rms_norm(x16, lw["ln1"], 1e-5)
+    lat = linear_a8w8(xn, lw["W_lat_q"], lw["W_lat_s"])
+    attention.cache_append(lat[:, Rq:Rq + k_off[-1]].contiguous(), mem_index, k_off, cache_k, scale_k)
+    attention.cache_append(lat[:, Rq + k_off[-1]:].contiguous(), mem_index, v_off, cache_v, scale_v)
+    ident = torch.zeros(v_off[-1], 1, dtype=torch.float16)
+    _, o_lat = attention.decode_absorb(lat[:, :Rq].reshape(-1, Hl, rank_q), cache_k, scale_k, cache_v, scale_v, lw["C"],
+                                       ident, k_off, v_off, req_to_token, b_req_idx, b_seq_len,
+                                       sm_scale=1.0 / math.sqrt(head_dim), dtype=torch.float32)
+    oq, os_ = quant.act_quant(o_lat.half())
+    part = (ffn._i32_matmul(oq, lw["W_uvo_q"]).float() * os_[:, None]) * lw["W_uvo_s"][None, :]
+    dist.all_reduce(part, group=group)
+    y1 = (part + xn.float()).half()
+    x2 = rms_norm(y1, lw["ln2"], 1e-6)
+    x2q, x2s = quant.act_quant(x2)
+    r = fw["U_q"].shape[0] // 2
+    lat2 = ffn._dequant16(ffn._i32_matmul(x2q, fw["U_q"]), x2s, fw["U_s"])
+    gq, gs = quant.act_quant(lat2[:, :r])
+    uq, us = quant.act_quant(lat2[:, r:])
+    g16 = torch.cat((ffn._dequant16(ffn._i32_matmul(gq, fw["Vg_q"]), gs, fw["Vg_s"]),
+                     ffn._dequant16(ffn._i32_matmul(x2q, fw["Wg_q"]), x2s, fw["Wg_s"])), 1)
+    u16 = torch.cat((ffn._dequant16(ffn._i32_matmul(uq, fw["Vu_q"]), us, fw["Vu_s"]),
+                     ffn._dequant16(ffn._i32_matmul(x2q, fw["Wu_q"]), x2s, fw["Wu_s"])), 1)
+    h_local = ffn.silu_mul16(g16, u16)
+    h = gather_hidden(h_local, info, world, group)
+    h_rot = ffn.hadamard_full(h, fw["had_K"], fw["K"])
+    hq, hs = quant.act_quant(h_rot)
+    s0, s1 = info["svd"]
+    q0, q1 = info["rtn"]
+    n_svd = info["n_svd"]
+    acc = ffn._i32_matmul(hq[:, s0:s1], fw["Wd_svd_q"]) + ffn._i32_matmul(hq[:, n_svd + q0:n_svd + q1], fw["Wd_rtn_q"])
+    dist.all_reduce(acc, group=group)
+    down = ((acc.float() * hs[:, None]) * fw["Wd_s"][None, :]).half()
+    out = (down.float() + y1.float()).half()
+    return out, dict(y1=y1, h_q=hq, down_acc=acc, out=out)

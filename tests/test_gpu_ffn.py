@@ -100,7 +100,7 @@ def test_gemv_int32_exact_and_dequant(m):
     assert torch.equal(out.cpu(), offn._dequant16(acc_ref, sa, sw))
 
 
-@pytest.mark.parametrize("m,n,k,split", [(1, 5504, 512, True), (64, 1024, 512, True), (8, 688, 4096, False), (64, 512, 4096, False),
+@pytest.mark.parametrize("m,n,k,split", [(2, 64, 688, False), (9, 32, 48, None), (4, 48, 1376 + 16, True), (1, 5504, 512, True), (64, 1024, 512, True), (8, 688, 4096, False), (64, 512, 4096, False),
                                           (3, 4096, 11008, None)])
 def test_gemv_shapes_dual_and_down(m, n, k, split):
     gen = torch.Generator().manual_seed(m * 7 + n)
