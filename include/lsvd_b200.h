@@ -237,6 +237,26 @@ typedef struct lsvd_gemv_args {
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * W8A8 GEMM for prefill / large batches on tcgen05 (kind::i8, accumulators in tensor memory, TMA-fed).
+ * acc[m, n] = sum_k a[m, k] * w[n, k] (int32, exact); out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n]);
+ * with w2: a gate/up pair sharing the activations, out = fp16(fp16(silu(gate)) * up).  Same values as
+ * lsvd_w8a8_gemv for any m.  n and k multiples of 16, rows 16-byte aligned.  Replaces the int8 tl.dot kernels of
+ * kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:410-500,903-1021,1152-1338 at prefill sizes.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lsvd_i8gemm_args {
+  int32_t m, n, k;
+  const int8_t* a;  int64_t a_row_stride;  const float* a_scale;     /* activations [m, k], scale per row      */
+  const int8_t* w;  int64_t w_row_stride;  const float* w_scale;     /* weights [n, k], scale per row           */
+  const int8_t* w2; int64_t w2_row_stride; const float* w2_scale;    /* NULL: single product                    */
+  void* out;                     /* device fp16, or NULL when only accumulators are wanted            */
+  int64_t out_row_stride;
+  int32_t out_col;
+  int32_t* acc_out;              /* optional device int32 [m, n] (single product only)                */
+  int32_t* status_word;          /* device int32 or NULL: LSVD_ERR_TIMEOUT if a bounded wait gave up  */
+} lsvd_i8gemm_args;
+int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,6 +87,17 @@ class GemvArgs(C.Structure):
     ]
 
 
+class I8GemmArgs(C.Structure):
+    _fields_ = [
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("a", C.c_void_p), ("a_row_stride", C.c_int64), ("a_scale", C.c_void_p),
+        ("w", C.c_void_p), ("w_row_stride", C.c_int64), ("w_scale", C.c_void_p),
+        ("w2", C.c_void_p), ("w2_row_stride", C.c_int64), ("w2_scale", C.c_void_p),
+        ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("out_col", C.c_int32),
+        ("acc_out", C.c_void_p), ("status_word", C.c_void_p),
+    ]
+
+
 # Every symbol include/lsvd_b200.h declares, with its ctypes signature.
 SIGNATURES = {
     "lsvd_abi_version": (C.c_int, []),
@@ -102,6 +113,7 @@ SIGNATURES = {
     "lsvd_hadamard_packed_bytes": (C.c_size_t, [C.c_int32]),
     "lsvd_hadamard_pack": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),
+    "lsvd_i8gemm_prefill": (C.c_int, [C.POINTER(I8GemmArgs), C.c_void_p]),
     "lsvd_attn_decode_plan": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
                                         C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
 }

@@ -310,3 +310,28 @@ class HybridFFN(nn.Module):
         for fn, args in calls:
             _lib.check(fn(C.byref(args), stream))
         return out.view(*shape[:-1], self.d_out)
+
+
+def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_col=0, want_acc=False, want_out=True,
+           status_word=None):
+    """W8A8 product for any number of tokens on the tcgen05 tensor cores (prefill-sized batches): the same values
+    as ``w8a8_gemv``.  Returns (out fp16 or None, acc int32 or None)."""
+    _require_cuda(a_q, w_q)
+    m, k = a_q.shape
+    n = w_q.shape[0]
+    dev = a_q.device
+    if out is None and want_out:
+        out = torch.empty(m, n, dtype=torch.float16, device=dev)
+    acc = torch.empty(m, n, dtype=torch.int32, device=dev) if want_acc else None
+    g = _lib.I8GemmArgs()
+    g.m, g.n, g.k = m, n, k
+    g.a, g.a_row_stride, g.a_scale = a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr()
+    g.w, g.w_row_stride, g.w_scale = w_q.data_ptr(), w_q.stride(0), w_scale.data_ptr()
+    if w2_q is not None:
+        g.w2, g.w2_row_stride, g.w2_scale = w2_q.data_ptr(), w2_q.stride(0), w2_scale.data_ptr()
+    if out is not None:
+        g.out, g.out_row_stride, g.out_col = out.data_ptr(), out.stride(0), out_col
+    g.acc_out = _ptr(acc)
+    g.status_word = _ptr(status_word)
+    _lib.check(_lib.load().lsvd_i8gemm_prefill(C.byref(g), _stream_ptr(a_q)))
+    return out, acc
