@@ -37,6 +37,8 @@ constexpr int kTileTokens = 32;          // tokens per tile
 constexpr int kStreamWarps = 16;         // warps per block (one block per SM)
 constexpr int kStreamThreads = kStreamWarps * 32;
 constexpr int kItemBytes = 24 * 1024;    // target size of a work item (K + V bytes of its tokens)
+constexpr int kMaxItemTiles = 8;         // and its largest number of 32-token steps: a step costs a memory round trip
+                                         // whatever the head's rank, and the last items of a call run alone
 constexpr int kLimbMax = 63 * (16384 + 128 + 1);   // largest integer three balanced base-128 limbs hold
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -252,25 +254,22 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     for (int r = 0; r < 4; ++r) acc[gi][r][0] = acc[gi][r][1] = 0.f;
 
   const int tok_begin = t0 * kTileTokens, tok_end = min(len, t1 * kTileTokens);
-  // slot of "my" token of the first step (lane = token role), fetched one step ahead from then on
-  int myslot = -1;
-  if (tok_begin + lane < tok_end) myslot = r2t[tok_begin + lane];
-
-  for (int tb = tok_begin; tb < tok_end; tb += kTileTokens) {
-    int slot_next = -1;
-    if (tb + kTileTokens + lane < tok_end) slot_next = r2t[tb + kTileTokens + lane];
-    bool valid = myslot >= 0;
-    if (valid && myslot >= p.num_slots) {
+  // Software pipeline: the K latents of step i+1 are requested right after the score MMAs of step i have
+  // consumed their registers, so they travel during the softmax and the value MMAs; the V latents of step i
+  // are requested at the top of the step and travel during its score MMAs.  Slot numbers run two steps ahead.
+  uint2 ka[4][4];                    // [token g + 8j][32-rank block]
+  auto resolve = [&](int slot, bool& valid, int& rslot) {
+    valid = slot >= 0;
+    if (valid && slot >= p.num_slots) {
       report_status(p.status_word, LSVD_ERR_BOUNDS);
       valid = false;
     }
     // Lanes without a token read the row of the step's first token instead (always a real row): what they
     // load meets a zero weight or a masked score, and no load needs a validity predicate.
-    const int slot0 = __shfl_sync(0xffffffffu, valid ? myslot : -1, 0);
-    const int rslot = valid ? myslot : max(slot0, 0);
-
-    // ---- issue the loads of the step ----
-    uint2 ka[4][4];                  // [token g + 8j][32-rank block]
+    const int slot0 = __shfl_sync(0xffffffffu, valid ? slot : -1, 0);
+    rslot = valid ? slot : max(slot0, 0);
+  };
+  auto load_k = [&](int rslot) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int slot = __shfl_sync(0xffffffffu, rslot, g + 8 * j);
@@ -281,6 +280,23 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
         if (kb * 2 + (t4 >> 1) < nk) ka[j][kb] = ldg64(row + kb * 32);
       }
     }
+  };
+  bool valid;
+  int rslot;
+  {
+    int s0 = -1;
+    if (tok_begin + lane < tok_end) s0 = r2t[tok_begin + lane];
+    resolve(s0, valid, rslot);
+  }
+  load_k(rslot);
+  float ks = __half2float(ksc[rslot * p.scale_k_row_stride]);
+  int slot_n1 = -1;                  // slot of "my" token of the next step (lane = token role)
+  if (tok_begin + kTileTokens + lane < tok_end) slot_n1 = r2t[tok_begin + kTileTokens + lane];
+
+  for (int tb = tok_begin; tb < tok_end; tb += kTileTokens) {
+    int slot_n2 = -1;
+    if (tb + 2 * kTileTokens + lane < tok_end) slot_n2 = r2t[tb + 2 * kTileTokens + lane];
+    // ---- request the V latents of this step ----
     uint2 va[8], vb[8];              // [token 8t + i] of the first / second 64-rank group
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -290,7 +306,6 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
       if (v_ok0) va[i] = ldg64(row);
       if (v_ok1) vb[i] = ldg64(row + 64);
     }
-    const float ks = __half2float(ksc[rslot * p.scale_k_row_stride]);
     const float vs = __half2float(vsc[rslot * p.scale_v_row_stride]);
 
     // ---- scores ----
@@ -323,13 +338,20 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
       if ((lane >> 3) == j) s_raw = got;
     }
     const float s = valid ? s_raw * (ks * step) : -INFINITY;      // log2 domain
+    // ---- request the K latents of the next step (their registers are free now) ----
+    const bool valid_cur = valid;
+    if (tb + kTileTokens < tok_end) {
+      resolve(slot_n1, valid, rslot);
+      load_k(rslot);
+      ks = __half2float(ksc[rslot * p.scale_k_row_stride]);
+    }
     // ---- online softmax; the running maximum is shared by the warp ----
     const float mx = fmaxf(m, warp_max_redux(s));
     const float corr = exp2f(m - mx);
     m = mx;
     const float pr = exp2f(s - mx);
     l = fmaf(l, corr, pr);
-    const float w = valid ? pr * vs : 0.f;
+    const float w = valid_cur ? pr * vs : 0.f;
     // ---- weights of the 32 tokens as two unsigned base-256 limbs against the step's largest weight (16 bits) ----
     const float wmax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(w)));   // w >= 0
     const float winv = wmax > 0.f ? 65535.f / wmax : 0.f;
@@ -374,7 +396,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
         }
       }
     }
-    myslot = slot_next;
+    slot_n1 = slot_n2;
   }
 
   // ---- this item's partial result ----
@@ -568,7 +590,6 @@ static int make_plan(int batch, int num_heads, const int32_t* k_off, const int32
   if (sms <= 0) return LSVD_ERR_CUDA;
   const int ntiles_max = (max_len + kTileTokens - 1) / kTileTokens;
   hp->item_bytes = choose_item_bytes(batch, k_off[num_heads], v_off[num_heads], max_len, sms);
-  int part_off = 0, acc_off = 0;
   for (int h = 0; h < num_heads; ++h) {
     HeadPlan& H = hp->head[h];
     const int rk = k_off[h + 1] - k_off[h], rv = v_off[h + 1] - v_off[h];
@@ -576,15 +597,19 @@ static int make_plan(int batch, int num_heads, const int32_t* k_off, const int32
     H.v_col = v_off[h];
     H.nk = static_cast<int16_t>(rk / 16);
     H.nv = static_cast<int16_t>(rv / 16);
-    const int ct = std::max(1, std::min(16384, hp->item_bytes / (kTileTokens * (rk + rv))));
+    const int ct = std::max(1, std::min(kMaxItemTiles, hp->item_bytes / (kTileTokens * (rk + rv))));
     H.chunk_tiles = static_cast<int16_t>(ct);
     const int parts = std::max(1, (ntiles_max + ct - 1) / ct);
     if (parts > 32767) return LSVD_ERR_UNSUPPORTED;
     H.parts = static_cast<int16_t>(parts);
+  }
+  int part_off = 0, acc_off = 0;
+  for (int h = 0; h < num_heads; ++h) {
+    HeadPlan& H = hp->head[h];
     H.part_off = part_off;
     H.acc_off = acc_off;
-    part_off += parts;
-    acc_off += parts * rv;
+    part_off += H.parts;
+    acc_off += H.parts * H.nv * 16;
   }
   hp->items_per_request = part_off;
   hp->acc_per_request = acc_off;
@@ -624,7 +649,8 @@ extern "C" size_t lsvd_attn_decode_workspace_bytes(int32_t batch, int32_t num_he
   const int sms = std::max(1, device_sm_count());
   const int64_t ntiles_max = (max_len_in_batch + kTileTokens - 1) / kTileTokens;
   const int item_bytes = choose_item_bytes(batch, sum_rank_k, sum_rank_v, max_len_in_batch, sms);
-  const int64_t items = 2 * ntiles_max * kTileTokens * (sum_rank_k + sum_rank_v) / item_bytes + num_heads + 1;
+  const int64_t items = 2 * ntiles_max * kTileTokens * (sum_rank_k + sum_rank_v) / item_bytes + num_heads + 1 +
+                        static_cast<int64_t>(num_heads) * (ntiles_max / kMaxItemTiles + 1);
   const int64_t items_b = std::min<int64_t>(items, ntiles_max * num_heads + num_heads);
   return workspace_layout(batch, num_heads, sum_rank_k, items_b, items_b * LSVD_MAX_RANK).total;
 }
