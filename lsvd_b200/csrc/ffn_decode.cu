@@ -426,9 +426,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0;
 
-  // this warp's share of K, in spans of 64 (a lane's 16 bytes per row cover two 32-wide MMA steps)
+  // K is cut into spans of 64 bytes (a lane's 16 bytes per row cover two 32-wide MMA steps).  Runs of kUnroll
+  // spans are dealt to the warps round-robin, so at any moment the block reads one contiguous stretch of each
+  // of its rows (8 warps x kUnroll x 64 bytes) instead of eight distant ones: DRAM pages stay open.
   const int spans = p.k >> 6;
-  const int s_begin = (warp * spans) / kGemvWarps, s_end = ((warp + 1) * spans) / kGemvWarps;
   const int8_t* wr0 = p.w + (row0 + g) * p.w_row_stride + 16 * t;
   const int8_t* wr1 = wr0 + 8 * p.w_row_stride;
   const int8_t* w2r0 = DUAL ? p.w2 + (row0 + g) * p.w2_row_stride + 16 * t : nullptr;
@@ -466,8 +467,18 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
       }
     }
   };
-#pragma unroll kUnroll
-  for (int s = s_begin; s < s_end; ++s) span(s * 64, true);
+  if (spans >= kGemvWarps * kUnroll) {
+    for (int s0 = warp * kUnroll; s0 < spans; s0 += kGemvWarps * kUnroll) {
+      if (s0 + kUnroll <= spans) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) span((s0 + u) * 64, true);
+      } else {
+        for (int s = s0; s < spans; ++s) span(s * 64, true);
+      }
+    }
+  } else {                                   // short K: single spans, so that every warp gets some
+    for (int s = warp; s < spans; s += kGemvWarps) span(s * 64, true);
+  }
   if ((p.k & 63) != 0 && warp == kGemvWarps - 1) span(spans * 64, 16 * t < (p.k & 63));
 
   // ---- sum the warps' shares ----

@@ -168,6 +168,8 @@ class HybridFFN(nn.Module):
         self.register_buffer("had_K_packed", None if (hk is None or self.K == 1 or not hk.is_cuda)
                              else hadamard_pack(self.had_K))
         self._plans = {}
+        self._side_streams = {}
+        self.overlap_branches = True      # RTN gate/up on a second stream beside the SVD branch
         self.rank = self.U_q.shape[0] // 2
         self.n_svd = self.Vg_q.shape[0]
         self.n_q = self.Wg_q.shape[0]
@@ -307,9 +309,35 @@ class HybridFFN(nn.Module):
         calls[-1][1].residual = _ptr(residual)
         calls[-1][1].residual_row_stride = residual.stride(0) if residual is not None else 0
         stream = _stream_ptr(x)
-        for fn, args in calls:
+        if not self.overlap_branches:
+            for fn, args in calls:
+                _lib.check(fn(C.byref(args), stream))
+            return out.view(*shape[:-1], self.d_out)
+        # The RTN gate/up product (calls[4]) needs only the quantised input: it runs on a second stream beside
+        # the SVD branch (latent product, latent quantiser, gate/up from the latents) and joins before the
+        # Hadamard quantiser.  Inside a CUDA graph capture the two streams become parallel branches.
+        cur = torch.cuda.current_stream(x.device)
+        side, fork, join = self._side(x.device)
+        _lib.check(calls[0][0](C.byref(calls[0][1]), stream))
+        fork.record(cur)
+        side.wait_event(fork)
+        _lib.check(calls[4][0](C.byref(calls[4][1]), side.cuda_stream))
+        join.record(side)
+        for fn, args in calls[1:4]:
+            _lib.check(fn(C.byref(args), stream))
+        cur.wait_event(join)
+        for fn, args in calls[5:]:
             _lib.check(fn(C.byref(args), stream))
         return out.view(*shape[:-1], self.d_out)
+
+    def _side(self, device):
+        key = str(device)
+        got = self._side_streams.get(key)
+        if got is None:
+            with torch.cuda.device(device):
+                got = (torch.cuda.Stream(), torch.cuda.Event(), torch.cuda.Event())
+            self._side_streams[key] = got
+        return got
 
 
 def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_col=0, want_acc=False, want_out=True,
