@@ -234,6 +234,11 @@ typedef struct lsvd_gemv_args {
   int32_t* acc2_out;             /* optional, of (w2, a2)                                            */
   const void* residual;          /* optional device fp16 [m, n] added to the fp16 result (fp16 add)  */
   int64_t residual_row_stride;
+  int32_t* status_word;          /* device int32 or NULL: LSVD_ERR_TIMEOUT if a pipeline wait of the   */
+                                 /* TMA-fed form ran out; the output is then incomplete               */
+  int32_t form;                  /* 0: register-fed kernel (default, the faster one so far);           */
+                                 /* 1: persistent TMA-fed kernel, m <= 16 only (LSVD_ERR_UNSUPPORTED   */
+                                 /*    beyond); same values                                            */
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 

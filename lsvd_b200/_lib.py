@@ -84,6 +84,7 @@ class GemvArgs(C.Structure):
         ("a2", C.c_void_p), ("a2_row_stride", C.c_int64), ("a2_scale", C.c_void_p), ("a2_scale_stride", C.c_int64),
         ("epilogue", C.c_int32), ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("out_col", C.c_int32),
         ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
+        ("status_word", C.c_void_p), ("form", C.c_int32),
     ]
 
 

@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(128) absorb_query_kernel(const __grid_constant
   __shared__ float qs[256];
   __shared__ float qt[LSVD_MAX_RANK];
   __shared__ float wmax[4];
+  grid_dependency_sync();
   const int h = blockIdx.x, b = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (h == 0 && b == 0 && threadIdx.x == 0) *p.queue = 0;
@@ -427,6 +428,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const 
   __shared__ uint4 limb_scratch[kStreamWarps][8 * 3];
   __shared__ __align__(16) uint8_t weight_limbs[kStreamWarps][96];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_dependency_sync();
 
   for (;;) {
     // ---- take the next item: (request b, head h, part k) ----
@@ -480,8 +482,9 @@ __global__ void __launch_bounds__(128) merge_up_kernel(const __grid_constant__ M
   __shared__ float olat[LSVD_MAX_RANK];
   const int h = blockIdx.x, b = blockIdx.y;
   const int v0_col = p.v_off[h], rv = p.v_off[h + 1] - v0_col;
-  // The up-factor does not depend on the partial results: fetch it first, with wide loads, so that its
-  // latency overlaps the merge.
+  grid_dependency_release();
+  // The up-factor does not depend on the partial results, nor on any kernel before this one: fetch it first,
+  // with wide loads, so that its latency overlaps the end of the stream kernel and the merge.
   if (p.out != nullptr && p.up_v_vec16) {
     const int per_row = p.head_dim >> 3;
     for (int i = threadIdx.x; i < rv * per_row; i += blockDim.x) {
@@ -490,6 +493,7 @@ __global__ void __launch_bounds__(128) merge_up_kernel(const __grid_constant__ M
           __ldg(reinterpret_cast<const uint4*>(p.up_v + static_cast<int64_t>(v0_col + r) * p.up_v_row_stride) + c);
     }
   }
+  grid_dependency_wait();
   // Items of (b, h) that held tokens: the same arithmetic as the stream kernel.
   const int ntiles = tiles_of(p.b_seq_len[b]);
   int nparts = (ntiles + p.chunk_tiles[h] - 1) / p.chunk_tiles[h];
@@ -708,8 +712,7 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
   ap.sum_rk = sum_rk;
   ap.up_k_vec16 = (aligned(a->up_k, 16) && (a->up_k_row_stride % 8) == 0) ? 1 : 0;
   std::memcpy(ap.k_off, a->k_off, sizeof(int32_t) * (a->num_heads + 1));
-  absorb_query_kernel<<<dim3(a->num_heads, a->batch), 128, 0, st>>>(ap);
-  LSVD_CUDA_TRY(cudaGetLastError());
+  LSVD_CUDA_TRY(launch_chained(absorb_query_kernel, dim3(a->num_heads, a->batch), dim3(128), 0, st, 1, true, ap));
 
   if (a->max_len_in_batch > 0) {
     StreamParams sp{};
@@ -740,8 +743,7 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
     sp.total_items = static_cast<int32_t>(hp.total_items);
     for (int h = 0; h < a->num_heads; ++h) sp.head[h] = hp.head[h];
     if (a->ev_stream_begin) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_begin), st));
-    latent_stream_kernel<<<hp.num_blocks, kStreamThreads, 0, st>>>(sp);
-    LSVD_CUDA_TRY(cudaGetLastError());
+    LSVD_CUDA_TRY(launch_chained(latent_stream_kernel, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
     if (a->ev_stream_end) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_end), st));
   }
 
@@ -773,8 +775,7 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
   for (int h = 0; h < a->num_heads; ++h) max_rv = std::max(max_rv, a->v_off[h + 1] - a->v_off[h]);
   const int merge_smem = (a->out != nullptr && mp.up_v_vec16) ? max_rv * a->head_dim * 2 : 0;
   if (merge_smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(merge_up_kernel), merge_smem));
-  merge_up_kernel<<<dim3(a->num_heads, a->batch), 128, merge_smem, st>>>(mp);
-  LSVD_CUDA_TRY(cudaGetLastError());
+  LSVD_CUDA_TRY(launch_chained(merge_up_kernel, dim3(a->num_heads, a->batch), dim3(128), merge_smem, st, 1, true, mp));
   return LSVD_OK;
 }
 

@@ -49,6 +49,7 @@ __device__ __forceinline__ int quantise_one(float x, float s) {
 
 template <int kRounding>
 __global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant__ AppendParams p) {
+  grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t per_side = static_cast<int64_t>(p.num_tokens) * p.num_heads;
@@ -168,10 +169,10 @@ extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
   const int64_t blocks = (warps + warps_per_block - 1) / warps_per_block;
   if (blocks > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>(blocks)), block(warps_per_block * 32);
   if (a->rounding == LSVD_ROUND_TORCH)
-    cache_append_kernel<LSVD_ROUND_TORCH><<<static_cast<unsigned>(blocks), warps_per_block * 32, 0, st>>>(p);
+    LSVD_CUDA_TRY(launch_chained(cache_append_kernel<LSVD_ROUND_TORCH>, grid, block, 0, st, 1, true, p));
   else
-    cache_append_kernel<LSVD_ROUND_TRITON><<<static_cast<unsigned>(blocks), warps_per_block * 32, 0, st>>>(p);
-  LSVD_CUDA_TRY(cudaGetLastError());
+    LSVD_CUDA_TRY(launch_chained(cache_append_kernel<LSVD_ROUND_TRITON>, grid, block, 0, st, 1, true, p));
   return LSVD_OK;
 }

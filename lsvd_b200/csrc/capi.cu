@@ -1,4 +1,5 @@
 // Status strings, device queries and other host-side plumbing shared by the entry points.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -31,6 +32,14 @@ static const DeviceInfo* current_device_info() {
   if (cudaDeviceGetAttribute(&info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
     return nullptr;
   return &(g_devices[dev] = info);
+}
+
+bool chained_launch_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LSVD_CHAINED_LAUNCH");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
 }
 
 int device_sm_count() {

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/lsvd_b200.h"
 
 namespace lsvd {
@@ -29,8 +31,53 @@ int device_max_smem_optin();     // opt-in shared memory per block of the curren
 // Raise a kernel's dynamic shared memory limit on the current device (remembered, so repeated calls are free).
 cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 
+// Kernels of one decode step run back to back on a stream, each a few microseconds long.  They are launched
+// with programmatic stream serialisation: the next kernel's blocks may become resident while the previous
+// kernel drains, and wait in grid_dependency_sync() (first statement of every such kernel) until the previous
+// grid has completed and its writes are visible.  LSVD_CHAINED_LAUNCH=0 in the environment turns it off.
+// The attention kernels use it; for the FFN kernels (chain = false) it measured slower inside a whole layer step.
+bool chained_launch_enabled();
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  int cluster_x, bool chain, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (chain && chained_launch_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
+
 // ---- device side -----------------------------------------------------------------------------
 #ifdef __CUDACC__
+
+// Let the next kernel of the stream start becoming resident, then wait for the previous one to have completed
+// (both are no-ops for a kernel launched without programmatic serialisation).
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_sync() {
+  grid_dependency_release();
+  grid_dependency_wait();
+}
 
 // Record the first error code seen by a kernel; later codes do not overwrite it.
 __device__ __forceinline__ void report_status(int32_t* status_word, int code) {

@@ -13,6 +13,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "gemv.cuh"
 
 namespace lsvd {
 
@@ -56,6 +57,7 @@ __device__ __forceinline__ int8_t act_code(float x, float s) {
 __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ ActQuantParams p) {
   extern __shared__ float row[];          // cols floats
   __shared__ float red[8];
+  grid_dependency_sync();
   const int r = blockIdx.x;
   const __half* x = p.x + r * p.x_row_stride;
   if (p.vec8) {
@@ -234,6 +236,7 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
   __half* Tt = reinterpret_cast<__half*>(smem_raw);          // [ntile_per * 8][ld]: my columns of the rotated blocks
   __half* xs = Tt + p.ntile_per * 8 * p.ld;                  // [cols]: the token's row, staged with wide loads
   __shared__ float red[8];
+  grid_dependency_sync();
   __shared__ float my_max;
   const int crank = static_cast<int>(cluster_rank());
   const int r = blockIdx.x / p.cluster;
@@ -384,35 +387,14 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
 // ----------------------------------------------------------------------------------------------
 // weight-streaming W8A8 product
 // ----------------------------------------------------------------------------------------------
-struct GemvParams {
-  const int8_t* w;  int64_t w_row_stride;  const float* w_scale;
-  const int8_t* w2; int64_t w2_row_stride; const float* w2_scale;
-  const int8_t* a;  int64_t a_row_stride;  const float* a_scale;  int64_t a_scale_stride;
-  const int8_t* a2; int64_t a2_row_stride; const float* a2_scale; int64_t a2_scale_stride;
-  __half* out; int64_t out_row_stride; int32_t out_col;
-  const __half* residual; int64_t residual_row_stride;
-  int32_t* acc_out; int32_t* acc2_out;
-  int32_t m, n, k, epilogue;
-};
-
 constexpr int kGemvWarps = 8;
-
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint4 ldg_u4(const int8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 // NT = token tiles of 8 (tokens beyond m read as zero); DUAL = a gate/up pair of matrices in one pass;
 // SPLIT_B = the second matrix has its own activations.
 template <int NT, bool DUAL, bool SPLIT_B>
 __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) int red[];      // [warp][matrix][NT][4][32]
+  grid_dependency_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * 16;
@@ -503,22 +485,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
       if (DUAL) sum1 += red[wi * (NMAT * NT * 4 * 32) + NT * 4 * 32 + e];
     }
     if (tok >= p.m) continue;
-    if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = sum0;
-    if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = sum1;
-    if (p.out == nullptr) continue;
-    const float sa = p.a_scale[tok * p.a_scale_stride];
-    const __half v0 = __float2half_rn((static_cast<float>(sum0) * sa) * p.w_scale[row]);
-    __half res = v0;
-    if (DUAL) {
-      const float sb = SPLIT_B ? p.a2_scale[tok * p.a2_scale_stride] : sa;
-      const __half u = __float2half_rn((static_cast<float>(sum1) * sb) * p.w2_scale[row]);
-      // silu in fp32 rounded to fp16, then an fp16 product: how PyTorch evaluates F.silu(g) * u on fp16 tensors
-      const __half sg = __float2half_rn(silu_f(__half2float(v0)));
-      res = __float2half_rn(__half2float(sg) * __half2float(u));
-    }
-    if (p.residual != nullptr)       // fp16 add of the fp16 result and the residual, as the reference's `x @ W + residual`
-      res = __float2half_rn(__half2float(res) + __half2float(p.residual[static_cast<int64_t>(tok) * p.residual_row_stride + row]));
-    p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = res;
+    gemv_store<DUAL, SPLIT_B>(p, tok, row, sum0, sum1);
   }
 }
 
@@ -532,8 +499,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   const int smem = kGemvWarps * (DUAL ? 2 : 1) * NT * 4 * 32 * 4;
   auto kern = w8a8_gemv_kernel<NT, DUAL, SPLIT_B>;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
-  kern<<<p.n / 16, kGemvWarps * 32, smem, st>>>(p);
-  LSVD_CUDA_TRY(cudaGetLastError());
+  LSVD_CUDA_TRY(launch_chained(kern, dim3(p.n / 16), dim3(kGemvWarps * 32), smem, st, 1, false, p));
   return LSVD_OK;
 }
 
@@ -572,8 +538,7 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
             (a->q_row_stride % 8) == 0 && (a->sign == nullptr || aligned(a->sign, 16))) ? 1 : 0;
   const int smem = a->cols * 4;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(act_quant_kernel), smem));
-  act_quant_kernel<<<a->rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(p);
-  LSVD_CUDA_TRY(cudaGetLastError());
+  LSVD_CUDA_TRY(launch_chained(act_quant_kernel, dim3(a->rows), dim3(256), smem, static_cast<cudaStream_t>(stream), 1, false, p));
   return LSVD_OK;
 }
 
@@ -624,19 +589,8 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
   const int smem = (p.ntile_per * 8 * p.ld + a->cols) * 2;
   p.x_vec16 = (aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && (a->cols % 8) == 0) ? 1 : 0;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(hadamard_quant_kernel), smem));
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(a->rows * p.cluster));
-  cfg.blockDim = dim3(256);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = p.cluster;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  LSVD_CUDA_TRY(cudaLaunchKernelEx(&cfg, hadamard_quant_kernel, p));
+  LSVD_CUDA_TRY(launch_chained(hadamard_quant_kernel, dim3(static_cast<unsigned>(a->rows * p.cluster)), dim3(256), smem,
+                               static_cast<cudaStream_t>(stream), p.cluster, false, p));
   return LSVD_OK;
 }
 
@@ -662,8 +616,11 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   p.out = static_cast<__half*>(a->out); p.out_row_stride = a->out_row_stride; p.out_col = a->out_col;
   p.residual = static_cast<const __half*>(a->residual); p.residual_row_stride = a->residual_row_stride;
   p.acc_out = a->acc_out; p.acc2_out = a->acc2_out;
+  p.status_word = a->status_word;
   p.m = a->m; p.n = a->n; p.k = a->k; p.epilogue = a->epilogue;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->form == 1) return a->m <= 16 ? launch_gemv_streamed(p, dual, split, st) : LSVD_ERR_UNSUPPORTED;
+  if (a->form != 0) return LSVD_ERR_INVALID_ARG;
   if (a->m <= 8) return launch_gemv_nt<1>(p, dual, split, st);
   if (a->m <= 16) return launch_gemv_nt<2>(p, dual, split, st);
   if (a->m <= 32) return launch_gemv_nt<4>(p, dual, split, st);

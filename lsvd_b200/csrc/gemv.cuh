@@ -1,0 +1,57 @@
+// Shared by the two forms of the weight-streaming W8A8 product: parameters, the int8 MMA and the epilogue.
+#pragma once
+
+#include "common.cuh"
+
+namespace lsvd {
+
+struct GemvParams {
+  const int8_t* w;  int64_t w_row_stride;  const float* w_scale;
+  const int8_t* w2; int64_t w2_row_stride; const float* w2_scale;
+  const int8_t* a;  int64_t a_row_stride;  const float* a_scale;  int64_t a_scale_stride;
+  const int8_t* a2; int64_t a2_row_stride; const float* a2_scale; int64_t a2_scale_stride;
+  __half* out; int64_t out_row_stride; int32_t out_col;
+  const __half* residual; int64_t residual_row_stride;
+  int32_t* acc_out; int32_t* acc2_out;
+  int32_t* status_word;
+  int32_t m, n, k, epilogue;
+};
+
+// The TMA-fed persistent form (gemv_tma.cu), for at most 16 tokens.
+int launch_gemv_streamed(const GemvParams& p, bool dual, bool split, cudaStream_t st);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_u4(const int8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// Dequantise, gate, add the residual and store one element; sum1 / the second scales are used by gate/up pairs.
+template <bool DUAL, bool SPLIT_B>
+__device__ __forceinline__ void gemv_store(const GemvParams& p, int tok, int row, int sum0, int sum1) {
+  if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = sum0;
+  if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = sum1;
+  if (p.out == nullptr) return;
+  const float sa = p.a_scale[tok * p.a_scale_stride];
+  const __half v0 = __float2half_rn((static_cast<float>(sum0) * sa) * p.w_scale[row]);
+  __half res = v0;
+  if (DUAL) {
+    const float sb = SPLIT_B ? p.a2_scale[tok * p.a2_scale_stride] : sa;
+    const __half u = __float2half_rn((static_cast<float>(sum1) * sb) * p.w2_scale[row]);
+    // silu in fp32 rounded to fp16, then an fp16 product: how PyTorch evaluates F.silu(g) * u on fp16 tensors
+    const __half sg = __float2half_rn(silu_f(__half2float(v0)));
+    res = __float2half_rn(__half2float(sg) * __half2float(u));
+  }
+  if (p.residual != nullptr)       // fp16 add of the fp16 result and the residual, as the reference's `x @ W + residual`
+    res = __float2half_rn(__half2float(res) + __half2float(p.residual[static_cast<int64_t>(tok) * p.residual_row_stride + row]));
+  p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = res;
+}
+#endif
+
+}  // namespace lsvd

@@ -1,0 +1,214 @@
+// Weight-streaming W8A8 product for decode batches of at most 16 tokens, fed by TMA:
+//   acc[tok, row] = sum_k a[tok, k] * w[row, k]      (int8 x int8 -> int32 on mma.sync m16n8k32)
+//
+// A decode GEMV is a pure HBM stream, and on this part a stream only runs at full rate with on the order of
+// 100 KB in flight per SM: more than the register file can hold as load destinations.  So the loads go
+// through shared memory.  One persistent block per SM walks its share of the 16-row tiles; a producer warp
+// (one elected lane) issues tiled TMA copies (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) of the
+// next 1 KB of K of the tile's rows of every weight matrix and of the token rows into a ring of stages; eight
+// consumer warps each take one 128-byte chunk of the stage, read it with conflict-free 16-byte shared loads in
+// MMA fragment order and accumulate; after the last stage of a tile their shares are summed through shared
+// memory and dequantised while the producer already streams the next tile.  Every mbarrier wait is bounded.
+//
+// Same values as the register-fed form in ffn_decode.cu (w8a8_gemv_kernel), which serves larger batches.
+#include <algorithm>
+#include <cstdlib>
+
+#include "gemv.cuh"
+#include "tma.cuh"
+
+namespace lsvd {
+
+constexpr int kTgConsumers = 8;                       // consumer warps = 128-byte chunks of a stage
+constexpr int kTgThreads = (kTgConsumers + 1) * 32;   // + the producer warp
+constexpr int kTgStageK = kTgConsumers * 128;         // bytes of K per stage
+constexpr int kTgRows = 16;                           // weight rows per tile and matrix
+constexpr int kTgMaxStages = 12;
+
+template <int NT, bool DUAL, bool SPLIT_B>
+struct TgLayout {
+  static constexpr int kW = kTgConsumers * kTgRows * 128;               // one matrix' rows of a stage
+  static constexpr int kA = kTgConsumers * NT * 8 * 128;                // the token rows of a stage
+  static constexpr int kStage = kW * (DUAL ? 2 : 1) + kA * (SPLIT_B ? 2 : 1);
+  static constexpr int kRed = kTgConsumers * (DUAL ? 2 : 1) * NT * 4 * 32 * 4;
+};
+
+__device__ __forceinline__ uint4 lds_u4(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// Named barrier of the consumer warps only: the producer never joins it.
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTgConsumers * 32) : "memory"); }
+
+template <int NT, bool DUAL, bool SPLIT_B>
+__global__ void __launch_bounds__(kTgThreads, 1)
+w8a8_gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
+                     const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a2,
+                     const __grid_constant__ GemvParams p, const int stages) {
+  using L = TgLayout<NT, DUAL, SPLIT_B>;
+  constexpr int NMAT = DUAL ? 2 : 1;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  int* red = reinterpret_cast<int*>(ring + static_cast<size_t>(stages) * L::kStage);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(red) + L::kRed);
+  uint64_t* empty_bar = full_bar + kTgMaxStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kTgConsumers);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int tiles = p.n / kTgRows;
+  const int ksteps = (p.k + kTgStageK - 1) / kTgStageK;
+
+  if (warp == kTgConsumers) {
+    // ================= producer =================
+    if (lane == 0) {
+      // Weights do not depend on the kernel before this one; the token rows do.
+      grid_dependency_wait();
+      int it = 0;
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int row0 = tile * kTgRows;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int s = it % stages;
+          if (!mbar_wait_bounded(&empty_bar[s], ((it / stages) & 1) ^ 1)) {
+            report_status(p.status_word, LSVD_ERR_TIMEOUT);
+            return;
+          }
+          uint8_t* st = ring + static_cast<size_t>(s) * L::kStage;
+          mbar_arrive_expect_tx(&full_bar[s], L::kStage);
+          const int k0 = ks * kTgStageK;
+#pragma unroll
+          for (int c = 0; c < kTgConsumers; ++c) {
+            tma_load_2d(st + c * (kTgRows * 128), &tm_w, k0 + c * 128, row0, &full_bar[s]);
+            if (DUAL) tma_load_2d(st + L::kW + c * (kTgRows * 128), &tm_w2, k0 + c * 128, row0, &full_bar[s]);
+            tma_load_2d(st + NMAT * L::kW + c * (NT * 8 * 128), &tm_a, k0 + c * 128, 0, &full_bar[s]);
+            if (SPLIT_B) tma_load_2d(st + NMAT * L::kW + L::kA + c * (NT * 8 * 128), &tm_a2, k0 + c * 128, 0, &full_bar[s]);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ================= consumers =================
+  const int g = lane >> 2, t = lane & 3;
+  int it = 0;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    int acc[NMAT][NT][4];
+#pragma unroll
+    for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0;
+
+    for (int ks = 0; ks < ksteps; ++ks, ++it) {
+      const int s = it % stages;
+      // Only the barrier decides: a stage is filled for all consumer warps or for none, so after a timeout
+      // none of them is left waiting at the named barrier below.
+      if (!mbar_wait_bounded(&full_bar[s], (it / stages) & 1)) {
+        report_status(p.status_word, LSVD_ERR_TIMEOUT);
+        return;
+      }
+      const uint8_t* st = ring + static_cast<size_t>(s) * L::kStage;
+      const uint8_t* wc = st + warp * (kTgRows * 128);                      // this warp's 128-byte chunk: [16 rows][128]
+      const uint8_t* ac = st + NMAT * L::kW + warp * (NT * 8 * 128);        // [NT * 8 tokens][128]
+      // 128-byte swizzle: the 16-byte unit j of row r sits at unit j ^ (r & 7); rows g and g + 8 share g & 7
+#pragma unroll
+      for (int sp = 0; sp < 2; ++sp) {
+        const int unit = ((4 * sp + t) ^ g) << 4;
+        const uint4 x0 = lds_u4(wc + g * 128 + unit), x1 = lds_u4(wc + (g + 8) * 128 + unit);
+        uint4 y0 = x0, y1 = x1;
+        if (DUAL) {
+          y0 = lds_u4(wc + L::kW + g * 128 + unit);
+          y1 = lds_u4(wc + L::kW + (g + 8) * 128 + unit);
+        }
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const uint4 bv = lds_u4(ac + (j * 8 + g) * 128 + unit);
+          // the MMA's k index is a permutation of the 32 columns that A and B share: k 4t..4t+3 <-> the first
+          // four of a lane's bytes, k 16+4t.. <-> the next four
+          mma_s8(acc[0][j], x0.x, x1.x, x0.y, x1.y, bv.x, bv.y);
+          mma_s8(acc[0][j], x0.z, x1.z, x0.w, x1.w, bv.z, bv.w);
+          if (DUAL) {
+            uint4 bw = bv;
+            if (SPLIT_B) bw = lds_u4(ac + L::kA + (j * 8 + g) * 128 + unit);
+            mma_s8(acc[NMAT - 1][j], y0.x, y1.x, y0.y, y1.y, bw.x, bw.y);
+            mma_s8(acc[NMAT - 1][j], y0.z, y1.z, y0.w, y1.w, bw.z, bw.w);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+
+    // ---- sum the warps' shares, dequantise, store ----
+    int* mine = red + warp * (NMAT * NT * 4 * 32);
+#pragma unroll
+    for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mine[((mtx * NT + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
+    consumer_sync();
+    const int row0 = tile * kTgRows;
+    // element e of a matrix: (j, c, lane) -> row = g + 8 (c >> 1), token = 8 j + 2 t + (c & 1)
+    for (int e = threadIdx.x; e < NT * 4 * 32; e += kTgConsumers * 32) {
+      const int el = e & 31, c = (e >> 5) & 3, j = e >> 7;
+      const int row = row0 + (el >> 2) + 8 * (c >> 1);
+      const int tok = j * 8 + 2 * (el & 3) + (c & 1);
+      int sum0 = 0, sum1 = 0;
+#pragma unroll
+      for (int wi = 0; wi < kTgConsumers; ++wi) {
+        sum0 += red[wi * (NMAT * NT * 4 * 32) + e];
+        if (DUAL) sum1 += red[wi * (NMAT * NT * 4 * 32) + NT * 4 * 32 + e];
+      }
+      if (tok < p.m) gemv_store<DUAL, SPLIT_B>(p, tok, row, sum0, sum1);
+    }
+    consumer_sync();                   // the shares are read before the next tile overwrites them
+  }
+}
+
+template <int NT, bool DUAL, bool SPLIT_B>
+static int launch_tg(const GemvParams& p, cudaStream_t st) {
+  using L = TgLayout<NT, DUAL, SPLIT_B>;
+  CUtensorMap mw, mw2, ma, ma2;
+  int rc = make_map_k128(&mw, p.w, p.n, p.k, p.w_row_stride, kTgRows);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&mw2, DUAL ? p.w2 : p.w, p.n, p.k, DUAL ? p.w2_row_stride : p.w_row_stride, kTgRows);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&ma, p.a, p.m, p.k, p.a_row_stride, NT * 8);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&ma2, SPLIT_B ? p.a2 : p.a, p.m, p.k, SPLIT_B ? p.a2_row_stride : p.a_row_stride, NT * 8);
+  if (rc != LSVD_OK) return rc;
+  const int fixed = 1024 /*alignment*/ + L::kRed + 2 * kTgMaxStages * 8 + 16;
+  const int budget = device_max_smem_optin() - 4096;
+  int stages = (budget - fixed) / L::kStage;
+  const int ksteps = (p.k + kTgStageK - 1) / kTgStageK;
+  const int tiles = p.n / kTgRows;
+  const int sms = std::max(1, device_sm_count());
+  const int grid = std::min(tiles, sms);
+  const int per_block = ((tiles + grid - 1) / grid) * ksteps;      // stages a block ever fills
+  stages = std::max(1, std::min(std::min(stages, kTgMaxStages), per_block));
+  if (stages < 1 || fixed + L::kStage > budget) return LSVD_ERR_UNSUPPORTED;
+  const int smem = fixed + stages * L::kStage;
+  auto kern = w8a8_gemv_tma_kernel<NT, DUAL, SPLIT_B>;
+  LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
+  LSVD_CUDA_TRY(launch_chained(kern, dim3(grid), dim3(kTgThreads), smem, st, 1, false, mw, mw2, ma, ma2, p, stages));
+  return LSVD_OK;
+}
+
+int launch_gemv_streamed(const GemvParams& p, bool dual, bool split, cudaStream_t st) {
+  if (p.m <= 8) {
+    if (!dual) return launch_tg<1, false, false>(p, st);
+    return split ? launch_tg<1, true, true>(p, st) : launch_tg<1, true, false>(p, st);
+  }
+  if (!dual) return launch_tg<2, false, false>(p, st);
+  return split ? launch_tg<2, true, true>(p, st) : launch_tg<2, true, false>(p, st);
+}
+
+}  // namespace lsvd

@@ -111,9 +111,11 @@ def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rot
 
 
 def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a2_scale=None, out=None, out_col=0,
-              want_acc=False, want_out=True, residual=None):
+              want_acc=False, want_out=True, residual=None, form=0, status_word=None):
     """acc = a_q @ w_q^T (int32, exact) for 1..64 tokens, dequantised to fp16; with (w2, a2) a gate/up pair whose
-    result is silu(gate) * up.  Returns (out fp16 [m, n] or the passed tensor, acc int32 or None, acc2 or None)."""
+    result is silu(gate) * up.  Returns (out fp16 [m, n] or the passed tensor, acc int32 or None, acc2 or None).
+    ``form`` 0 is the register-fed kernel, 1 the persistent TMA-fed one (at most 16 tokens); ``status_word`` (int32
+    device tensor) receives LSVD_ERR_TIMEOUT if a pipeline wait of form 1 gives up."""
     _require_cuda(a_q, w_q)
     m, k = a_q.shape
     n = w_q.shape[0]
@@ -139,6 +141,7 @@ def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a
     g.acc_out, g.acc2_out = _ptr(acc), _ptr(acc2)
     if residual is not None:
         g.residual, g.residual_row_stride = residual.data_ptr(), residual.stride(0)
+    g.form, g.status_word = form, _ptr(status_word)
     _lib.check(_lib.load().lsvd_w8a8_gemv(C.byref(g), _stream_ptr(a_q)))
     return out, acc, acc2
 

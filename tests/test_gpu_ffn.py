@@ -127,6 +127,41 @@ def test_gemv_shapes_dual_and_down(m, n, k, split):
     assert (d == 0).float().mean() > 0.999 and d.max() <= 2 ** -10 * h_ref.float().abs().max()
 
 
+@pytest.mark.parametrize("m,n,k,kind", [(1, 1024, 4096, "single"), (16, 4096, 11008, "single"), (5, 48, 1376 + 16, "single"),
+                                        (16, 5504, 4096, "dual"), (9, 688, 4096, "dual"), (16, 5504, 512, "split"),
+                                        (3, 64, 48, "split")])
+def test_gemv_tma_form_equals_register_form(m, n, k, kind):
+    """form 1 (persistent, TMA-fed, at most 16 tokens) against form 0 and the oracle: same integers, same fp16."""
+    gen = torch.Generator().manual_seed(m * 11 + n + k)
+    a = torch.randint(-128, 128, (m, k), generator=gen, dtype=torch.int8).cuda()
+    w = torch.randint(-128, 128, (n, k), generator=gen, dtype=torch.int8).cuda()
+    sa = (torch.rand(m, generator=gen) * 0.02 + 1e-3).cuda()
+    sw = (torch.rand(n, generator=gen) * 0.002 + 1e-4).cuda()
+    kw = {}
+    if kind != "single":
+        kw["w2_q"] = torch.randint(-128, 128, (n, k), generator=gen, dtype=torch.int8).cuda()
+        kw["w2_scale"] = (torch.rand(n, generator=gen) * 0.002 + 1e-4).cuda()
+    if kind == "split":
+        kw["a2_q"] = torch.randint(-128, 128, (m, k), generator=gen, dtype=torch.int8).cuda()
+        kw["a2_scale"] = (torch.rand(m, generator=gen) * 0.02 + 1e-3).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o0, acc0, acc0b = w8a8_gemv(a, sa, w, sw, want_acc=True, form=0, **kw)
+    o1, acc1, acc1b = w8a8_gemv(a, sa, w, sw, want_acc=True, form=1, status_word=status, **kw)
+    assert int(status.item()) == 0
+    assert torch.equal(acc1.cpu(), offn._i32_matmul(a.cpu(), w.cpu()))
+    assert torch.equal(acc0, acc1) and torch.equal(o0, o1)
+    if kind != "single":
+        assert torch.equal(acc0b, acc1b)
+
+
+def test_gemv_tma_form_rejects_large_batches():
+    a = torch.zeros(17, 64, dtype=torch.int8, device="cuda")
+    w = torch.zeros(16, 64, dtype=torch.int8, device="cuda")
+    s = torch.ones(17, device="cuda")
+    with pytest.raises(ValueError):
+        w8a8_gemv(a, s, w, s[:16].contiguous(), form=1)
+
+
 def _golden_weights(g):
     K = g["K"]
     return {"had_sign": None, "K": K, "had_K": unpack_had(g["had_bits"], K),
