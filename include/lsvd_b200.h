@@ -163,6 +163,52 @@ size_t lsvd_attn_decode_static_scratch_bytes(void);
 int lsvd_attn_decode_static(const lsvd_attn_decode_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Decode attention in the reference's own form ("rope_recon"): int8 K up-factor, keys rebuilt per token and
+ * rotated at their logical position, uniform ranks, grouped-query heads.  Replaces
+ * token_decode_attention_flash_int8_latent_per_head_decoding_rope (kernels/layer_bench/fd_kernel/flash_decoding.py:3-57),
+ * i.e. stage 1 (flash_int8_latent_per_head_decoding_rope_stage1.py:32-250) + stage 2
+ * (flash_latent_per_head_decoding_stage2.py:7-69):
+ *   K_t = fp16((z_k[t] . wk) * scale_k[t] * wk_scale), rotated at position t; q rotated at position L - 1 (fp16);
+ *   o[b, h, :] = sum_t softmax_t(q_rot . K_rot / sqrt(D)) * scale_v[t] * z_v[t]       fp16 [B, H, rank_v]
+ * The kv head of query head h is h / (num_q_heads / num_kv_heads).  A request of length 0 gets zeros.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lsvd_attn_rope_args {
+  int32_t batch, num_q_heads, num_kv_heads;
+  int32_t head_dim;              /* 32, 64 or 128                                                                 */
+  int32_t rank_k, rank_v;        /* multiples of 16, <= LSVD_MAX_RANK                                            */
+  const void* q;                 /* device fp16 (b, h, d) at q[b*q_stride_b + h*q_stride_h + d]                  */
+  int64_t q_stride_b, q_stride_h;
+  const int8_t* cache_k;         /* device int8 (slot, kv head, rank) at slot*slot_stride + head*head_stride + r */
+  int64_t cache_k_slot_stride, cache_k_head_stride;
+  const void* scale_k;           /* device fp16 (slot, kv head) at slot*scale_k_slot_stride + head               */
+  int64_t scale_k_slot_stride;
+  const int8_t* cache_v;
+  int64_t cache_v_slot_stride, cache_v_head_stride;
+  const void* scale_v;
+  int64_t scale_v_slot_stride;
+  const int8_t* wk;              /* device int8 [rank_k, num_kv_heads*head_dim], rows 16-byte aligned            */
+  int64_t wk_row_stride;
+  const void* wk_scale;          /* device fp16 [num_kv_heads*head_dim]                                          */
+  const int32_t* req_to_token;   /* device int32 [requests, >= max_len_in_batch]                                 */
+  int64_t req_to_token_stride;
+  const int32_t* b_req_idx;      /* device int32 [batch]                                                         */
+  const int32_t* b_seq_len;      /* device int32 [batch]                                                         */
+  int32_t num_slots;
+  int32_t max_len_in_batch;
+  int32_t block_seq;             /* tokens per run (the reference's BLOCK_SEQ, 256); multiple of 16              */
+  float sm_scale;                /* <= 0: 1 / sqrt(head_dim)                                                     */
+  float rope_theta;              /* <= 0: 10000                                                                  */
+  void* out;                     /* device fp16 (b, h, rank_v) at out[b*out_stride_b + h*out_stride_h + i]       */
+  int64_t out_stride_b, out_stride_h;
+  void* workspace;               /* device, 256-byte aligned                                                     */
+  size_t workspace_bytes;
+  int32_t* status_word;          /* device int32 or NULL                                                         */
+} lsvd_attn_rope_args;
+size_t lsvd_attn_decode_rope_workspace_bytes(int32_t batch, int32_t num_q_heads, int32_t head_dim, int32_t rank_v,
+                                             int32_t max_len_in_batch, int32_t block_seq);
+int lsvd_attn_decode_rope(const lsvd_attn_rope_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Hybrid SVD/RTN FFN, decode (1..64 tokens): building blocks and the fused chain.
  * Semantics follow fake_quant/utils/hybrid_ffn_utils.py:956-984 (HybridSVDQuantFFN.forward) with real
  * int8 codes: activations are quantised per token (fake_quant/utils/quant_utils.py:201-212,30-33),

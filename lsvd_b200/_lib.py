@@ -60,6 +60,25 @@ class AttnDecodeArgs(C.Structure):
     ]
 
 
+class AttnRopeArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("rank_k", C.c_int32), ("rank_v", C.c_int32),
+        ("q", C.c_void_p), ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64),
+        ("cache_k", C.c_void_p), ("cache_k_slot_stride", C.c_int64), ("cache_k_head_stride", C.c_int64),
+        ("scale_k", C.c_void_p), ("scale_k_slot_stride", C.c_int64),
+        ("cache_v", C.c_void_p), ("cache_v_slot_stride", C.c_int64), ("cache_v_head_stride", C.c_int64),
+        ("scale_v", C.c_void_p), ("scale_v_slot_stride", C.c_int64),
+        ("wk", C.c_void_p), ("wk_row_stride", C.c_int64), ("wk_scale", C.c_void_p),
+        ("req_to_token", C.c_void_p), ("req_to_token_stride", C.c_int64),
+        ("b_req_idx", C.c_void_p), ("b_seq_len", C.c_void_p),
+        ("num_slots", C.c_int32), ("max_len_in_batch", C.c_int32), ("block_seq", C.c_int32),
+        ("sm_scale", C.c_float), ("rope_theta", C.c_float),
+        ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status_word", C.c_void_p),
+    ]
+
+
 class ActQuantArgs(C.Structure):
     _fields_ = [
         ("rows", C.c_int32), ("cols", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
@@ -109,6 +128,8 @@ SIGNATURES = {
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_static_scratch_bytes": (C.c_size_t, []),
     "lsvd_attn_decode_static": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
+    "lsvd_attn_decode_rope_workspace_bytes": (C.c_size_t, [C.c_int32] * 6),
+    "lsvd_attn_decode_rope": (C.c_int, [C.POINTER(AttnRopeArgs), C.c_void_p]),
     "lsvd_act_quant": (C.c_int, [C.POINTER(ActQuantArgs), C.c_void_p]),
     "lsvd_hadamard_quant": (C.c_int, [C.POINTER(HadamardQuantArgs), C.c_void_p]),
     "lsvd_hadamard_packed_bytes": (C.c_size_t, [C.c_int32]),

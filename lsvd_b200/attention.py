@@ -324,3 +324,64 @@ class LatentDecodeAttention(nn.Module):
         return token_decode_attention_int8_latent_absorb(
             q, infer_state, self.layout.num_heads, self.head_dim, cache_k, scale_k, cache_v, scale_v,
             self.up_k, self.up_v, layout=self.layout, out=out, workspace=ws)
+
+
+@torch.no_grad()
+def token_decode_attention_flash_int8_latent_per_head_decoding_rope(
+        q, infer_state, q_head_num: int, head_dim: int,
+        cache_latent_k, cache_latent_k_scale, cache_latent_v, cache_latent_v_scale, wk, wk_scale,
+        out=None, alloc_tensor_func=torch.empty, block_seq: int = 256, rope_theta: float = 10000.0,
+        sm_scale: Optional[float] = None, workspace=None, status_word=None):
+    """The reference's decode attention under its own name and argument list
+    (kernels/layer_bench/fd_kernel/flash_decoding.py:3-17): int8 K up-factor ``wk [R_k, H_kv*D]`` with fp16 column
+    scales ``wk_scale [1, H_kv*D]``, keys rebuilt and rotated per token, caches ``[N, H_kv, R]`` int8 with scales
+    ``[N, H_kv]`` fp16, grouped-query heads when ``H_kv < q_head_num``.  Returns ``o [B, H, R_v]`` fp16 in the value
+    latent space, as the reference does.  ``alloc_tensor_func`` provides the output and the workspace."""
+    _require_cuda(q, cache_latent_k, cache_latent_v, wk)
+    lib = _lib.load()
+    B = infer_state.batch_size
+    if cache_latent_k.dim() != 3 or cache_latent_v.dim() != 3:
+        raise ValueError("latent caches must be [N, H_kv, R]")
+    if q.dtype != torch.float16 or wk.dtype != torch.int8 or wk_scale.dtype != torch.float16:
+        raise ValueError("q fp16, wk int8 and wk_scale fp16 are expected")
+    N, Hkv, Rk = cache_latent_k.shape
+    Rv = cache_latent_v.shape[-1]
+    if q_head_num % Hkv:
+        raise ValueError("q_head_num must be a multiple of the number of kv heads")
+    if tuple(wk.shape) != (Rk, Hkv * head_dim) or wk_scale.numel() != Hkv * head_dim:
+        raise ValueError("wk must be [R_k, H_kv*D] and wk_scale [1, H_kv*D]")
+    q = q.view(B, q_head_num, head_dim)
+    if q.stride(2) != 1:
+        q = q.contiguous()
+    for t in (cache_latent_k, cache_latent_v):
+        if t.stride(2) != 1:
+            raise ValueError("the rank dimension of the caches must be contiguous")
+    if cache_latent_k_scale.stride(-1) != 1 or cache_latent_v_scale.stride(-1) != 1 or wk.stride(1) != 1:
+        raise ValueError("scales and wk must have unit inner stride")
+    dev = q.device
+    if out is None:
+        out = alloc_tensor_func((B, q_head_num, Rv), dtype=torch.float16, device=dev)
+    max_len = int(infer_state.max_len_in_batch)
+    need = lib.lsvd_attn_decode_rope_workspace_bytes(B, q_head_num, head_dim, Rv, max_len, block_seq)
+    if workspace is None:
+        workspace = alloc_tensor_func((max(need, 256),), dtype=torch.uint8, device=dev)
+    r2t = infer_state.req_manager.req_to_token_indexs
+    wk_scale = wk_scale.reshape(-1)
+    a = _lib.AttnRopeArgs()
+    a.batch, a.num_q_heads, a.num_kv_heads, a.head_dim, a.rank_k, a.rank_v = B, q_head_num, Hkv, head_dim, Rk, Rv
+    a.q, a.q_stride_b, a.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    a.cache_k, a.cache_k_slot_stride, a.cache_k_head_stride = cache_latent_k.data_ptr(), cache_latent_k.stride(0), cache_latent_k.stride(1)
+    a.scale_k, a.scale_k_slot_stride = cache_latent_k_scale.data_ptr(), cache_latent_k_scale.stride(0)
+    a.cache_v, a.cache_v_slot_stride, a.cache_v_head_stride = cache_latent_v.data_ptr(), cache_latent_v.stride(0), cache_latent_v.stride(1)
+    a.scale_v, a.scale_v_slot_stride = cache_latent_v_scale.data_ptr(), cache_latent_v_scale.stride(0)
+    a.wk, a.wk_row_stride, a.wk_scale = wk.data_ptr(), wk.stride(0), wk_scale.data_ptr()
+    a.req_to_token, a.req_to_token_stride = r2t.data_ptr(), r2t.stride(0)
+    a.b_req_idx, a.b_seq_len = infer_state.b_req_idx.data_ptr(), infer_state.b_seq_len.data_ptr()
+    a.num_slots, a.max_len_in_batch, a.block_seq = N, max_len, block_seq
+    a.sm_scale = float(sm_scale) if sm_scale is not None else 0.0
+    a.rope_theta = float(rope_theta)
+    a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    a.status_word = status_word.data_ptr() if status_word is not None else None
+    _lib.check(lib.lsvd_attn_decode_rope(C.byref(a), _stream_ptr(q)))
+    return out
