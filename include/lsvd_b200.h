@@ -305,6 +305,12 @@ typedef struct lsvd_i8gemm_args {
   int32_t out_col;
   int32_t* acc_out;              /* optional device int32 [m, n] (single product only)                */
   int32_t* status_word;          /* device int32 or NULL: LSVD_ERR_TIMEOUT if a bounded wait gave up  */
+  int64_t a_scale_stride;        /* elements between the scales of consecutive rows; 0 means 1        */
+  const void* gate;              /* single product only, optional device fp16: the result becomes      */
+  int64_t gate_row_stride;       /*   fp16(fp16(silu(gate[m, gate_col + n])) * value)  (an "up" product */
+  int32_t gate_col;              /*   whose gate was computed before, with other activations)          */
+  const void* residual;          /* single product only, optional device fp16 [m, n]: fp16 add         */
+  int64_t residual_row_stride;
 } lsvd_i8gemm_args;
 int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* args, void* stream);
 

@@ -115,6 +115,8 @@ class I8GemmArgs(C.Structure):
         ("w2", C.c_void_p), ("w2_row_stride", C.c_int64), ("w2_scale", C.c_void_p),
         ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("out_col", C.c_int32),
         ("acc_out", C.c_void_p), ("status_word", C.c_void_p),
+        ("a_scale_stride", C.c_int64), ("gate", C.c_void_p), ("gate_row_stride", C.c_int64), ("gate_col", C.c_int32),
+        ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
     ]
 
 

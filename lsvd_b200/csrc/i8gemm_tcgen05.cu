@@ -1,50 +1,54 @@
 // W8A8 GEMM for prefill and large batches on the fifth-generation tensor cores:
 //   acc[m, n] = sum_k a[m, k] * w[n, k]   (int8 x int8 -> int32, exact), dequantised to fp16 in the epilogue.
 //
-// One thread block computes a 128 (tokens) x 256 (channels) tile.  Warp 0 (one elected lane) streams the A and B
-// tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a four-stage shared-memory ring;
-// warp 1 (one elected lane) issues tcgen05.mma kind::i8 (M 128, N 256, K 32 per instruction) whose accumulator
-// lives in tensor memory (256 columns of 32 bits, allocated by warp 1); tcgen05.commit hands each ring stage
-// back to the producer and finally signals the four epilogue warps, which read the accumulator with
-// tcgen05.ld (lane = token row, 32 columns at a time), apply token and channel scales (and SiLU gating for a
-// gate/up pair) and store fp16.  Every mbarrier wait is bounded; a wait that gives up sets the status word and
-// the block still releases its tensor memory.
+// Persistent: one block per SM walks 128 (tokens) x 256 (channels) tiles.  Warp 0 (one elected lane) streams the
+// A and B tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a four-stage shared-memory
+// ring; warp 1 (one elected lane) issues tcgen05.mma kind::i8 (M 128, N 256, K 32 per instruction) into one of
+// two accumulators in tensor memory (2 x 256 columns of 32 bits, allocated by warp 1); tcgen05.commit hands each
+// ring stage back to the producer and, after a tile's last MMA, hands the accumulator to the eight epilogue warps,
+// which read it with tcgen05.ld (lane = token row, 32 columns at a time), apply token and channel scales (and
+// SiLU gating / a residual) and store fp16 while the MMAs of the next tile fill the other accumulator.  Every
+// mbarrier wait is bounded; a wait that gives up sets the status word and the block still releases its tensor
+// memory.
 //
 // Replaces the Triton tl.dot int8 kernels of the reference for M >> 64
 // (kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:410-500, 903-1021, 1152-1338) and produces the same values as
 // the decode-sized lsvd_w8a8_gemv.
-#include <cuda.h>
-
+#include <algorithm>
 #include <cmath>
-#include <mutex>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace lsvd {
 
 constexpr int kBM = 128, kBN = 256, kBK = 128, kStages = 4;
 constexpr int kATile = kBM * kBK, kBTile = kBN * kBK;                     // bytes (int8)
-constexpr int kGemmThreads = 192;                                          // producer, MMA issuer, four epilogue warps
-constexpr int kGemmSmem = kStages * (kATile + kBTile) + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr uint32_t kTmemCols = 256;
+constexpr int kEpiWarps = 8;                                               // two per quarter of the TMEM lanes
+constexpr int kGemmThreads = 64 + kEpiWarps * 32;                          // producer, MMA issuer, epilogue warps
+constexpr int kGemmSmem = kStages * (kATile + kBTile) + 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * kBN * 4 /*scales*/;
+constexpr uint32_t kTmemCols = 512;                                        // two accumulators of kBN columns
 
 struct GemmParams {
   const float* a_scale;
+  int64_t a_scale_stride;
   const float* w_scale;
   const float* w2_scale;
   __half* out;
   int64_t out_row_stride;
   int32_t out_col;
+  const __half* gate;        // epilogue of a lone "up" product: out = fp16(fp16(silu(gate)) * value)
+  int64_t gate_row_stride;
+  int32_t gate_col;
+  const __half* residual;    // fp16 add of the fp16 result and the residual (single product)
+  int64_t residual_row_stride;
   int32_t* acc_out;          // optional raw accumulators [m, n] (single-matrix form only)
   int32_t* status_word;
   int32_t m, n, k, dual;     // dual: the B tile is 128 gate channels followed by their 128 up channels
+  int32_t m_tiles, n_tiles;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -89,6 +93,16 @@ constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<ui
 
 __device__ __forceinline__ float silu_pf(float g) { return g / (1.0f + expf(-g)); }
 
+// Eight consecutive fp16 values: one 16-byte load when the address allows it.
+__device__ __forceinline__ void load8_halves(__half (&dst)[8], const __half* src) {
+  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dst[e] = src[e];
+  }
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
 i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ GemmParams p) {
@@ -98,21 +112,26 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   uint8_t* sB = tiles + kStages * kATile;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + kStages * (kATile + kBTile));
   uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* acc_bar = empty_bar + kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  uint64_t* acc_full = empty_bar + kStages;        // [2] accumulator ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;              // [2] accumulator drained by the epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* col_scale = reinterpret_cast<float*>(tmem_slot + 4);       // [2][kBN] channel scales of the tiles in flight
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM;
-  const int n0 = blockIdx.x * (p.dual ? kBN / 2 : kBN);       // first channel of the tile (per matrix when dual)
   const int kiters = (p.k + kBK - 1) / kBK;
+  const int ntile_cols = p.dual ? kBN / 2 : kBN;   // channels per tile (per matrix when dual)
+  const int total_tiles = p.m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], kEpiWarps);
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -122,113 +141,177 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Tiles in channel-fastest order: the blocks that run together share a few token tiles and all weight tiles.
   if (warp == 0) {
     if (lane == 0) {
       // ================= TMA producer =================
-      for (int it = 0; it < kiters; ++it) {
-        const int s = it % kStages;
-        if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) {
-          report_status(p.status_word, LSVD_ERR_TIMEOUT);
-          *abort_flag = 1;
-          break;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int m0 = (tile / p.n_tiles) * kBM, n0 = (tile % p.n_tiles) * ntile_cols;
+        for (int kk = 0; kk < kiters; ++kk, ++it) {
+          const int s = it % kStages;
+          if (*abort_flag || !mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) {
+            report_status(p.status_word, LSVD_ERR_TIMEOUT);
+            *abort_flag = 1;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_bar[s], kATile + kBTile);
+          tma_load_2d(sA + s * kATile, &tm_a, kk * kBK, m0, &full_bar[s]);
+          if (p.dual) {
+            tma_load_2d(sB + s * kBTile, &tm_b, kk * kBK, n0, &full_bar[s]);
+            tma_load_2d(sB + s * kBTile + kBTile / 2, &tm_b2, kk * kBK, n0, &full_bar[s]);
+          } else {
+            tma_load_2d(sB + s * kBTile, &tm_b, kk * kBK, n0, &full_bar[s]);
+            tma_load_2d(sB + s * kBTile + kBTile / 2, &tm_b, kk * kBK, n0 + kBN / 2, &full_bar[s]);
+          }
         }
-        mbar_arrive_expect_tx(&full_bar[s], kATile + kBTile);
-        tma_load_2d(sA + s * kATile, &tm_a, it * kBK, m0, &full_bar[s]);
-        if (p.dual) {
-          tma_load_2d(sB + s * kBTile, &tm_b, it * kBK, n0, &full_bar[s]);
-          tma_load_2d(sB + s * kBTile + kBTile / 2, &tm_b2, it * kBK, n0, &full_bar[s]);
-        } else {
-          tma_load_2d(sB + s * kBTile, &tm_b, it * kBK, n0, &full_bar[s]);
-          tma_load_2d(sB + s * kBTile + kBTile / 2, &tm_b, it * kBK, n0 + kBN / 2, &full_bar[s]);
-        }
+        if (*abort_flag) break;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ================= MMA issuer =================
-      bool ok = true;
-      for (int it = 0; it < kiters && ok; ++it) {
-        const int s = it % kStages;
-        if (*abort_flag || !mbar_wait_bounded(&full_bar[s], (it / kStages) & 1)) {
+      int it = 0, li = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++li) {
+        const int buf = li & 1;
+        if (!mbar_wait_bounded(&acc_empty[buf], ((li >> 1) & 1) ^ 1)) {
           report_status(p.status_word, LSVD_ERR_TIMEOUT);
           *abort_flag = 1;
-          ok = false;
           break;
         }
         tc_fence_after();
-        const uint64_t adesc = smem_desc_k_major_sw128(sA + s * kATile);
-        const uint64_t bdesc = smem_desc_k_major_sw128(sB + s * kBTile);
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kBN);
+        for (int kk = 0; kk < kiters; ++kk, ++it) {
+          const int s = it % kStages;
+          if (*abort_flag || !mbar_wait_bounded(&full_bar[s], (it / kStages) & 1)) {
+            report_status(p.status_word, LSVD_ERR_TIMEOUT);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = smem_desc_k_major_sw128(sA + s * kATile);
+          const uint64_t bdesc = smem_desc_k_major_sw128(sB + s * kBTile);
 #pragma unroll
-        for (int kk = 0; kk < kBK / 32; ++kk)        // 32 int8 of K per instruction: 32 bytes further inside the swizzled row
-          umma_i8(tmem_base, adesc + static_cast<uint64_t>(kk * 32 >> 4), bdesc + static_cast<uint64_t>(kk * 32 >> 4), kIdesc,
-                  (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&empty_bar[s]);                  // the stage is free once these MMAs have read it
+          for (int q = 0; q < kBK / 32; ++q)         // 32 int8 of K per instruction: 32 bytes further inside the swizzled row
+            umma_i8(tmem_d, adesc + static_cast<uint64_t>(q * 32 >> 4), bdesc + static_cast<uint64_t>(q * 32 >> 4), kIdesc,
+                    (kk > 0 || q > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
+        }
+        umma_commit(&acc_full[buf]);                 // arrives when every MMA above has finished (also after an abort)
       }
-      umma_commit(acc_bar);                          // arrives when every MMA above has finished (also after an abort)
     }
   } else {
-    // ================= epilogue: warps 2..5, TMEM lanes 32 * (warp % 4) .. + 31 =================
+    // ================= epilogue: warps 2..9; a warp reads the TMEM lanes 32 * (warp % 4) .. + 31, and the two
+    // warps of a quarter take alternate 32-column chunks =================
     const int quarter = warp & 3;
-    const bool ok = mbar_wait_bounded(acc_bar, 0) && *abort_flag == 0;
-    if (!ok) report_status(p.status_word, LSVD_ERR_TIMEOUT);
-    tc_fence_after();
-    const int row = m0 + quarter * 32 + lane;
-    const float sa = (ok && row < p.m) ? p.a_scale[row] : 0.f;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    if (ok) {
-      if (!p.dual) {
-#pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + c * 32, v);
-          const int col0 = n0 + c * 32;
-          if (row < p.m) {
+    const int half_id = (warp - 2) >> 2;             // 0 or 1: which of the quarter's two warps
+    const int et = threadIdx.x - 64;                 // 0..255 among the epilogue threads
+    int li = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++li) {
+      const int buf = li & 1;
+      const int m0 = (tile / p.n_tiles) * kBM, n0 = (tile % p.n_tiles) * ntile_cols;
+      // Channel scales of the tile, in accumulator column order, staged once per tile: the inner loops then
+      // read them from shared memory instead of waiting on global loads value by value.
+      float* cs = col_scale + buf * kBN;
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const int col = col0 + j;
-              if (col < p.n) {        // n is even: a pair is inside or outside together
-                if (p.acc_out != nullptr) {
-                  p.acc_out[static_cast<int64_t>(row) * p.n + col] = static_cast<int>(v[j]);
-                  p.acc_out[static_cast<int64_t>(row) * p.n + col + 1] = static_cast<int>(v[j + 1]);
-                }
-                if (p.out != nullptr) {
-                  const float f0 = (static_cast<float>(static_cast<int>(v[j])) * sa) * p.w_scale[col];
-                  const float f1 = (static_cast<float>(static_cast<int>(v[j + 1])) * sa) * p.w_scale[col + 1];
-                  *reinterpret_cast<__half2*>(p.out + static_cast<int64_t>(row) * p.out_row_stride + p.out_col + col) =
-                      __floats2half2_rn(f0, f1);
-                }
-              }
-            }
+      for (int i = et; i < kBN; i += kEpiWarps * 32) {
+        float v = 0.f;
+        if (p.dual) {
+          const int col = n0 + (i & (kBN / 2 - 1));
+          if (col < p.n) v = (i < kBN / 2) ? p.w_scale[col] : p.w2_scale[col];
+        } else if (n0 + i < p.n) {
+          v = p.w_scale[n0 + i];
+        }
+        cs[i] = v;
+      }
+      // Only the barrier decides whether to go on: it completes for all epilogue warps or for none, so none of them
+      // is left alone at the named barrier below.
+      if (!mbar_wait_bounded(&acc_full[buf], (li >> 1) & 1)) {
+        report_status(p.status_word, LSVD_ERR_TIMEOUT);
+        *abort_flag = 1;
+        break;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");   // the staged scales are visible; tile li - 2's readers are done
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const float sa = row_ok ? p.a_scale[row * p.a_scale_stride] : 0.f;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * kBN);
+      __half* orow = p.out != nullptr ? p.out + static_cast<int64_t>(row) * p.out_row_stride + p.out_col : nullptr;
+      const __half* grow = p.gate != nullptr ? p.gate + static_cast<int64_t>(row) * p.gate_row_stride + p.gate_col : nullptr;
+      const __half* rrow = p.residual != nullptr ? p.residual + static_cast<int64_t>(row) * p.residual_row_stride : nullptr;
+      const int chunks = p.dual ? kBN / 64 : kBN / 32;
+      // Gate / residual values come from DRAM with a row per lane: the 64 bytes a lane needs for a chunk of 32
+      // channels are requested together, before the accumulator is read.
+      uint4 gq[4], rq[4];
+      auto fetch_side = [&](int c) {
+        const int col0 = n0 + c * 32;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          gq[q] = rq[q] = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok && col0 + q * 8 < p.n) {
+            if (grow != nullptr) load8_halves(reinterpret_cast<__half(&)[8]>(gq[q]), grow + col0 + q * 8);
+            if (rrow != nullptr) load8_halves(reinterpret_cast<__half(&)[8]>(rq[q]), rrow + col0 + q * 8);
           }
         }
-      } else {
-        // columns 0..127: gate channels n0.., columns 128..255: the same channels of the up matrix
+      };
+      const bool side = grow != nullptr || rrow != nullptr;
 #pragma unroll 1
-        for (int c = 0; c < kBN / 64; ++c) {
-          uint32_t gv[32], uv[32];
-          tmem_ld32(lane_addr + c * 32, gv);
-          tmem_ld32(lane_addr + kBN / 2 + c * 32, uv);
-          const int col0 = n0 + c * 32;
-          if (row < p.m) {
+      for (int c = half_id; c < chunks; c += 2) {
+        uint32_t v[32], u[32];
+        if (side) fetch_side(c);
+        __syncwarp();
+        tmem_ld32(lane_addr + c * 32, v);
+        if (p.dual) tmem_ld32(lane_addr + kBN / 2 + c * 32, u);
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.n) continue;
+        if (p.acc_out != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const int col = col0 + j;
-              if (col < p.n) {
-                float h[2];
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.n) p.acc_out[static_cast<int64_t>(row) * p.n + col0 + j] = static_cast<int>(v[j]);
+        }
+        if (orow == nullptr) continue;
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const __half g16 = __float2half_rn((static_cast<float>(static_cast<int>(gv[j + e])) * sa) * p.w_scale[col + e]);
-                  const __half u16 = __float2half_rn((static_cast<float>(static_cast<int>(uv[j + e])) * sa) * p.w2_scale[col + e]);
-                  const __half sg = __float2half_rn(silu_pf(__half2float(g16)));
-                  h[e] = __half2float(sg) * __half2float(u16);
-                }
-                *reinterpret_cast<__half2*>(p.out + static_cast<int64_t>(row) * p.out_row_stride + p.out_col + col) =
-                    __floats2half2_rn(h[0], h[1]);
-              }
+        for (int j0 = 0; j0 < 32; j0 += 8) {         // eight channels = one 16-byte store; n is a multiple of 16
+          const int col = col0 + j0;
+          if (col >= p.n) break;
+          __align__(16) __half r[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            r[e] = __float2half_rn((static_cast<float>(static_cast<int>(v[j0 + e])) * sa) * cs[c * 32 + j0 + e]);
+          if (p.dual) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const __half u16 = __float2half_rn((static_cast<float>(static_cast<int>(u[j0 + e])) * sa) * cs[kBN / 2 + c * 32 + j0 + e]);
+              const __half sg = __float2half_rn(silu_pf(__half2float(r[e])));
+              r[e] = __float2half_rn(__half2float(sg) * __half2float(u16));
             }
+          }
+          if (grow != nullptr) {
+            const __half* gt = reinterpret_cast<const __half*>(&gq[j0 >> 3]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const __half sg = __float2half_rn(silu_pf(__half2float(gt[e])));
+              r[e] = __float2half_rn(__half2float(sg) * __half2float(r[e]));
+            }
+          }
+          if (rrow != nullptr) {
+            const __half* rs = reinterpret_cast<const __half*>(&rq[j0 >> 3]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) r[e] = __float2half_rn(__half2float(r[e]) + __half2float(rs[e]));
+          }
+          if ((reinterpret_cast<uintptr_t>(orow + col) & 15) == 0) {
+            *reinterpret_cast<uint4*>(orow + col) = *reinterpret_cast<const uint4*>(r);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) orow[col + e] = r[e];
           }
         }
       }
+      // this warp's reads of the accumulator are complete (tcgen05.wait::ld in tmem_ld32): hand it back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tc_fence_before();
@@ -239,39 +322,6 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   }
 }
 
-// ---- host --------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
-// Tensor map of an int8 matrix [rows, k] (row stride in bytes), boxes of 128 rows x 128 bytes, 128-byte swizzle,
-// out-of-range elements read as zero.
-static int make_map(CUtensorMap* map, const int8_t* base, int64_t rows, int64_t k, int64_t row_stride) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) return LSVD_ERR_CUDA;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride)};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), 128u};
-  const cuuint32_t estr[2] = {1u, 1u};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? LSVD_OK : LSVD_ERR_CUDA;
-}
-
 }  // namespace lsvd
 
 extern "C" int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* a, void* stream) {
@@ -280,30 +330,42 @@ extern "C" int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* a, void* stream) {
   if (!a->a || !a->w || !a->a_scale || !a->w_scale) return LSVD_ERR_INVALID_ARG;
   if (a->out == nullptr && a->acc_out == nullptr) return LSVD_ERR_INVALID_ARG;
   const bool dual = a->w2 != nullptr;
-  if (dual && (!a->w2_scale || a->out == nullptr || a->acc_out != nullptr)) return LSVD_ERR_INVALID_ARG;
+  if (dual && (!a->w2_scale || a->out == nullptr || a->acc_out != nullptr || a->gate != nullptr || a->residual != nullptr))
+    return LSVD_ERR_INVALID_ARG;
+  if ((a->gate != nullptr || a->residual != nullptr) && a->out == nullptr) return LSVD_ERR_INVALID_ARG;
   if (!aligned(a->a, 16) || (a->a_row_stride % 16) || !aligned(a->w, 16) || (a->w_row_stride % 16)) return LSVD_ERR_INVALID_ARG;
   if (dual && (!aligned(a->w2, 16) || (a->w2_row_stride % 16))) return LSVD_ERR_INVALID_ARG;
   if (a->out && (!aligned(a->out, 4) || (a->out_row_stride % 2) || (a->out_col % 2))) return LSVD_ERR_INVALID_ARG;
   CUtensorMap ma, mb, mb2;
-  int rc = make_map(&ma, a->a, a->m, a->k, a->a_row_stride);
+  int rc = make_map_k128(&ma, a->a, a->m, a->k, a->a_row_stride, kBM);
   if (rc != LSVD_OK) return rc;
-  rc = make_map(&mb, a->w, a->n, a->k, a->w_row_stride);
+  rc = make_map_k128(&mb, a->w, a->n, a->k, a->w_row_stride, kBN / 2);
   if (rc != LSVD_OK) return rc;
-  rc = make_map(&mb2, dual ? a->w2 : a->w, a->n, a->k, dual ? a->w2_row_stride : a->w_row_stride);
+  rc = make_map_k128(&mb2, dual ? a->w2 : a->w, a->n, a->k, dual ? a->w2_row_stride : a->w_row_stride, kBN / 2);
   if (rc != LSVD_OK) return rc;
   GemmParams p{};
   p.a_scale = a->a_scale;
+  p.a_scale_stride = a->a_scale_stride > 0 ? a->a_scale_stride : 1;
   p.w_scale = a->w_scale;
   p.w2_scale = a->w2_scale;
   p.out = static_cast<__half*>(a->out);
   p.out_row_stride = a->out_row_stride;
   p.out_col = a->out_col;
+  p.gate = static_cast<const __half*>(a->gate);
+  p.gate_row_stride = a->gate_row_stride;
+  p.gate_col = a->gate_col;
+  p.residual = static_cast<const __half*>(a->residual);
+  p.residual_row_stride = a->residual_row_stride;
   p.acc_out = a->acc_out;
   p.status_word = a->status_word;
   p.m = a->m; p.n = a->n; p.k = a->k; p.dual = dual ? 1 : 0;
-  LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(i8gemm_tcgen05_kernel), kGemmSmem));
   const int ntile = dual ? kBN / 2 : kBN;
-  dim3 grid((a->n + ntile - 1) / ntile, (a->m + kBM - 1) / kBM);
+  p.m_tiles = (a->m + kBM - 1) / kBM;
+  p.n_tiles = (a->n + ntile - 1) / ntile;
+  const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  if (tiles > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
+  LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(i8gemm_tcgen05_kernel), kGemmSmem));
+  const int grid = static_cast<int>(std::min<int64_t>(tiles, std::max(1, device_sm_count())));
   i8gemm_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmem, static_cast<cudaStream_t>(stream)>>>(ma, mb, mb2, p);
   LSVD_CUDA_TRY(cudaGetLastError());
   return LSVD_OK;

@@ -344,9 +344,11 @@ class HybridFFN(nn.Module):
 
 
 def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_col=0, want_acc=False, want_out=True,
-           status_word=None):
+           status_word=None, gate=None, gate_col=0, residual=None):
     """W8A8 product for any number of tokens on the tcgen05 tensor cores (prefill-sized batches): the same values
-    as ``w8a8_gemv``.  Returns (out fp16 or None, acc int32 or None)."""
+    as ``w8a8_gemv``.  ``gate`` (fp16, columns gate_col.. of it) turns a single product into the up half of a gate/up
+    pair whose gate came from other activations; ``residual`` is added in fp16.  Returns (out fp16 or None, acc int32
+    or None)."""
     _require_cuda(a_q, w_q)
     m, k = a_q.shape
     n = w_q.shape[0]
@@ -356,8 +358,12 @@ def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_c
     acc = torch.empty(m, n, dtype=torch.int32, device=dev) if want_acc else None
     g = _lib.I8GemmArgs()
     g.m, g.n, g.k = m, n, k
-    g.a, g.a_row_stride, g.a_scale = a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr()
+    g.a, g.a_row_stride, g.a_scale, g.a_scale_stride = a_q.data_ptr(), a_q.stride(0), a_scale.data_ptr(), a_scale.stride(0)
     g.w, g.w_row_stride, g.w_scale = w_q.data_ptr(), w_q.stride(0), w_scale.data_ptr()
+    if gate is not None:
+        g.gate, g.gate_row_stride, g.gate_col = gate.data_ptr(), gate.stride(0), gate_col
+    if residual is not None:
+        g.residual, g.residual_row_stride = residual.data_ptr(), residual.stride(0)
     if w2_q is not None:
         g.w2, g.w2_row_stride, g.w2_scale = w2_q.data_ptr(), w2_q.stride(0), w2_scale.data_ptr()
     if out is not None:
