@@ -291,7 +291,8 @@ class HybridFFN(nn.Module):
     @torch.no_grad()
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
                 norm_eps: float = 1e-6, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x [..., d_in] fp16 (at most 64 tokens) -> [..., d_out] fp16.  Intermediate buffers are kept per batch size,
+        """x [..., d_in] fp16 -> [..., d_out] fp16.  Up to 64 tokens take the weight-streaming decode kernels, more
+        take ``forward_prefill`` (same values).  In the decode form intermediate buffers are kept per batch size,
         so apart from the result (unless ``out`` is passed) a call allocates nothing and can be captured in a CUDA graph.
         ``norm_weight`` applies RMSNorm(x) * weight inside the first quantiser (for modules without an input rotation);
         ``residual [tokens, d_out]`` is added to the result in the down projection's epilogue."""
@@ -299,10 +300,13 @@ class HybridFFN(nn.Module):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         m = x2.shape[0]
-        if m > 64 or m < 1:
-            raise ValueError("the decode FFN takes 1..64 tokens per call")
+        if m < 1:
+            raise ValueError("the FFN needs at least one token")
         if x2.dtype != torch.float16 or x2.stride(1) != 1 or shape[-1] != self.d_in:
             raise ValueError("x must be fp16 [..., d_in] with unit inner stride")
+        if m > 64:
+            y = self.forward_prefill(x2, out, norm_weight, norm_eps, residual)
+            return y.view(*shape[:-1], self.d_out)
         if out is None:
             out = torch.empty(m, self.d_out, dtype=torch.float16, device=x.device)
         _, calls = self._plan(m, x.device)
@@ -332,6 +336,34 @@ class HybridFFN(nn.Module):
         for fn, args in calls[5:]:
             _lib.check(fn(C.byref(args), stream))
         return out.view(*shape[:-1], self.d_out)
+
+    @torch.no_grad()
+    def forward_prefill(self, x2: torch.Tensor, out: Optional[torch.Tensor] = None, norm_weight=None, norm_eps: float = 1e-6,
+                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The same block for prefill-sized batches ``x2 [m, d_in]``: the quantisers as in decode, every product on
+        the tcgen05 GEMM (``i8gemm``).  The SVD branch's gate and up products have different activations (their own
+        latents): the gate product writes its fp16 values into the hidden buffer and the up product's epilogue
+        gates them in place.  Bit-identical to the decode form row by row."""
+        m = x2.shape[0]
+        r, dev = self.rank, x2.device
+        x_q, x_s, _ = act_quant(x2, sign=self.had_sign, norm_weight=norm_weight, norm_eps=norm_eps)
+        lat16, _ = i8gemm(x_q, x_s, self.U_q, self.U_s)
+        z_q, z_s, _ = act_quant(lat16.view(2 * m, r))
+        z_q, z_s = z_q.view(m, 2 * r), z_s.view(m, 2)
+        h16 = torch.empty(m, self.d_ffn, dtype=torch.float16, device=dev)
+        i8gemm(z_q[:, :r], z_s[:, 0], self.Vg_q, self.Vg_s, out=h16, out_col=0)
+        i8gemm(z_q[:, r:], z_s[:, 1], self.Vu_q, self.Vu_s, out=h16, out_col=0, gate=h16, gate_col=0)
+        i8gemm(x_q, x_s, self.Wg_q, self.Wg_s, self.Wu_q, self.Wu_s, out=h16, out_col=self.n_svd)
+        if self.online_had and self.K > 1:
+            if self.had_K_packed is None:
+                self.had_K_packed = hadamard_pack(self.had_K)
+            h_q, h_s, _ = hadamard_quant(h16, self.had_K_packed, self.K)
+        else:
+            h_q, h_s, _ = act_quant(h16, fwht=self.online_had)
+        if out is None:
+            out = torch.empty(m, self.d_out, dtype=torch.float16, device=dev)
+        i8gemm(h_q, h_s, self.Wd_q, self.Wd_s, out=out, residual=residual)
+        return out
 
     def _side(self, device):
         key = str(device)

@@ -209,3 +209,28 @@ def test_config2_chain_stage_by_stage(m):
     # end to end
     err = rel_to_norm(st["out"].float(), ref["out"].float())
     assert err < TOL, err
+
+
+@pytest.mark.parametrize("m", [65, 300])
+def test_prefill_form_equals_decode_form_row_by_row(m):
+    """More than 64 tokens go through the tcgen05 GEMMs (forward_prefill): same bits as the decode kernels fed
+    the same rows 64 at a time, with and without a residual; the golden-fixture module likewise."""
+    g = load_golden("hadamard")
+    hk = unpack_had(g["had172_bits"], 172)
+    w = synth.ffn_weights(4096, 11008, 512, 5504, seed=3, had_K=hk, K=172)
+    gen = torch.Generator().manual_seed(200 + m)
+    x = torch.randn(m, 4096, generator=gen).half().cuda()
+    res = torch.randn(m, 4096, generator=gen).half().cuda()
+    ffn = HybridFFN(to_dev(w))
+    y = ffn(x)
+    y_res = ffn(x, residual=res)
+    for r0 in range(0, m, 64):
+        assert torch.equal(y[r0:r0 + 64], ffn(x[r0:r0 + 64]))
+        assert torch.equal(y_res[r0:r0 + 64], ffn(x[r0:r0 + 64], residual=res[r0:r0 + 64]))
+    gf = load_golden("hybrid_ffn")
+    small = HybridFFN(to_dev(_golden_weights(gf)))
+    xs = gf["x"].cuda()
+    reps = (70 + xs.shape[0] - 1) // xs.shape[0]
+    xb = xs.repeat(reps, 1)
+    yb = small(xb)
+    assert torch.equal(yb[:xs.shape[0]], small(xs))
