@@ -46,6 +46,15 @@ WORKLOADS = {
                               "context 4096, ragged per-head K/V ranks (multiples of 16 in [16,128], mean 64)"),
     "c1_attention": dict(batch=1, heads=32, head_dim=128, context=2048, ragged=False,
                          desc="BASELINE config 1: batch 1, context 2048, uniform rank 64"),
+    "c1_attention_rope": dict(batch=1, heads=32, head_dim=128, context=2048, aux="rope",
+                              desc="BASELINE config 1 shape in the reference's own attention form: int8 K up-factor, "
+                                   "keys rebuilt and rotated per token (lsvd_attn_decode_rope)"),
+    "c3_attention_rope": dict(batch=16, heads=32, head_dim=128, context=4096, aux="rope",
+                              desc="BASELINE config 3 batch/context with uniform rank 64 in the reference's own attention "
+                                   "form (int8 K up-factor, rotary keys)"),
+    "c5_prefill_ffn": dict(batch=8, context=4096, aux="prefill_ffn",
+                           desc="BASELINE config 5 prefill, FFN block of one layer: 8 x 4096 tokens through the hybrid "
+                                "SVD/RTN FFN 4096/11008 (rank 512, 50 % SVD channels) on the tcgen05 int8 GEMM"),
 }
 
 
@@ -365,6 +374,142 @@ def run_ours(args, rank, world, local):
     return line
 
 
+def run_aux(args, rank, world, local):
+    """Auxiliary workloads with their own step: the rotary attention form and the prefill FFN.  Same timing rules
+    and JSON keys as the decode workloads; ranks run replicas (no collective on these paths)."""
+    from lsvd_b200 import _lib
+    _lib.load()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    w = WORKLOADS[args.workload]
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    g = torch.Generator(device=dev).manual_seed(11 + rank)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    if w["aux"] == "rope":
+        from lsvd_b200.attention import InferState, token_decode_attention_flash_int8_latent_per_head_decoding_rope as rope
+        B, H, D, L, R = w["batch"], w["heads"], w["head_dim"], w["context"], 64
+        n_slots = B * L
+        ck = torch.randint(-128, 128, (n_slots, H, R), dtype=torch.int8, device=dev, generator=g)
+        cv = torch.randint(-128, 128, (n_slots, H, R), dtype=torch.int8, device=dev, generator=g)
+        sk = (torch.rand(n_slots, H, device=dev, generator=g) * 0.02 + 0.01).half()
+        sv = (torch.rand(n_slots, H, device=dev, generator=g) * 0.02 + 0.01).half()
+        wk = torch.randint(-128, 128, (R, H * D), dtype=torch.int8, device=dev, generator=g)
+        wks = (torch.rand(1, H * D, device=dev, generator=g) * 0.002 + 0.001).half()
+        st = InferState(B, L, [L] * B, device=dev)
+        qs_host = [torch.randn(B, H, D).half().pin_memory() for _ in range(8)]
+        qs = [t.to(dev) for t in qs_host]
+        q_in = torch.empty_like(qs[0])
+        out = torch.empty(B, H, R, dtype=torch.float16, device=dev)
+        need = _lib.load().lsvd_attn_decode_rope_workspace_bytes(B, H, D, R, L, 256)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        host_out = torch.empty(out.shape, dtype=torch.float16).pin_memory()
+        step = lambda: rope(q_in, st, H, D, ck, sk, cv, sv, wk, wks, out=out, workspace=ws, status_word=status)
+        feed = lambda i, host: q_in.copy_((qs_host if host else qs)[i % 8], non_blocking=True)
+        units, metric, launches = B, "decode_tokens_per_s", 3
+        abytes = n_slots * H * R * 2 + n_slots * H * 4 + n_slots * 4
+        roof = dict(kernel="rope_recon_kernel", bound="hbm", peak=float(peaks.get("hbm_gbs", 6650.0)), unit="GB/s", work=abytes)
+        h2d, d2h = q_in.numel() * 2, out.numel() * 2
+        l2 = "the cache (%.0f MB) %s L2" % (abytes / 1e6, "exceeds" if abytes > 126e6 else "fits in")
+        what = "cos/sin table + rotary reconstruct attention + merge"
+    else:
+        M = w["batch"] * w["context"]
+        ffn = make_ffn(dev, seed=50 + rank, copies=1)[0]
+        xs_host = [torch.randn(M, FFN_SHAPE["d_in"]).half().pin_memory() for _ in range(2)]
+        xs = [t.to(dev) for t in xs_host]
+        x_in = torch.empty_like(xs[0])
+        out = torch.empty(M, FFN_SHAPE["d_in"], dtype=torch.float16, device=dev)
+        host_out = torch.empty(out.shape, dtype=torch.float16).pin_memory()
+        step = lambda: ffn(x_in, out=out)
+        feed = lambda i, host: x_in.copy_((xs_host if host else xs)[i % 2], non_blocking=True)
+        units, metric, launches = M, "prefill_tokens_per_s", 9
+        ops = 2.0 * M * FFN_BYTES
+        int8_peak = 2.0 * float(peaks.get("bf16_tflops", 1590.0))
+        roof = dict(kernel="i8gemm_tcgen05_kernel (whole FFN step: six GEMM launches + three quantiser launches)",
+                    bound="tensor", peak=int8_peak, unit="TOP/s", work=ops,
+                    peak_note="int8 dense rate taken as twice the measured bf16 GEMM figure; nominal 4500")
+        h2d, d2h = x_in.numel() * 2, out.numel() * 2
+        l2 = "activations of %.0f MB per stage exceed L2" % (M * FFN_SHAPE["d_ffn"] * 2 / 1e6)
+        what = "input rotation + A8 quantisers + SVD and RTN gate/up GEMMs + Hadamard 64x172 + down GEMM"
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        feed(i, False)
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    e0, e1 = ev(), ev()
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        feed(i, False)
+        step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    f0, f1 = ev(), ev()
+    barrier()
+    f0.record()
+    for i in range(args.steps):
+        feed(i, True)
+        step()
+        host_out.copy_(out, non_blocking=True)
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+    # the step alone (no input refresh), for the roofline figure
+    k0, k1 = ev(), ev()
+    torch.cuda.synchronize()
+    k0.record()
+    for i in range(args.steps):
+        step()
+    k1.record()
+    torch.cuda.synchronize()
+    k_ms = k0.elapsed_time(k1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if status.item() != 0:
+        raise RuntimeError(f"device status word = {status.item()}")
+    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = t.tolist()
+    if rank != 0:
+        return None
+    ms_step = ms_total / args.steps
+    achieved = roof["work"] / (k_ms * 1e-3) / (1e9 if roof["bound"] == "hbm" else 1e12)
+    line = {
+        "metric": metric, "value": units * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp16 out", "data": "synthetic",
+        "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": w["batch"], "layers": 1, "step": what,
+                   "launch": "eager launches on one stream", "l2": l2},
+        "e2e": {"value": units * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"kernel": roof["kernel"], "bound": roof["bound"], "achieved": achieved, "peak": roof["peak"],
+                     "unit": roof["unit"], "frac": achieved / roof["peak"], "of": "measured" if peaks else "fallback",
+                     "traffic": None, "work_per_step": roof["work"], "step_us": k_ms * 1e3,
+                     **({"peak_note": roof["peak_note"]} if "peak_note" in roof else {})},
+        "clocks": clocks,
+    }
+    return line
+
+
 def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
     """The oracle (a CPU port of the reference's algorithm: the reference has no CPU implementation of latent
     attention, and its FFN module is fake-quant fp16 GPU code) timed on the host cores on a bounded sample of
@@ -374,6 +519,8 @@ def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
     w = dict(WORKLOADS[workload])
+    if w.get("aux"):
+        return cpu_baseline_aux(w, seconds_hint, threads)
     if w.get("ffn_only"):
         w["batch"] = tokens
     B = w["batch"]
@@ -415,13 +562,51 @@ def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
                       f"(int8 products evaluated in float64 for exactness, attention in fp32; the cache is pre-quantised)"}
 
 
+def cpu_baseline_aux(w, seconds_hint, threads):
+    """CPU port timings of the auxiliary workloads on a bounded sample."""
+    import math
+    from oracle import attention as oattn, ffn as offn, quant
+    from lsvd_b200 import synth
+    gen = torch.Generator().manual_seed(0)
+    if w["aux"] == "rope":
+        H, D, L, R, hs = w["heads"], w["head_dim"], w["context"], 64, 4
+        ck, sk = quant.latent_quant(torch.randn(L, hs, R, generator=gen).half())
+        cv, sv = quant.latent_quant(torch.randn(L, hs, R, generator=gen).half())
+        wk, wks = quant.wuk_quant((torch.randn(R, hs * D, generator=gen) / math.sqrt(R)).half())
+        q = torch.randn(1, hs, D, generator=gen).half()
+        r2t = torch.arange(L, dtype=torch.int32)[None]
+        one = torch.tensor([0], dtype=torch.int32)
+        fn = lambda: oattn.decode_rope_recon(q, ck, sk, cv, sv, wk, wks, r2t, one, torch.tensor([L], dtype=torch.int32))
+        per_call = hs / H                      # requests' worth of work per call
+        sample = f"1 request, {hs} of {H} heads, context {L}"
+    else:
+        fw = synth.ffn_weights(FFN_SHAPE["d_in"], FFN_SHAPE["d_ffn"], FFN_SHAPE["rank"], FFN_SHAPE["n_svd"], seed=0,
+                               had_K=synth.sign_matrix(FFN_SHAPE["K"]).float(), K=FFN_SHAPE["K"])
+        x = torch.randn(64, FFN_SHAPE["d_in"], generator=gen).half()
+        fn = lambda: offn.hybrid_ffn_stages(x, fw)
+        per_call = 64
+        sample = f"64 of {w['batch'] * w['context']} tokens"
+    fn()
+    n, t0 = 0, time.perf_counter()
+    while True:
+        fn()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > seconds_hint or n >= 20:
+            break
+    return {"value": per_call * n / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{sample}, {n} calls of the oracle, torch on {threads} threads"}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return None
     w = WORKLOADS[args.workload]
     B = args.tokens if w.get("ffn_only") else w["batch"]
+    if w.get("aux") == "prefill_ffn":
+        B = w["batch"] * w["context"]
     cb = cpu_baseline(args.workload, args.tokens, seconds_hint=max(5.0, 3.0 * args.steps))
-    return {"impl": "reference", "metric": "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
+    return {"impl": "reference", "metric": "prefill_tokens_per_s" if w.get("aux") == "prefill_ffn" else "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * B / cb["value"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32/fp64 (CPU)", "data": "synthetic",
             "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B}, "cpu_baseline": cb,
@@ -444,7 +629,7 @@ def main():
         if line is not None:
             print(json.dumps(line))
         return
-    line = run_ours(args, rank, world, local)
+    line = run_aux(args, rank, world, local) if WORKLOADS[args.workload].get("aux") else run_ours(args, rank, world, local)
     if line is not None:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload, args.tokens)

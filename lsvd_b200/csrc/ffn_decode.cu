@@ -10,6 +10,7 @@
 // Reference semantics: fake_quant/utils/hybrid_ffn_utils.py:956-984 (module forward),
 // fake_quant/utils/quant_utils.py:201-212,30-33 (activation quantiser), :319-338 (wrapped Linear),
 // fake_quant/utils/hadamard_utils.py:99-113 (rotations).
+#include <algorithm>
 #include <cmath>
 
 #include "common.cuh"
@@ -229,8 +230,11 @@ __device__ __forceinline__ float cluster_peer_float(const float* local, uint32_t
 }
 
 constexpr int kHadMaxTilesPerWarp = 2;     // m tiles a warp keeps in registers: Kp <= 256 with 8 warps
-constexpr int kHadMaxNtilePer = 2;         // 8-column tiles per block: nb <= 128 with a cluster of 8
+// 8-column tiles per block (template parameter NTP): 2 covers nb <= 128 with a cluster of 8 blocks per token, the
+// latency-oriented form of decode batches; 8 lets one block (nb <= 64) or two (nb = 128) take a whole token, the
+// throughput-oriented form of prefill batches, where tokens outnumber the SMs by far.
 
+template <int kHadMaxNtilePer>
 __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_constant__ HadQuantParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half* Tt = reinterpret_cast<__half*>(smem_raw);          // [ntile_per * 8][ld]: my columns of the rotated blocks
@@ -320,19 +324,26 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
       for (int c = 0; c < 4; ++c) d[mi][ni][c] = 0.f;
     if (mt < tiles) {
       const uint4* ap = p.packed + (static_cast<int64_t>(mt) * tiles) * 32 + lane;
-      uint4 a[16];                                         // every k tile of this m tile, loaded together
+      // decode form: every k tile of this m tile requested together (one memory round trip); prefill form: one
+      // at a time (they stay in L1 for the next tokens of the SM, and the registers hold more accumulators instead)
+      constexpr int kAhead = kHadMaxNtilePer <= 2 ? 16 : 1;
+      uint4 a[kAhead];
+      if (kAhead == 16) {
 #pragma unroll
-      for (int kt = 0; kt < 16; ++kt) a[kt] = kt < tiles ? __ldg(ap + kt * 32) : make_uint4(0u, 0u, 0u, 0u);
+        for (int kt = 0; kt < kAhead; ++kt) a[kt] = kt < tiles ? __ldg(ap + kt * 32) : make_uint4(0u, 0u, 0u, 0u);
+      }
 #pragma unroll
       for (int kt = 0; kt < 16; ++kt) {
         if (kt < tiles) {
+          if (kAhead == 1) a[0] = __ldg(ap + kt * 32);
+          const uint4 af = a[kAhead == 16 ? kt : 0];
 #pragma unroll
           for (int ni = 0; ni < kHadMaxNtilePer; ++ni) {
             if (ni < p.ntile_per) {
               const __half* brow = Tt + (ni * 8 + g) * ld + kt * 16 + 2 * t;
               const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow);
               const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 8);
-              mma_f16_16x8x16(d[mi][ni], a[kt].x, a[kt].y, a[kt].z, a[kt].w, b0, b1);
+              mma_f16_16x8x16(d[mi][ni], af.x, af.y, af.z, af.w, b0, b1);
             }
           }
         }
@@ -583,13 +594,21 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
   p.Kp = (a->K + 15) / 16 * 16;
   p.ld = p.Kp + 8;
   const int ntiles = nb / 8;
-  p.cluster = ntiles < 8 ? ntiles : 8;
+  // Few tokens: a cluster of up to 8 blocks per token shortens the critical path.  Many tokens: one block (two
+  // for nb = 128) per token keeps every SM busy without the cluster's redundant staging.
+  const bool many = a->rows > 2 * std::max(1, device_sm_count());
+  if (many) {
+    p.cluster = ntiles <= 8 ? 1 : ntiles / 8;
+  } else {
+    p.cluster = ntiles < 8 ? ntiles : 8;
+  }
   p.ntile_per = ntiles / p.cluster;
   p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
   const int smem = (p.ntile_per * 8 * p.ld + a->cols) * 2;
   p.x_vec16 = (aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && (a->cols % 8) == 0) ? 1 : 0;
-  if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(hadamard_quant_kernel), smem));
-  LSVD_CUDA_TRY(launch_chained(hadamard_quant_kernel, dim3(static_cast<unsigned>(a->rows * p.cluster)), dim3(256), smem,
+  void (*kern)(HadQuantParams) = p.ntile_per <= 2 ? hadamard_quant_kernel<2> : hadamard_quant_kernel<8>;
+  if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
+  LSVD_CUDA_TRY(launch_chained(kern, dim3(static_cast<unsigned>(a->rows * p.cluster)), dim3(256), smem,
                                static_cast<cudaStream_t>(stream), p.cluster, false, p));
   return LSVD_OK;
 }
