@@ -164,6 +164,95 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const __grid_constant__ 
 }
 
 // ----------------------------------------------------------------------------------------------
+// The input rotation for rows of 4096 entries (the 7B hidden size): radix-16 butterflies in registers
+// ----------------------------------------------------------------------------------------------
+// 256 threads x 16 entries.  Three rounds of four butterfly stages each run in registers (strides 1..8 on 16
+// consecutive entries, 16..128 and 256..2048 after an exchange through shared memory): the same additions in the
+// same order as the stage-by-stage loop of act_quant_kernel, with 5 block barriers instead of 14.
+__device__ __forceinline__ int rot_slot(int j) { return j + (j >> 4); }      // one pad word per 16: conflict-free exchanges
+
+__device__ __forceinline__ void butterflies16(float (&e)[16]) {
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if ((i & h) == 0) {
+        const float a = e[i], b = e[i + h];
+        e[i] = a + b;
+        e[i + h] = a - b;
+      }
+}
+
+__global__ void __launch_bounds__(256) act_quant_rot4096_kernel(const __grid_constant__ ActQuantParams p) {
+  __shared__ float row[4096 + 256];
+  __shared__ float red[8];
+  grid_dependency_sync();
+  const int r = blockIdx.x, T = threadIdx.x;
+  const __half* x = p.x + r * p.x_row_stride;
+  float e[16];
+  {
+    const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(x) + 2 * T), v1 = __ldg(reinterpret_cast<const uint4*>(x) + 2 * T + 1);
+    uint4 s0 = make_uint4(0u, 0u, 0u, 0u), s1 = s0;
+    if (p.sign != nullptr) {
+      s0 = __ldg(reinterpret_cast<const uint4*>(p.sign) + 2 * T);
+      s1 = __ldg(reinterpret_cast<const uint4*>(p.sign) + 2 * T + 1);
+    }
+    const __half2* xa = reinterpret_cast<const __half2*>(&v0);
+    const __half2* xb = reinterpret_cast<const __half2*>(&v1);
+    const __half2* sa = reinterpret_cast<const __half2*>(&s0);
+    const __half2* sb = reinterpret_cast<const __half2*>(&s1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __half22float2(xa[i]), g2 = __half22float2(xb[i]);
+      if (p.sign != nullptr) {
+        const float2 u = __half22float2(sa[i]), w = __half22float2(sb[i]);
+        f.x *= u.x; f.y *= u.y; g2.x *= w.x; g2.y *= w.y;
+      }
+      e[2 * i] = f.x; e[2 * i + 1] = f.y; e[8 + 2 * i] = g2.x; e[8 + 2 * i + 1] = g2.y;
+    }
+  }
+  butterflies16(e);                                            // strides 1, 2, 4, 8: entries 16 T + i
+#pragma unroll
+  for (int i = 0; i < 16; ++i) row[rot_slot(16 * T + i)] = e[i];
+  __syncthreads();
+  const int j2 = (T >> 4) * 256 + (T & 15);                    // strides 16 .. 128: entries j2 + 16 i
+#pragma unroll
+  for (int i = 0; i < 16; ++i) e[i] = row[rot_slot(j2 + 16 * i)];
+  butterflies16(e);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) row[rot_slot(j2 + 16 * i)] = e[i];
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) e[i] = row[rot_slot(T + 256 * i)];   // strides 256 .. 2048: entries T + 256 i
+  butterflies16(e);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    e[i] = __half2float(__float2half_rn(e[i] * p.rot_scale));
+    amax = fmaxf(amax, fabsf(e[i]));
+    row[rot_slot(T + 256 * i)] = e[i];
+  }
+  amax = block_max(amax, red);                                 // its barriers also publish the rotated row
+  const float s = act_scale_of(amax);
+  if (T == 0) p.scale[r] = s;
+  // 16 consecutive entries per thread again: one 16-byte store of codes (and two of fp16 values if wanted)
+  __align__(16) int8_t codes[16];
+  __align__(16) __half hv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float v = row[rot_slot(16 * T + i)];
+    codes[i] = act_code(v, s);
+    hv[i] = __float2half_rn(v);
+  }
+  *reinterpret_cast<uint4*>(p.q + r * p.q_row_stride + 16 * T) = *reinterpret_cast<const uint4*>(codes);
+  if (p.x_rot != nullptr) {
+    uint4* dst = reinterpret_cast<uint4*>(p.x_rot + static_cast<int64_t>(r) * p.cols + 16 * T);
+    dst[0] = reinterpret_cast<const uint4*>(hv)[0];
+    dst[1] = reinterpret_cast<const uint4*>(hv)[1];
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
 // (H_K kron H_nb) rotation + per-token quantisation: a thread-block cluster per token
 // ----------------------------------------------------------------------------------------------
 // y[k', j] = sum_k had_K[k', k] * fwht(x[k, :])[j] / sqrt(cols).  The blocks of a cluster split the nb
@@ -396,6 +485,139 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
 }
 
 // ----------------------------------------------------------------------------------------------
+// The same rotation + quantisation for many tokens (prefill): one block per token, built for throughput
+// ----------------------------------------------------------------------------------------------
+// nb = 64.  A warp rotates four 64-entry blocks at a time: a lane holds eight consecutive entries of one block
+// (one 16-byte load), does the strides 1, 2, 4 in registers and the strides 8, 16, 32 with three rounds of
+// shuffles: the same additions in the same order as the butterfly loop.  The had_K product and the fp16
+// roundings are those of hadamard_quant_kernel; the int8 codes are staged in shared memory and leave as
+// 16-byte stores.
+constexpr int kRowsNb = 64;
+
+__global__ void __launch_bounds__(256) hadamard_quant_rows_kernel(const __grid_constant__ HadQuantParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __shared__ float red[8];
+  const int K = p.K, ld = p.ld;                              // ld = Kp + 10 halves here
+  __half* Tt = reinterpret_cast<__half*>(smem_raw);           // [64][ld]: column j of every rotated block
+  uint8_t* Tq = smem_raw;                                     // [Kp][80] int8 codes, after the product (same bytes)
+  const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __half* xg = p.x + r * p.x_row_stride;
+
+  // columns K .. Kp of Tt meet zero entries of had_K in the product: they must hold numbers, not leftovers
+  for (int i = threadIdx.x; i < kRowsNb * (p.Kp - K); i += blockDim.x) {
+    const int j = i / (p.Kp - K), k = K + (i - j * (p.Kp - K));
+    Tt[j * ld + k] = __float2half_rn(0.f);
+  }
+  {
+    const int sub = lane & 7, quad = lane >> 3;
+    for (int k0 = warp * 4; k0 < K; k0 += 32) {
+      const int k = k0 + quad;
+      float e[8];
+      if (k < K) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(xg + k * kRowsNb) + sub);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h2[i]);
+          e[2 * i] = f.x;
+          e[2 * i + 1] = f.y;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = 0.f;
+      }
+#pragma unroll
+      for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if ((i & h) == 0) {
+            const float a = e[i], b = e[i + h];
+            e[i] = a + b;
+            e[i + h] = a - b;
+          }
+#pragma unroll
+      for (int h = 1; h < 8; h <<= 1)              // strides 8, 16, 32 <-> lane bits 0, 1, 2
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float o = __shfl_xor_sync(0xffffffffu, e[i], h);
+          e[i] = (sub & h) ? o - e[i] : e[i] + o;
+        }
+      if (k < K) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) Tt[(sub * 8 + i) * ld + k] = __float2half_rn(e[i] * p.rot_scale);
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- had_K product: warp w owns m tiles w, w + 8 ----
+  const int g = lane >> 2, t = lane & 3;
+  const int tiles = p.Kp >> 4;
+  float d[kHadMaxTilesPerWarp][8][4];
+  float amax = 0.f;
+#pragma unroll
+  for (int mi = 0; mi < kHadMaxTilesPerWarp; ++mi) {
+    const int mt = warp + mi * 8;
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) d[mi][ni][c] = 0.f;
+    if (mt < tiles) {
+      const uint4* ap = p.packed + (static_cast<int64_t>(mt) * tiles) * 32 + lane;
+      uint4 af = __ldg(ap);
+      for (int kt = 0; kt < tiles; ++kt) {
+        const uint4 an = kt + 1 < tiles ? __ldg(ap + (kt + 1) * 32) : af;       // next fragment in flight
+#pragma unroll
+        for (int ni = 0; ni < 8; ++ni) {
+          const __half* brow = Tt + (ni * 8 + g) * ld + kt * 16 + 2 * t;
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 8);
+          mma_f16_16x8x16(d[mi][ni], af.x, af.y, af.z, af.w, b0, b1);
+        }
+        af = an;
+      }
+#pragma unroll
+      for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          d[mi][ni][c] = __half2float(__float2half_rn(d[mi][ni][c]));        // the reference's fp16 result
+          if (mt * 16 + g + 8 * (c >> 1) < K) amax = fmaxf(amax, fabsf(d[mi][ni][c]));
+        }
+    }
+  }
+  amax = block_max(amax, red);                // its barriers also end every warp's reads of Tt
+  const float s = act_scale_of(amax);
+  if (threadIdx.x == 0) p.scale[r] = s;
+
+  // ---- quantise into shared memory (rows of 80 bytes: conflict-free 2-byte stores, 16-byte aligned rows) ----
+#pragma unroll
+  for (int mi = 0; mi < kHadMaxTilesPerWarp; ++mi) {
+    const int mt = warp + mi * 8;
+    if (mt >= tiles) continue;
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int row = mt * 16 + g + 8 * hf;
+        const uint16_t packed = static_cast<uint16_t>(static_cast<uint8_t>(act_code(d[mi][ni][2 * hf], s))) |
+                                (static_cast<uint16_t>(static_cast<uint8_t>(act_code(d[mi][ni][2 * hf + 1], s))) << 8);
+        *reinterpret_cast<uint16_t*>(Tq + row * 80 + ni * 8 + 2 * t) = packed;
+      }
+  }
+  __syncthreads();
+  int8_t* q = p.q + r * p.q_row_stride;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+    for (int i = threadIdx.x; i < K * 4; i += blockDim.x) {
+      const int row = i >> 2, c = i & 3;
+      reinterpret_cast<uint4*>(q)[i] = *reinterpret_cast<const uint4*>(Tq + row * 80 + c * 16);
+    }
+  } else {
+    for (int i = threadIdx.x; i < K * kRowsNb; i += blockDim.x) q[i] = static_cast<int8_t>(Tq[(i >> 6) * 80 + (i & 63)]);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
 // weight-streaming W8A8 product
 // ----------------------------------------------------------------------------------------------
 constexpr int kGemvWarps = 8;
@@ -547,6 +769,12 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
   p.vec8 = ((a->cols % 8) == 0 && aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && aligned(a->q, 8) &&
             (a->q_row_stride % 8) == 0 && (a->sign == nullptr || aligned(a->sign, 16))) ? 1 : 0;
+  if (rotate && a->cols == 4096 && p.vec8 && p.norm_weight == nullptr && aligned(a->q, 16) && (a->q_row_stride % 16) == 0 &&
+      (p.x_rot == nullptr || aligned(p.x_rot, 16))) {
+    LSVD_CUDA_TRY(launch_chained(act_quant_rot4096_kernel, dim3(a->rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
+                                 false, p));
+    return LSVD_OK;
+  }
   const int smem = a->cols * 4;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(act_quant_kernel), smem));
   LSVD_CUDA_TRY(launch_chained(act_quant_kernel, dim3(a->rows), dim3(256), smem, static_cast<cudaStream_t>(stream), 1, false, p));
@@ -606,6 +834,15 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
   p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
   const int smem = (p.ntile_per * 8 * p.ld + a->cols) * 2;
   p.x_vec16 = (aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && (a->cols % 8) == 0) ? 1 : 0;
+  if (many && nb == kRowsNb && a->y == nullptr && p.x_vec16 && (a->x_row_stride % 8) == 0) {
+    p.ld = p.Kp + 10;
+    const int smem_rows = std::max(kRowsNb * p.ld * 2, p.Kp * 80);
+    if (smem_rows > 48 * 1024)
+      LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(hadamard_quant_rows_kernel), smem_rows));
+    LSVD_CUDA_TRY(launch_chained(hadamard_quant_rows_kernel, dim3(static_cast<unsigned>(a->rows)), dim3(256), smem_rows,
+                                 static_cast<cudaStream_t>(stream), 1, false, p));
+    return LSVD_OK;
+  }
   void (*kern)(HadQuantParams) = p.ntile_per <= 2 ? hadamard_quant_kernel<2> : hadamard_quant_kernel<8>;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
   LSVD_CUDA_TRY(launch_chained(kern, dim3(static_cast<unsigned>(a->rows * p.cluster)), dim3(256), smem,
