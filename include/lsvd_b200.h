@@ -289,6 +289,44 @@ typedef struct lsvd_gemv_args {
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The whole hybrid SVD/RTN FFN for a decode batch (1..64 tokens) in one call: the chain of lsvd_act_quant,
+ * lsvd_w8a8_gemv and lsvd_hadamard_quant launches that replaces HybridSVDQuantFFN.forward
+ * (fake_quant/utils/hybrid_ffn_utils.py:956-984):
+ *   x_q = quant([rmsnorm | rotate](x));  z = quant(U x_q) (gate and up latents separately);
+ *   h = [ silu(Vg z_g) * (Vu z_u) | silu(Wg x_q) * (Wu x_q) ];  out = Wd quant(hadamard(h)) [+ residual]
+ * Weights are int8 [out, in] row-major with one fp32 scale per output channel; all of them contiguous.
+ * With overlap != 0 the RTN pair runs on a second stream owned by the library (created on first use, one per
+ * device) and rejoins `stream` before the Hadamard step, also inside a stream capture.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lsvd_ffn_decode_args {
+  int32_t m, d_in, d_ffn, d_out, rank, n_svd;   /* d_ffn = n_svd (SVD channels, first) + RTN channels            */
+  int32_t K;                     /* order of the non-power-of-two Hadamard factor (1: none)                       */
+  int32_t online_had;            /* rotate the hidden vector before quantising it                                 */
+  int32_t overlap;               /* RTN gate/up pair on the library's second stream                               */
+  const void* x;                 /* device fp16 [m, d_in]                                                         */
+  int64_t x_row_stride;
+  const void* had_sign;          /* device fp16 [d_in] of +-1 (input rotation), or NULL                           */
+  const void* norm_weight;       /* device fp16 [d_in] or NULL (RMSNorm inside the first quantiser; not with had_sign) */
+  float norm_eps;
+  const int8_t* U_q;  const float* U_s;          /* [2 rank, d_in]: gate latent rows, then up latent rows         */
+  const int8_t* Vg_q; const float* Vg_s;         /* [n_svd, rank]                                                 */
+  const int8_t* Vu_q; const float* Vu_s;
+  const int8_t* Wg_q; const float* Wg_s;         /* [d_ffn - n_svd, d_in]                                         */
+  const int8_t* Wu_q; const float* Wu_s;
+  const int8_t* Wd_q; const float* Wd_s;         /* [d_out, d_ffn], input columns [SVD | RTN]                     */
+  const void* had_K_packed;      /* from lsvd_hadamard_pack, when K > 1                                           */
+  const void* residual;          /* optional device fp16 [m, d_out]                                               */
+  int64_t residual_row_stride;
+  void* out;                     /* device fp16 [m, d_out]                                                        */
+  int64_t out_row_stride;
+  void* workspace;               /* device, 256-byte aligned, lsvd_ffn_decode_workspace_bytes(m, d_in, d_ffn, rank) */
+  size_t workspace_bytes;
+  int32_t* status_word;          /* device int32 or NULL                                                          */
+} lsvd_ffn_decode_args;
+size_t lsvd_ffn_decode_workspace_bytes(int32_t m, int32_t d_in, int32_t d_ffn, int32_t rank);
+int lsvd_ffn_decode(const lsvd_ffn_decode_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * W8A8 GEMM for prefill / large batches on tcgen05 (kind::i8, accumulators in tensor memory, TMA-fed).
  * acc[m, n] = sum_k a[m, k] * w[n, k] (int32, exact); out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n]);
  * with w2: a gate/up pair sharing the activations, out = fp16(fp16(silu(gate)) * up).  Same values as

@@ -107,6 +107,21 @@ class GemvArgs(C.Structure):
     ]
 
 
+class FfnDecodeArgs(C.Structure):
+    _fields_ = [
+        ("m", C.c_int32), ("d_in", C.c_int32), ("d_ffn", C.c_int32), ("d_out", C.c_int32), ("rank", C.c_int32),
+        ("n_svd", C.c_int32), ("K", C.c_int32), ("online_had", C.c_int32), ("overlap", C.c_int32),
+        ("x", C.c_void_p), ("x_row_stride", C.c_int64), ("had_sign", C.c_void_p), ("norm_weight", C.c_void_p),
+        ("norm_eps", C.c_float),
+        ("U_q", C.c_void_p), ("U_s", C.c_void_p), ("Vg_q", C.c_void_p), ("Vg_s", C.c_void_p),
+        ("Vu_q", C.c_void_p), ("Vu_s", C.c_void_p), ("Wg_q", C.c_void_p), ("Wg_s", C.c_void_p),
+        ("Wu_q", C.c_void_p), ("Wu_s", C.c_void_p), ("Wd_q", C.c_void_p), ("Wd_s", C.c_void_p),
+        ("had_K_packed", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
+        ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("status_word", C.c_void_p),
+    ]
+
+
 class I8GemmArgs(C.Structure):
     _fields_ = [
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
@@ -130,6 +145,8 @@ SIGNATURES = {
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_static_scratch_bytes": (C.c_size_t, []),
     "lsvd_attn_decode_static": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
+    "lsvd_ffn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 4),
+    "lsvd_ffn_decode": (C.c_int, [C.POINTER(FfnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_rope_workspace_bytes": (C.c_size_t, [C.c_int32] * 6),
     "lsvd_attn_decode_rope": (C.c_int, [C.POINTER(AttnRopeArgs), C.c_void_p]),
     "lsvd_act_quant": (C.c_int, [C.POINTER(ActQuantArgs), C.c_void_p]),

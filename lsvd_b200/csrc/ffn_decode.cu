@@ -494,14 +494,15 @@ __global__ void __launch_bounds__(256) hadamard_quant_kernel(const __grid_consta
 // 16-byte stores.
 constexpr int kRowsNb = 64;
 
-__global__ void __launch_bounds__(256) hadamard_quant_rows_kernel(const __grid_constant__ HadQuantParams p) {
+__global__ void __launch_bounds__(512) hadamard_quant_rows_kernel(const __grid_constant__ HadQuantParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __shared__ float red[8];
+  __shared__ float red[16];
   const int K = p.K, ld = p.ld;                              // ld = Kp + 10 halves here
   __half* Tt = reinterpret_cast<__half*>(smem_raw);           // [64][ld]: column j of every rotated block
   uint8_t* Tq = smem_raw;                                     // [Kp][80] int8 codes, after the product (same bytes)
   const int r = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nw = blockDim.x >> 5;                              // one warp per 16-row tile of had_K: Kp / 16 warps
   const __half* xg = p.x + r * p.x_row_stride;
 
   // columns K .. Kp of Tt meet zero entries of had_K in the product: they must hold numbers, not leftovers
@@ -511,21 +512,27 @@ __global__ void __launch_bounds__(256) hadamard_quant_rows_kernel(const __grid_c
   }
   {
     const int sub = lane & 7, quad = lane >> 3;
-    for (int k0 = warp * 4; k0 < K; k0 += 32) {
-      const int k = k0 + quad;
+    constexpr int kMaxIter = 4;                     // K / 4 groups of four blocks over Kp / 16 warps: at most 4 each
+    uint4 xv[kMaxIter];
+#pragma unroll
+    for (int it = 0; it < kMaxIter; ++it) {         // every load of this lane in flight before the first use
+      const int k = (warp + it * nw) * 4 + quad;
+      xv[it] = make_uint4(0u, 0u, 0u, 0u);
+      if (k < K) xv[it] = __ldg(reinterpret_cast<const uint4*>(xg + k * kRowsNb) + sub);
+    }
+#pragma unroll
+    for (int it = 0; it < kMaxIter; ++it) {
+      const int k = (warp + it * nw) * 4 + quad;
+      if ((warp + it * nw) * 4 >= K) break;
       float e[8];
-      if (k < K) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(xg + k * kRowsNb) + sub);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+      {
+        const __half2* h2 = reinterpret_cast<const __half2*>(&xv[it]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 f = __half22float2(h2[i]);
           e[2 * i] = f.x;
           e[2 * i + 1] = f.y;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = 0.f;
       }
 #pragma unroll
       for (int h = 1; h < 8; h <<= 1)
@@ -551,40 +558,45 @@ __global__ void __launch_bounds__(256) hadamard_quant_rows_kernel(const __grid_c
   }
   __syncthreads();
 
-  // ---- had_K product: warp w owns m tiles w, w + 8 ----
+  // ---- had_K product: warp w owns m tile w ----
   const int g = lane >> 2, t = lane & 3;
   const int tiles = p.Kp >> 4;
-  float d[kHadMaxTilesPerWarp][8][4];
+  const int mt = warp;
+  float d[8][4];
   float amax = 0.f;
 #pragma unroll
-  for (int mi = 0; mi < kHadMaxTilesPerWarp; ++mi) {
-    const int mt = warp + mi * 8;
+  for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) d[ni][c] = 0.f;
+  {
+    const uint4* ap = p.packed + (static_cast<int64_t>(mt) * tiles) * 32 + lane;
+    uint4 af[4];                                 // four fragments of had_K in flight
+#pragma unroll
+    for (int u = 0; u < 4; ++u) af[u] = u < tiles ? __ldg(ap + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+    for (int kt0 = 0; kt0 < tiles; kt0 += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int kt = kt0 + u;
+        if (kt < tiles) {
+          const uint4 a4 = af[u];
+          if (kt + 4 < tiles) af[u] = __ldg(ap + (kt + 4) * 32);
+#pragma unroll
+          for (int ni = 0; ni < 8; ++ni) {
+            const __half* brow = Tt + (ni * 8 + g) * ld + kt * 16 + 2 * t;
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 8);
+            mma_f16_16x8x16(d[ni], a4.x, a4.y, a4.z, a4.w, b0, b1);
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int ni = 0; ni < 8; ++ni)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) d[mi][ni][c] = 0.f;
-    if (mt < tiles) {
-      const uint4* ap = p.packed + (static_cast<int64_t>(mt) * tiles) * 32 + lane;
-      uint4 af = __ldg(ap);
-      for (int kt = 0; kt < tiles; ++kt) {
-        const uint4 an = kt + 1 < tiles ? __ldg(ap + (kt + 1) * 32) : af;       // next fragment in flight
-#pragma unroll
-        for (int ni = 0; ni < 8; ++ni) {
-          const __half* brow = Tt + (ni * 8 + g) * ld + kt * 16 + 2 * t;
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 8);
-          mma_f16_16x8x16(d[mi][ni], af.x, af.y, af.z, af.w, b0, b1);
-        }
-        af = an;
+      for (int c = 0; c < 4; ++c) {
+        d[ni][c] = __half2float(__float2half_rn(d[ni][c]));        // the reference's fp16 result
+        if (mt * 16 + g + 8 * (c >> 1) < K) amax = fmaxf(amax, fabsf(d[ni][c]));
       }
-#pragma unroll
-      for (int ni = 0; ni < 8; ++ni)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          d[mi][ni][c] = __half2float(__float2half_rn(d[mi][ni][c]));        // the reference's fp16 result
-          if (mt * 16 + g + 8 * (c >> 1) < K) amax = fmaxf(amax, fabsf(d[mi][ni][c]));
-        }
-    }
   }
   amax = block_max(amax, red);                // its barriers also end every warp's reads of Tt
   const float s = act_scale_of(amax);
@@ -592,19 +604,14 @@ __global__ void __launch_bounds__(256) hadamard_quant_rows_kernel(const __grid_c
 
   // ---- quantise into shared memory (rows of 80 bytes: conflict-free 2-byte stores, 16-byte aligned rows) ----
 #pragma unroll
-  for (int mi = 0; mi < kHadMaxTilesPerWarp; ++mi) {
-    const int mt = warp + mi * 8;
-    if (mt >= tiles) continue;
+  for (int ni = 0; ni < 8; ++ni)
 #pragma unroll
-    for (int ni = 0; ni < 8; ++ni)
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const int row = mt * 16 + g + 8 * hf;
-        const uint16_t packed = static_cast<uint16_t>(static_cast<uint8_t>(act_code(d[mi][ni][2 * hf], s))) |
-                                (static_cast<uint16_t>(static_cast<uint8_t>(act_code(d[mi][ni][2 * hf + 1], s))) << 8);
-        *reinterpret_cast<uint16_t*>(Tq + row * 80 + ni * 8 + 2 * t) = packed;
-      }
-  }
+    for (int hf = 0; hf < 2; ++hf) {
+      const int row = mt * 16 + g + 8 * hf;
+      const uint16_t packed = static_cast<uint16_t>(static_cast<uint8_t>(act_code(d[ni][2 * hf], s))) |
+                              (static_cast<uint16_t>(static_cast<uint8_t>(act_code(d[ni][2 * hf + 1], s))) << 8);
+      *reinterpret_cast<uint16_t*>(Tq + row * 80 + ni * 8 + 2 * t) = packed;
+    }
   __syncthreads();
   int8_t* q = p.q + r * p.q_row_stride;
   if ((reinterpret_cast<uintptr_t>(q) & 15) == 0) {
@@ -824,7 +831,8 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
   const int ntiles = nb / 8;
   // Few tokens: a cluster of up to 8 blocks per token shortens the critical path.  Many tokens: one block (two
   // for nb = 128) per token keeps every SM busy without the cluster's redundant staging.
-  const bool many = a->rows > 2 * std::max(1, device_sm_count());
+  // a cluster of 8 blocks per token stops paying once the clusters no longer fit on the GPU together
+  const bool many = a->rows * 8 > 2 * std::max(1, device_sm_count());
   if (many) {
     p.cluster = ntiles <= 8 ? 1 : ntiles / 8;
   } else {
@@ -839,7 +847,7 @@ extern "C" int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* a, void* stre
     const int smem_rows = std::max(kRowsNb * p.ld * 2, p.Kp * 80);
     if (smem_rows > 48 * 1024)
       LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(hadamard_quant_rows_kernel), smem_rows));
-    LSVD_CUDA_TRY(launch_chained(hadamard_quant_rows_kernel, dim3(static_cast<unsigned>(a->rows)), dim3(256), smem_rows,
+    LSVD_CUDA_TRY(launch_chained(hadamard_quant_rows_kernel, dim3(static_cast<unsigned>(a->rows)), dim3(p.Kp * 2), smem_rows,
                                  static_cast<cudaStream_t>(stream), 1, false, p));
     return LSVD_OK;
   }

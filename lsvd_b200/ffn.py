@@ -171,7 +171,7 @@ class HybridFFN(nn.Module):
         self.register_buffer("had_K_packed", None if (hk is None or self.K == 1 or not hk.is_cuda)
                              else hadamard_pack(self.had_K))
         self._plans = {}
-        self._side_streams = {}
+        self._chains = {}
         self.overlap_branches = True      # RTN gate/up on a second stream beside the SVD branch
         self.rank = self.U_q.shape[0] // 2
         self.n_svd = self.Vg_q.shape[0]
@@ -309,33 +309,43 @@ class HybridFFN(nn.Module):
             return y.view(*shape[:-1], self.d_out)
         if out is None:
             out = torch.empty(m, self.d_out, dtype=torch.float16, device=x.device)
-        _, calls = self._plan(m, x.device)
-        calls[0][1].x, calls[0][1].x_row_stride = x2.data_ptr(), x2.stride(0)
-        calls[0][1].norm_weight, calls[0][1].norm_eps = _ptr(norm_weight), norm_eps
-        calls[-1][1].out = out.data_ptr()
-        calls[-1][1].residual = _ptr(residual)
-        calls[-1][1].residual_row_stride = residual.stride(0) if residual is not None else 0
-        stream = _stream_ptr(x)
-        if not self.overlap_branches:
-            for fn, args in calls:
-                _lib.check(fn(C.byref(args), stream))
-            return out.view(*shape[:-1], self.d_out)
-        # The RTN gate/up product (calls[4]) needs only the quantised input: it runs on a second stream beside
-        # the SVD branch (latent product, latent quantiser, gate/up from the latents) and joins before the
-        # Hadamard quantiser.  Inside a CUDA graph capture the two streams become parallel branches.
-        cur = torch.cuda.current_stream(x.device)
-        side, fork, join = self._side(x.device)
-        _lib.check(calls[0][0](C.byref(calls[0][1]), stream))
-        fork.record(cur)
-        side.wait_event(fork)
-        _lib.check(calls[4][0](C.byref(calls[4][1]), side.cuda_stream))
-        join.record(side)
-        for fn, args in calls[1:4]:
-            _lib.check(fn(C.byref(args), stream))
-        cur.wait_event(join)
-        for fn, args in calls[5:]:
-            _lib.check(fn(C.byref(args), stream))
+        a, _ = self._chain(m, x.device)
+        a.x, a.x_row_stride = x2.data_ptr(), x2.stride(0)
+        a.norm_weight, a.norm_eps = _ptr(norm_weight), norm_eps
+        a.out, a.out_row_stride = out.data_ptr(), out.stride(0)
+        a.residual = _ptr(residual)
+        a.residual_row_stride = residual.stride(0) if residual is not None else 0
+        a.overlap = 1 if self.overlap_branches else 0
+        _lib.check(_lib.load().lsvd_ffn_decode(C.byref(a), _stream_ptr(x)))
         return out.view(*shape[:-1], self.d_out)
+
+    def _chain(self, m: int, device):
+        """Argument block and workspace of ``lsvd_ffn_decode`` for m tokens (kept, so a call allocates nothing)."""
+        key = (m, str(device))
+        got = self._chains.get(key)
+        if got is not None:
+            return got
+        lib = _lib.load()
+        for t in (self.U_q, self.Vg_q, self.Vu_q, self.Wg_q, self.Wu_q, self.Wd_q):
+            if not t.is_contiguous():
+                raise ValueError("weights must be contiguous")
+        a = _lib.FfnDecodeArgs()
+        a.m, a.d_in, a.d_ffn, a.d_out, a.rank, a.n_svd = m, self.d_in, self.d_ffn, self.d_out, self.rank, self.n_svd
+        a.K, a.online_had = self.K, 1 if self.online_had else 0
+        a.had_sign = _ptr(self.had_sign)
+        for name in ("U", "Vg", "Vu", "Wg", "Wu", "Wd"):
+            setattr(a, name + "_q", getattr(self, name + "_q").data_ptr())
+            setattr(a, name + "_s", getattr(self, name + "_s").data_ptr())
+        if self.online_had and self.K > 1:
+            if self.had_K_packed is None:
+                self.had_K_packed = hadamard_pack(self.had_K)
+            a.had_K_packed = self.had_K_packed.data_ptr()
+        ws = torch.empty(int(lib.lsvd_ffn_decode_workspace_bytes(m, self.d_in, self.d_ffn, self.rank)), dtype=torch.uint8,
+                         device=device)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        got = (a, ws)
+        self._chains[key] = got
+        return got
 
     @torch.no_grad()
     def forward_prefill(self, x2: torch.Tensor, out: Optional[torch.Tensor] = None, norm_weight=None, norm_eps: float = 1e-6,
@@ -364,15 +374,6 @@ class HybridFFN(nn.Module):
             out = torch.empty(m, self.d_out, dtype=torch.float16, device=dev)
         i8gemm(h_q, h_s, self.Wd_q, self.Wd_s, out=out, residual=residual)
         return out
-
-    def _side(self, device):
-        key = str(device)
-        got = self._side_streams.get(key)
-        if got is None:
-            with torch.cuda.device(device):
-                got = (torch.cuda.Stream(), torch.cuda.Event(), torch.cuda.Event())
-            self._side_streams[key] = got
-        return got
 
 
 def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_col=0, want_acc=False, want_out=True,
