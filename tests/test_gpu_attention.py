@@ -111,3 +111,10 @@ def test_softmax_shift_invariance_full_size():
     c2["max_len"] = 2 * L
     o2 = U.run_gpu(c2)
     assert rel_to_norm(o2.float(), o1.float()) < TIGHT
+
+
+def test_13b_shape_heads():
+    """BASELINE config 4's attention shape: 40 heads x 128, ragged ranks, three requests."""
+    kr = synth.ragged_ranks(40, 64, seed=7)
+    vr = synth.ragged_ranks(40, 64, seed=8)
+    check(U.build_case(3, 40, 128, kr, vr, [513, 64, 1000], seed=9, shuffle=True))

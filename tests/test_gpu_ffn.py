@@ -234,3 +234,32 @@ def test_prefill_form_equals_decode_form_row_by_row(m):
     xb = xs.repeat(reps, 1)
     yb = small(xb)
     assert torch.equal(yb[:xs.shape[0]], small(xs))
+
+
+def test_13b_shape_chain_hadamard_108_x_128():
+    """BASELINE config 4's FFN shape: hidden 5120, intermediate 13824 = 108 x 128 (had_K of order 108), rank 640, half
+    of the channels on the SVD branch, no input rotation (5120 is not a power of two: the model's residual rotation is
+    folded into the weights offline)."""
+    g = load_golden("hadamard")
+    hk = unpack_had(g["had108_bits"], 108)
+    w = synth.ffn_weights(5120, 13824, 640, 6912, seed=4, had_K=hk, K=108, input_had=False)
+    gen = torch.Generator().manual_seed(13)
+    x = torch.randn(8, 5120, generator=gen).half()
+    ffn = HybridFFN(to_dev(w))
+    st = ffn.forward_stages(x.cuda(), want_acc=True)
+    st = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
+    ref = offn.hybrid_ffn_stages(x, w)
+    assert torch.equal(st["x_q"], ref["x_q"]) and torch.equal(st["lat_acc"], ref["lat_acc"])
+    assert torch.equal(st["g_svd_acc"], ref["g_svd_acc"]) and torch.equal(st["u_rtn_acc"], ref["u_rtn_acc"])
+    y_ref = offn.hadamard_full(st["h16"], hk, 108)
+    assert (st["h_rot"].float() - y_ref.float()).abs().max() <= 2 ** -10 * y_ref.float().abs().max()
+    hq_ref, hs_ref = quant.act_quant(st["h_rot"])
+    assert torch.equal(st["h_q"], hq_ref) and torch.equal(st["h_s"], hs_ref)
+    assert torch.equal(st["out_acc"], offn._i32_matmul(st["h_q"], w["Wd_q"]))
+    y = ffn(x.cuda()).cpu()
+    assert torch.equal(y, st["out"])
+    assert rel_to_norm(y.float(), ref["out"].float()) < TOL
+    # prefill form of the same module (tokens beyond 64)
+    xb = torch.randn(80, 5120, generator=gen).half().cuda()
+    yb = ffn(xb)
+    assert torch.equal(yb[:64], ffn(xb[:64])) and torch.equal(yb[64:], ffn(xb[64:]))
