@@ -224,7 +224,8 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
   const __half* vsc = p.scale_v + h;
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
   const float step = p.qstep[b * p.num_heads + h];
-  const int64_t kstride = p.cache_k_row_stride, vstride = p.cache_v_row_stride;
+  // row strides fit 32 bits (checked by the host): a row address is one 32 x 32 + 64-bit multiply-add
+  const uint32_t kstride = static_cast<uint32_t>(p.cache_k_row_stride), vstride = static_cast<uint32_t>(p.cache_v_row_stride);
 
   __syncwarp();
   {
@@ -274,7 +275,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int slot = __shfl_sync(0xffffffffu, rslot, g + 8 * j);
-      const int8_t* row = kbase + slot * kstride;
+      const int8_t* row = kbase + static_cast<uint64_t>(static_cast<uint32_t>(slot)) * kstride;
 #pragma unroll
       for (int kb = 0; kb < 4; ++kb) {
         ka[j][kb] = make_uint2(0u, 0u);
@@ -302,7 +303,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int slot = __shfl_sync(0xffffffffu, rslot, t4 * 8 + i);
-      const int8_t* row = vbase + slot * vstride;
+      const int8_t* row = vbase + static_cast<uint64_t>(static_cast<uint32_t>(slot)) * vstride;
       va[i] = vb[i] = make_uint2(0u, 0u);
       if (v_ok0) va[i] = ldg64(row);
       if (v_ok1) vb[i] = ldg64(row + 64);
@@ -688,6 +689,7 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
   if (!aligned(a->cache_k, 16) || !aligned(a->cache_v, 16) || (a->cache_k_row_stride % 16) != 0 ||
       (a->cache_v_row_stride % 16) != 0 || a->cache_k_row_stride < sum_rk || a->cache_v_row_stride < sum_rv)
     return LSVD_ERR_INVALID_ARG;
+  if (a->cache_k_row_stride > 0x7fffffffLL || a->cache_v_row_stride > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
   if (a->scale_k_row_stride < a->num_heads || a->scale_v_row_stride < a->num_heads) return LSVD_ERR_INVALID_ARG;
   if (!aligned(a->q, 2) || !aligned(a->up_k, 2) || !aligned(a->scale_k, 2) || !aligned(a->scale_v, 2))
     return LSVD_ERR_INVALID_ARG;
