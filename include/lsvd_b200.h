@@ -349,6 +349,10 @@ typedef struct lsvd_i8gemm_args {
   int32_t gate_col;              /*   whose gate was computed before, with other activations)          */
   const void* residual;          /* single product only, optional device fp16 [m, n]: fp16 add         */
   int64_t residual_row_stride;
+  const int8_t* a2;              /* gate/up pair only, optional: the up matrix' own activations [m, k]  */
+  int64_t a2_row_stride;         /*   (the SVD branch: gate and up read different latents)              */
+  const float* a2_scale;
+  int64_t a2_scale_stride;
 } lsvd_i8gemm_args;
 int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* args, void* stream);
 

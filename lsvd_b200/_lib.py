@@ -132,6 +132,7 @@ class I8GemmArgs(C.Structure):
         ("acc_out", C.c_void_p), ("status_word", C.c_void_p),
         ("a_scale_stride", C.c_int64), ("gate", C.c_void_p), ("gate_row_stride", C.c_int64), ("gate_col", C.c_int32),
         ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
+        ("a2", C.c_void_p), ("a2_row_stride", C.c_int64), ("a2_scale", C.c_void_p), ("a2_scale_stride", C.c_int64),
     ]
 
 

@@ -22,11 +22,11 @@
 
 namespace lsvd {
 
-constexpr int kBM = 128, kBN = 256, kBK = 128, kStages = 4;
+constexpr int kBM = 128, kBN = 256, kBK = 128, kMaxStages = 4;
 constexpr int kATile = kBM * kBK, kBTile = kBN * kBK;                     // bytes (int8)
 constexpr int kEpiWarps = 8;                                               // two per quarter of the TMEM lanes
 constexpr int kGemmThreads = 64 + kEpiWarps * 32;                          // producer, MMA issuer, epilogue warps
-constexpr int kGemmSmem = kStages * (kATile + kBTile) + 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * kBN * 4 /*scales*/;
+constexpr int kGemmSmem = kMaxStages * (kATile + kBTile) + 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * kBN * 4 /*scales*/;
 constexpr uint32_t kTmemCols = 512;                                        // two accumulators of kBN columns
 
 struct GemmParams {
@@ -45,6 +45,9 @@ struct GemmParams {
   int32_t* acc_out;          // optional raw accumulators [m, n] (single-matrix form only)
   int32_t* status_word;
   int32_t m, n, k, dual;     // dual: the B tile is 128 gate channels followed by their 128 up channels
+  int32_t split;             // dual with separate activations for the up half: a second A tile per stage, two N = 128 MMAs
+  const float* a2_scale;
+  int64_t a2_scale_stride;
   int32_t m_tiles, n_tiles;
 };
 
@@ -88,6 +91,8 @@ __device__ __forceinline__ uint64_t smem_desc_k_major_sw128(const void* tile) {
 }
 // Instruction descriptor: D = S32 (2 at bit 4), A = S8 (1 at bit 7), B = S8 (1 at bit 10), both K-major,
 // N >> 3 at bit 17, M >> 4 at bit 24.
+constexpr uint32_t kIdescHalf = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>((kBN / 2) >> 3) << 17) |
+                                (static_cast<uint32_t>(kBM >> 4) << 24);
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBN >> 3) << 17) |
                             (static_cast<uint32_t>(kBM >> 4) << 24);
 
@@ -104,15 +109,18 @@ __device__ __forceinline__ void load8_halves(__half (&dst)[8], const __half* src
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
-i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ GemmParams p) {
+i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a2,
+                      const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b2,
+                      const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sA = tiles;
-  uint8_t* sB = tiles + kStages * kATile;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + kStages * (kATile + kBTile));
-  uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* acc_full = empty_bar + kStages;        // [2] accumulator ready for the epilogue
+  // a stage: [A tile][second A tile, split form only][B tile]; 4 stages of 48 KB or 3 of 64 KB
+  const int kStages = p.split ? 3 : 4;
+  const int a_tiles = p.split ? 2 : 1;
+  const int stage_bytes = a_tiles * kATile + kBTile;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + kMaxStages * (kATile + kBTile));
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* acc_full = empty_bar + kMaxStages;     // [2] accumulator ready for the epilogue
   uint64_t* acc_empty = acc_full + 2;              // [2] accumulator drained by the epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -155,14 +163,17 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             *abort_flag = 1;
             break;
           }
-          mbar_arrive_expect_tx(&full_bar[s], kATile + kBTile);
-          tma_load_2d(sA + s * kATile, &tm_a, kk * kBK, m0, &full_bar[s]);
+          uint8_t* stA = tiles + s * stage_bytes;
+          uint8_t* stB = stA + a_tiles * kATile;
+          mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
+          tma_load_2d(stA, &tm_a, kk * kBK, m0, &full_bar[s]);
+          if (p.split) tma_load_2d(stA + kATile, &tm_a2, kk * kBK, m0, &full_bar[s]);
           if (p.dual) {
-            tma_load_2d(sB + s * kBTile, &tm_b, kk * kBK, n0, &full_bar[s]);
-            tma_load_2d(sB + s * kBTile + kBTile / 2, &tm_b2, kk * kBK, n0, &full_bar[s]);
+            tma_load_2d(stB, &tm_b, kk * kBK, n0, &full_bar[s]);
+            tma_load_2d(stB + kBTile / 2, &tm_b2, kk * kBK, n0, &full_bar[s]);
           } else {
-            tma_load_2d(sB + s * kBTile, &tm_b, kk * kBK, n0, &full_bar[s]);
-            tma_load_2d(sB + s * kBTile + kBTile / 2, &tm_b, kk * kBK, n0 + kBN / 2, &full_bar[s]);
+            tma_load_2d(stB, &tm_b, kk * kBK, n0, &full_bar[s]);
+            tma_load_2d(stB + kBTile / 2, &tm_b, kk * kBK, n0 + kBN / 2, &full_bar[s]);
           }
         }
         if (*abort_flag) break;
@@ -189,12 +200,27 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             break;
           }
           tc_fence_after();
-          const uint64_t adesc = smem_desc_k_major_sw128(sA + s * kATile);
-          const uint64_t bdesc = smem_desc_k_major_sw128(sB + s * kBTile);
+          const uint8_t* stA = tiles + s * stage_bytes;
+          const uint8_t* stB = stA + a_tiles * kATile;
+          const uint64_t adesc = smem_desc_k_major_sw128(stA);
+          const uint64_t bdesc = smem_desc_k_major_sw128(stB);
+          if (!p.split) {
 #pragma unroll
-          for (int q = 0; q < kBK / 32; ++q)         // 32 int8 of K per instruction: 32 bytes further inside the swizzled row
-            umma_i8(tmem_d, adesc + static_cast<uint64_t>(q * 32 >> 4), bdesc + static_cast<uint64_t>(q * 32 >> 4), kIdesc,
-                    (kk > 0 || q > 0) ? 1u : 0u);
+            for (int q = 0; q < kBK / 32; ++q)       // 32 int8 of K per instruction: 32 bytes further inside the swizzled row
+              umma_i8(tmem_d, adesc + static_cast<uint64_t>(q * 32 >> 4), bdesc + static_cast<uint64_t>(q * 32 >> 4), kIdesc,
+                      (kk > 0 || q > 0) ? 1u : 0u);
+          } else {
+            // gate half: A x B rows 0..127 into columns 0..127; up half: second A x B rows 128..255 into columns 128..255
+            const uint64_t a2desc = smem_desc_k_major_sw128(stA + kATile);
+            const uint64_t b2desc = smem_desc_k_major_sw128(stB + kBTile / 2);
+#pragma unroll
+            for (int q = 0; q < kBK / 32; ++q) {
+              const uint64_t off = static_cast<uint64_t>(q * 32 >> 4);
+              const uint32_t accumulate = (kk > 0 || q > 0) ? 1u : 0u;
+              umma_i8(tmem_d, adesc + off, bdesc + off, kIdescHalf, accumulate);
+              umma_i8(tmem_d + kBN / 2, a2desc + off, b2desc + off, kIdescHalf, accumulate);
+            }
+          }
           umma_commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
         }
         umma_commit(&acc_full[buf]);                 // arrives when every MMA above has finished (also after an abort)
@@ -236,6 +262,7 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.m;
       const float sa = row_ok ? p.a_scale[row * p.a_scale_stride] : 0.f;
+      const float sa2 = (row_ok && p.split) ? p.a2_scale[row * p.a2_scale_stride] : sa;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * kBN);
       __half* orow = p.out != nullptr ? p.out + static_cast<int64_t>(row) * p.out_row_stride + p.out_col : nullptr;
       const __half* grow = p.gate != nullptr ? p.gate + static_cast<int64_t>(row) * p.gate_row_stride + p.gate_col : nullptr;
@@ -282,7 +309,7 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           if (p.dual) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              const __half u16 = __float2half_rn((static_cast<float>(static_cast<int>(u[j0 + e])) * sa) * cs[kBN / 2 + c * 32 + j0 + e]);
+              const __half u16 = __float2half_rn((static_cast<float>(static_cast<int>(u[j0 + e])) * sa2) * cs[kBN / 2 + c * 32 + j0 + e]);
               const __half sg = __float2half_rn(silu_pf(__half2float(r[e])));
               r[e] = __float2half_rn(__half2float(sg) * __half2float(u16));
             }
@@ -336,8 +363,13 @@ extern "C" int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* a, void* stream) {
   if (!aligned(a->a, 16) || (a->a_row_stride % 16) || !aligned(a->w, 16) || (a->w_row_stride % 16)) return LSVD_ERR_INVALID_ARG;
   if (dual && (!aligned(a->w2, 16) || (a->w2_row_stride % 16))) return LSVD_ERR_INVALID_ARG;
   if (a->out && (!aligned(a->out, 4) || (a->out_row_stride % 2) || (a->out_col % 2))) return LSVD_ERR_INVALID_ARG;
-  CUtensorMap ma, mb, mb2;
+  const bool split = dual && a->a2 != nullptr;
+  if (a->a2 != nullptr && !dual) return LSVD_ERR_INVALID_ARG;
+  if (split && (!a->a2_scale || !aligned(a->a2, 16) || (a->a2_row_stride % 16))) return LSVD_ERR_INVALID_ARG;
+  CUtensorMap ma, ma2, mb, mb2;
   int rc = make_map_k128(&ma, a->a, a->m, a->k, a->a_row_stride, kBM);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&ma2, split ? a->a2 : a->a, a->m, a->k, split ? a->a2_row_stride : a->a_row_stride, kBM);
   if (rc != LSVD_OK) return rc;
   rc = make_map_k128(&mb, a->w, a->n, a->k, a->w_row_stride, kBN / 2);
   if (rc != LSVD_OK) return rc;
@@ -359,6 +391,9 @@ extern "C" int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* a, void* stream) {
   p.acc_out = a->acc_out;
   p.status_word = a->status_word;
   p.m = a->m; p.n = a->n; p.k = a->k; p.dual = dual ? 1 : 0;
+  p.split = split ? 1 : 0;
+  p.a2_scale = a->a2_scale;
+  p.a2_scale_stride = a->a2_scale_stride > 0 ? a->a2_scale_stride : 1;
   const int ntile = dual ? kBN / 2 : kBN;
   p.m_tiles = (a->m + kBM - 1) / kBM;
   p.n_tiles = (a->n + ntile - 1) / ntile;
@@ -366,7 +401,7 @@ extern "C" int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* a, void* stream) {
   if (tiles > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
   LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(i8gemm_tcgen05_kernel), kGemmSmem));
   const int grid = static_cast<int>(std::min<int64_t>(tiles, std::max(1, device_sm_count())));
-  i8gemm_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmem, static_cast<cudaStream_t>(stream)>>>(ma, mb, mb2, p);
+  i8gemm_tcgen05_kernel<<<grid, kGemmThreads, kGemmSmem, static_cast<cudaStream_t>(stream)>>>(ma, ma2, mb, mb2, p);
   LSVD_CUDA_TRY(cudaGetLastError());
   return LSVD_OK;
 }

@@ -351,9 +351,8 @@ class HybridFFN(nn.Module):
     def forward_prefill(self, x2: torch.Tensor, out: Optional[torch.Tensor] = None, norm_weight=None, norm_eps: float = 1e-6,
                         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The same block for prefill-sized batches ``x2 [m, d_in]``: the quantisers as in decode, every product on
-        the tcgen05 GEMM (``i8gemm``).  The SVD branch's gate and up products have different activations (their own
-        latents): the gate product writes its fp16 values into the hidden buffer and the up product's epilogue
-        gates them in place.  Bit-identical to the decode form row by row."""
+        the tcgen05 GEMM (``i8gemm``); the SVD branch's gate and up products, which read different latents, are one
+        launch with two activation tiles per stage.  Bit-identical to the decode form row by row."""
         m = x2.shape[0]
         r, dev = self.rank, x2.device
         x_q, x_s, _ = act_quant(x2, sign=self.had_sign, norm_weight=norm_weight, norm_eps=norm_eps)
@@ -361,8 +360,8 @@ class HybridFFN(nn.Module):
         z_q, z_s, _ = act_quant(lat16.view(2 * m, r))
         z_q, z_s = z_q.view(m, 2 * r), z_s.view(m, 2)
         h16 = torch.empty(m, self.d_ffn, dtype=torch.float16, device=dev)
-        i8gemm(z_q[:, :r], z_s[:, 0], self.Vg_q, self.Vg_s, out=h16, out_col=0)
-        i8gemm(z_q[:, r:], z_s[:, 1], self.Vu_q, self.Vu_s, out=h16, out_col=0, gate=h16, gate_col=0)
+        i8gemm(z_q[:, :r], z_s[:, 0], self.Vg_q, self.Vg_s, self.Vu_q, self.Vu_s, out=h16, out_col=0,
+               a2_q=z_q[:, r:], a2_scale=z_s[:, 1])
         i8gemm(x_q, x_s, self.Wg_q, self.Wg_s, self.Wu_q, self.Wu_s, out=h16, out_col=self.n_svd)
         if self.online_had and self.K > 1:
             if self.had_K_packed is None:
@@ -377,11 +376,11 @@ class HybridFFN(nn.Module):
 
 
 def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_col=0, want_acc=False, want_out=True,
-           status_word=None, gate=None, gate_col=0, residual=None):
+           status_word=None, gate=None, gate_col=0, residual=None, a2_q=None, a2_scale=None):
     """W8A8 product for any number of tokens on the tcgen05 tensor cores (prefill-sized batches): the same values
     as ``w8a8_gemv``.  ``gate`` (fp16, columns gate_col.. of it) turns a single product into the up half of a gate/up
-    pair whose gate came from other activations; ``residual`` is added in fp16.  Returns (out fp16 or None, acc int32
-    or None)."""
+    pair whose gate came from other activations; ``residual`` is added in fp16; ``a2_q`` / ``a2_scale`` give the up
+    matrix of a pair its own activations.  Returns (out fp16 or None, acc int32 or None)."""
     _require_cuda(a_q, w_q)
     m, k = a_q.shape
     n = w_q.shape[0]
@@ -399,6 +398,9 @@ def i8gemm(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, out=None, out_c
         g.residual, g.residual_row_stride = residual.data_ptr(), residual.stride(0)
     if w2_q is not None:
         g.w2, g.w2_row_stride, g.w2_scale = w2_q.data_ptr(), w2_q.stride(0), w2_scale.data_ptr()
+    if a2_q is not None:
+        g.a2, g.a2_row_stride = a2_q.data_ptr(), a2_q.stride(0)
+        g.a2_scale, g.a2_scale_stride = a2_scale.data_ptr(), a2_scale.stride(0)
     if out is not None:
         g.out, g.out_row_stride, g.out_col = out.data_ptr(), out.stride(0), out_col
     g.acc_out = _ptr(acc)

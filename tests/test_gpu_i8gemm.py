@@ -80,3 +80,26 @@ def test_gated_up_product_and_residual():
     s2 = torch.stack([sa, sa * 3], 1).contiguous().cuda()
     out3, _ = i8gemm(a.cuda(), s2[:, 1], wu.cuda(), su.cuda())
     assert torch.equal(out3.cpu(), offn._dequant16(offn._i32_matmul(a, wu), sa * 3, su))
+
+
+def test_gate_up_pair_with_separate_activations():
+    """The SVD branch's form: the up matrix reads its own activations (and row scales with a stride)."""
+    m, n, k = 300, 688, 512
+    a, wg, sa, sg = _rand(m, n, k, 21)
+    a2, wu, sa2, su = _rand(m, n, k, 22)
+    wg = (wg.float() / 6).round().to(torch.int8)
+    wu = (wu.float() / 6).round().to(torch.int8)
+    sg, su = sg * 0.2, su * 0.2
+    z = torch.cat([a, a2], 1).contiguous().cuda()                       # [m, 2k]: the two latents side by side
+    zs = torch.stack([sa, sa2], 1).contiguous().cuda()                  # [m, 2]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, _ = i8gemm(z[:, :k], zs[:, 0], wg.cuda(), sg.cuda(), wu.cuda(), su.cuda(), a2_q=z[:, k:], a2_scale=zs[:, 1],
+                    status_word=status)
+    assert status.item() == 0
+    g = offn._dequant16(offn._i32_matmul(a, wg), sa, sg)
+    u = offn._dequant16(offn._i32_matmul(a2, wu), sa2, su)
+    ref = offn.silu_mul16(g, u)
+    d = (out.cpu().float() - ref.float()).abs()
+    assert (d == 0).float().mean() > 0.999 and d.max() <= 2 ** -10 * ref.float().abs().max()
+    out64, _, _ = w8a8_gemv(z[:64, :k], zs[:64, 0], wg.cuda(), sg.cuda(), wu.cuda(), su.cuda(), a2_q=z[:64, k:], a2_scale=zs[:64, 1])
+    assert torch.equal(out64.cpu(), out[:64].cpu())
