@@ -4,7 +4,7 @@
 // A decode GEMV is a pure HBM stream, and on this part a stream only runs at full rate with on the order of
 // 100 KB in flight per SM: more than the register file can hold as load destinations.  So the loads go
 // through shared memory.  One persistent block per SM walks its share of the 16-row tiles; a producer warp
-// (one elected lane) issues tiled TMA copies (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) of the
+// (one elected lane) issues tiled TMA copies (cp.async.bulk.tensor.2d, 128-byte swizzle, every block loads its own tiles) of the
 // next 1 KB of K of the tile's rows of every weight matrix and of the token rows into a ring of stages; eight
 // consumer warps each take one 128-byte chunk of the stage, read it with conflict-free 16-byte shared loads in
 // MMA fragment order and accumulate; after the last stage of a tile their shares are summed through shared

@@ -2,7 +2,7 @@
 //   acc[m, n] = sum_k a[m, k] * w[n, k]   (int8 x int8 -> int32, exact), dequantised to fp16 in the epilogue.
 //
 // Persistent: one block per SM walks 128 (tokens) x 256 (channels) tiles.  Warp 0 (one elected lane) streams the
-// A and B tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a four-stage shared-memory
+// A and B tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, every block loads its own tiles) into a four-stage shared-memory
 // ring; warp 1 (one elected lane) issues tcgen05.mma kind::i8 (M 128, N 256, K 32 per instruction) into one of
 // two accumulators in tensor memory (2 x 256 columns of 32 bits, allocated by warp 1); tcgen05.commit hands each
 // ring stage back to the producer and, after a tile's last MMA, hands the accumulator to the eight epilogue warps,
