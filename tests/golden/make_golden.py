@@ -26,7 +26,9 @@ import importlib.abc
 import importlib.machinery
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LSVD_REFERENCE", "")
+if not os.path.isdir(REF):
+    sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of SAI-Lab-NYU/LSVD>  (or set LSVD_REFERENCE)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 import numpy as np
