@@ -259,6 +259,22 @@ int lsvd_hadamard_quant(const lsvd_hadamard_quant_args* args, void* stream);
 size_t lsvd_hadamard_packed_bytes(int32_t K);
 int lsvd_hadamard_pack(const void* had_K, int32_t K, void* packed, void* stream);
 
+/* Hadamard across heads followed by per-token int8 quantisation: a row [heads * head_dim] is seen as
+ * [heads][head_dim] and every column is transformed over its `heads` entries (a power of two up to 64), scale
+ * 1 / sqrt(heads), fp32 inside and fp16 out; then the row is quantised as in lsvd_act_quant.  The online
+ * rotation in front of o_proj: ActQuantWrapper.forward with online_partial_had and K == 1
+ * (fake_quant/utils/quant_utils.py:302-322).  head_dim even, <= 256. */
+typedef struct lsvd_heads_hadamard_quant_args {
+  int32_t rows, heads, head_dim;
+  const void* x;                 /* device fp16 [rows, heads * head_dim]                            */
+  int64_t x_row_stride;
+  int8_t* q;                     /* device int8 [rows, heads * head_dim]                            */
+  int64_t q_row_stride;
+  float* scale;                  /* device fp32 [rows]                                              */
+  void* y;                       /* optional device fp16 [rows, heads * head_dim] (contiguous): the rotated row */
+} lsvd_heads_hadamard_quant_args;
+int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* args, void* stream);
+
 /* Weight-streaming W8A8 product for 1..64 tokens: acc[m, n] = sum_k a[m, k] * w[n, k] (int32, exact),
  * optionally for a second weight matrix w2 (with its own activations a2, or the same ones) in the same pass.
  *   epilogue 0: out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n])              (a quantised Linear)
@@ -282,9 +298,11 @@ typedef struct lsvd_gemv_args {
   int64_t residual_row_stride;
   int32_t* status_word;          /* device int32 or NULL: LSVD_ERR_TIMEOUT if a pipeline wait of the   */
                                  /* TMA-fed form ran out; the output is then incomplete               */
-  int32_t form;                  /* 0: register-fed kernel (default, the faster one so far);           */
-                                 /* 1: persistent TMA-fed kernel, m <= 16 only (LSVD_ERR_UNSUPPORTED   */
-                                 /*    beyond); same values                                            */
+  int32_t form;                  /* 0: chosen by batch size (register-fed up to 16 tokens, 2 beyond);   */
+                                 /* 1: persistent TMA-fed kernel with K split over warps, m <= 16 only   */
+                                 /*    (LSVD_ERR_UNSUPPORTED beyond); 2: TMA-fed kernel whose warps      */
+                                 /*    share the token rows (built for 17..64 tokens, valid for any m);   */
+                                 /* 3: register-fed kernel for any m.  Same values in every form.        */
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 

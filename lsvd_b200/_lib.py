@@ -94,6 +94,14 @@ class HadamardQuantArgs(C.Structure):
     ]
 
 
+class HeadsHadamardQuantArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("x", C.c_void_p), ("x_row_stride", C.c_int64), ("q", C.c_void_p), ("q_row_stride", C.c_int64),
+        ("scale", C.c_void_p), ("y", C.c_void_p),
+    ]
+
+
 class GemvArgs(C.Structure):
     _fields_ = [
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
@@ -146,6 +154,7 @@ SIGNATURES = {
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_static_scratch_bytes": (C.c_size_t, []),
     "lsvd_attn_decode_static": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
+    "lsvd_heads_hadamard_quant": (C.c_int, [C.POINTER(HeadsHadamardQuantArgs), C.c_void_p]),
     "lsvd_ffn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 4),
     "lsvd_ffn_decode": (C.c_int, [C.POINTER(FfnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_rope_workspace_bytes": (C.c_size_t, [C.c_int32] * 6),

@@ -253,6 +253,72 @@ __global__ void __launch_bounds__(256) act_quant_rot4096_kernel(const __grid_con
 }
 
 // ----------------------------------------------------------------------------------------------
+// Hadamard across heads + per-token quantisation (the online rotation in front of o_proj)
+// ----------------------------------------------------------------------------------------------
+// A row is [H][D]; every column d is transformed over its H entries (H a power of two), scale 1 / sqrt(H), fp16
+// rounding, then the row is quantised like any activation.  A thread owns two adjacent columns and keeps their
+// 2 H entries in registers: the butterflies need no exchange at all.
+struct HeadsHadParams {
+  const __half* x;
+  int64_t x_row_stride;
+  int8_t* q;
+  int64_t q_row_stride;
+  float* scale;
+  __half* y;
+  int32_t rows, heads, head_dim;
+  float rot_scale;
+};
+
+template <int H>
+__global__ void __launch_bounds__(128) heads_hadamard_quant_kernel(const __grid_constant__ HeadsHadParams p) {
+  __shared__ float red[8];
+  grid_dependency_sync();
+  const int r = blockIdx.x, D = p.head_dim;
+  const __half* x = p.x + r * p.x_row_stride;
+  const int c = 2 * threadIdx.x;                  // columns c, c + 1
+  const bool on = c < D;
+  float e0[H], e1[H];
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    e0[h] = e1[h] = 0.f;
+    if (on) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(x + h * D + c));
+      e0[h] = f.x;
+      e1[h] = f.y;
+    }
+  }
+#pragma unroll
+  for (int s = 1; s < H; s <<= 1)
+#pragma unroll
+    for (int h = 0; h < H; ++h)
+      if ((h & s) == 0) {
+        const float a0 = e0[h], b0 = e0[h + s], a1 = e1[h], b1 = e1[h + s];
+        e0[h] = a0 + b0; e0[h + s] = a0 - b0;
+        e1[h] = a1 + b1; e1[h + s] = a1 - b1;
+      }
+  float amax = 0.f;
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    e0[h] = __half2float(__float2half_rn(e0[h] * p.rot_scale));
+    e1[h] = __half2float(__float2half_rn(e1[h] * p.rot_scale));
+    amax = fmaxf(amax, fmaxf(fabsf(e0[h]), fabsf(e1[h])));
+  }
+  amax = block_max(amax, red);
+  const float s = act_scale_of(amax);
+  if (threadIdx.x == 0) p.scale[r] = s;
+  if (!on) return;
+  int8_t* q = p.q + r * p.q_row_stride;
+#pragma unroll
+  for (int h = 0; h < H; ++h) {
+    const uint16_t packed = static_cast<uint16_t>(static_cast<uint8_t>(act_code(e0[h], s))) |
+                            (static_cast<uint16_t>(static_cast<uint8_t>(act_code(e1[h], s))) << 8);
+    *reinterpret_cast<uint16_t*>(q + h * D + c) = packed;
+    if (p.y != nullptr)
+      *reinterpret_cast<__half2*>(p.y + static_cast<int64_t>(r) * H * D + h * D + c) = __floats2half2_rn(e0[h], e1[h]);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
 // (H_K kron H_nb) rotation + per-token quantisation: a thread-block cluster per token
 // ----------------------------------------------------------------------------------------------
 // y[k', j] = sum_k had_K[k', k] * fwht(x[k, :])[j] / sqrt(cols).  The blocks of a cluster split the nb
@@ -788,6 +854,33 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   return LSVD_OK;
 }
 
+extern "C" int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* a, void* stream) {
+  using namespace lsvd;
+  if (a == nullptr || a->rows < 0 || a->heads <= 1 || a->head_dim <= 0 || (a->head_dim % 2) || a->head_dim > 256)
+    return LSVD_ERR_INVALID_ARG;
+  if (a->rows == 0) return LSVD_OK;
+  if (!a->x || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
+  if (!aligned(a->x, 4) || (a->x_row_stride % 2) || !aligned(a->q, 2) || (a->q_row_stride % 2) || (a->y && !aligned(a->y, 4)))
+    return LSVD_ERR_INVALID_ARG;
+  HeadsHadParams p{};
+  p.x = static_cast<const __half*>(a->x); p.x_row_stride = a->x_row_stride;
+  p.q = a->q; p.q_row_stride = a->q_row_stride; p.scale = a->scale; p.y = static_cast<__half*>(a->y);
+  p.rows = a->rows; p.heads = a->heads; p.head_dim = a->head_dim;
+  p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->heads)));
+  void (*kern)(HeadsHadParams) = nullptr;
+  switch (a->heads) {
+    case 2: kern = heads_hadamard_quant_kernel<2>; break;
+    case 4: kern = heads_hadamard_quant_kernel<4>; break;
+    case 8: kern = heads_hadamard_quant_kernel<8>; break;
+    case 16: kern = heads_hadamard_quant_kernel<16>; break;
+    case 32: kern = heads_hadamard_quant_kernel<32>; break;
+    case 64: kern = heads_hadamard_quant_kernel<64>; break;
+    default: return LSVD_ERR_UNSUPPORTED;       // a head count that is not a power of two needs the had_K form
+  }
+  LSVD_CUDA_TRY(launch_chained(kern, dim3(a->rows), dim3(128), 0, static_cast<cudaStream_t>(stream), 1, false, p));
+  return LSVD_OK;
+}
+
 extern "C" size_t lsvd_hadamard_packed_bytes(int32_t K) {
   if (K <= 1 || K > 256) return 0;
   const size_t tiles = (static_cast<size_t>(K) + 15) / 16;
@@ -884,7 +977,10 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   p.m = a->m; p.n = a->n; p.k = a->k; p.epilogue = a->epilogue;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->form == 1) return a->m <= 16 ? launch_gemv_streamed(p, dual, split, st) : LSVD_ERR_UNSUPPORTED;
-  if (a->form != 0) return LSVD_ERR_INVALID_ARG;
+  if (a->form == 2) return launch_gemv_wide(p, dual, split, st);
+  if (a->form != 0 && a->form != 3) return LSVD_ERR_INVALID_ARG;
+  // more than 16 tokens: the form that shares the token rows between a block's warps
+  if (a->form == 0 && a->m > 16) return launch_gemv_wide(p, dual, split, st);
   if (a->m <= 8) return launch_gemv_nt<1>(p, dual, split, st);
   if (a->m <= 16) return launch_gemv_nt<2>(p, dual, split, st);
   if (a->m <= 32) return launch_gemv_nt<4>(p, dual, split, st);

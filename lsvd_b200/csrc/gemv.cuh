@@ -19,6 +19,8 @@ struct GemvParams {
 
 // The TMA-fed persistent form (gemv_tma.cu), for at most 16 tokens.
 int launch_gemv_streamed(const GemvParams& p, bool dual, bool split, cudaStream_t st);
+// The TMA-fed form for 17..64 tokens: token rows shared by the block's warps through shared memory.
+int launch_gemv_wide(const GemvParams& p, bool dual, bool split, cudaStream_t st);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,

@@ -173,6 +173,177 @@ w8a8_gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// 17..64 tokens: the token rows are as large as a block's weight rows, so they are shared
+// ----------------------------------------------------------------------------------------------
+// With more tokens the register-fed form re-reads every token row once per 16 output channels (L1-bound:
+// 68 us for the 45 MB gate/up pair at 64 tokens).  Here a block owns up to 64 channels (one consumer warp per 16)
+// and a stage holds 256 bytes of K of those weight rows and of ALL token rows, fetched once per block by TMA;
+// every consumer warp reads the whole token tile from shared memory and only its own weight rows, keeps complete
+// sums for its channels in registers, and stores them itself: no reduction across warps.
+constexpr int kWideStageK = 256;                      // bytes of K per stage: two 128-byte chunks
+constexpr int kWideMaxWarps = 4;
+
+template <int NT, bool DUAL, bool SPLIT_B>
+__global__ void __launch_bounds__((kWideMaxWarps + 1) * 32, 1)
+w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
+                      const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a2,
+                      const __grid_constant__ GemvParams p, const int stages, const int warps) {
+  constexpr int NMAT = DUAL ? 2 : 1;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int rows = warps * 16;                        // channels per block (and matrix)
+  const int w_bytes = 2 * rows * 128;                 // one matrix' rows of a stage: [2 chunks][rows][128]
+  const int a_bytes = 2 * NT * 8 * 128;               // the token rows of a stage: [2 chunks][NT * 8][128]
+  const int stage_bytes = NMAT * w_bytes + (SPLIT_B ? 2 : 1) * a_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * stage_bytes);
+  uint64_t* empty_bar = full_bar + kTgMaxStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], warps);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int tiles = (p.n + rows - 1) / rows;
+  const int ksteps = (p.k + kWideStageK - 1) / kWideStageK;
+
+  if (warp == warps) {
+    // ================= producer =================
+    if (lane == 0) {
+      grid_dependency_wait();
+      int it = 0;
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int row0 = tile * rows;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int s = it % stages;
+          if (!mbar_wait_bounded(&empty_bar[s], ((it / stages) & 1) ^ 1)) {
+            report_status(p.status_word, LSVD_ERR_TIMEOUT);
+            return;
+          }
+          uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
+          mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int k0 = ks * kWideStageK + c * 128;
+            tma_load_2d(st + c * (rows * 128), &tm_w, k0, row0, &full_bar[s]);
+            if (DUAL) tma_load_2d(st + w_bytes + c * (rows * 128), &tm_w2, k0, row0, &full_bar[s]);
+            tma_load_2d(st + NMAT * w_bytes + c * (NT * 8 * 128), &tm_a, k0, 0, &full_bar[s]);
+            if (SPLIT_B) tma_load_2d(st + NMAT * w_bytes + a_bytes + c * (NT * 8 * 128), &tm_a2, k0, 0, &full_bar[s]);
+          }
+        }
+      }
+    }
+    return;
+  }
+  if (warp > warps) return;
+
+  // ================= consumers: warp w owns channels 16 w .. 16 w + 15 of the block's tile =================
+  const int g = lane >> 2, t = lane & 3;
+  int it = 0;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    int acc[NMAT][NT][4];
+#pragma unroll
+    for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0;
+    for (int ks = 0; ks < ksteps; ++ks, ++it) {
+      const int s = it % stages;
+      if (!mbar_wait_bounded(&full_bar[s], (it / stages) & 1)) {
+        report_status(p.status_word, LSVD_ERR_TIMEOUT);
+        return;
+      }
+      const uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint8_t* wc = st + c * (rows * 128) + warp * (16 * 128);        // [16 rows of this warp][128], swizzled
+        const uint8_t* ac = st + NMAT * w_bytes + c * (NT * 8 * 128);         // [NT * 8 tokens][128]
+#pragma unroll
+        for (int sp = 0; sp < 2; ++sp) {
+          const int unit = ((4 * sp + t) ^ g) << 4;
+          const uint4 x0 = lds_u4(wc + g * 128 + unit), x1 = lds_u4(wc + (g + 8) * 128 + unit);
+          uint4 y0 = x0, y1 = x1;
+          if (DUAL) {
+            y0 = lds_u4(wc + w_bytes + g * 128 + unit);
+            y1 = lds_u4(wc + w_bytes + (g + 8) * 128 + unit);
+          }
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const uint4 bv = lds_u4(ac + (j * 8 + g) * 128 + unit);
+            mma_s8(acc[0][j], x0.x, x1.x, x0.y, x1.y, bv.x, bv.y);
+            mma_s8(acc[0][j], x0.z, x1.z, x0.w, x1.w, bv.z, bv.w);
+            if (DUAL) {
+              uint4 bw = bv;
+              if (SPLIT_B) bw = lds_u4(ac + a_bytes + (j * 8 + g) * 128 + unit);
+              mma_s8(acc[NMAT - 1][j], y0.x, y1.x, y0.y, y1.y, bw.x, bw.y);
+              mma_s8(acc[NMAT - 1][j], y0.z, y1.z, y0.w, y1.w, bw.z, bw.w);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    // ---- complete sums of channels (g, g + 8) x tokens (8 j + 2 t, + 1): dequantise and store ----
+    const int row_base = tile * rows + warp * 16;
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int row = row_base + g + 8 * (c >> 1);
+        const int tok = j * 8 + 2 * t + (c & 1);
+        if (row < p.n && tok < p.m) gemv_store<DUAL, SPLIT_B>(p, tok, row, acc[0][j][c], acc[NMAT - 1][j][c]);
+      }
+  }
+}
+
+template <int NT, bool DUAL, bool SPLIT_B>
+static int launch_wide(const GemvParams& p, cudaStream_t st) {
+  constexpr int NMAT = DUAL ? 2 : 1;
+  const int sms = std::max(1, device_sm_count());
+  const int row_tiles = (p.n + 15) / 16;
+  const int warps = std::max(1, std::min(kWideMaxWarps, (row_tiles + sms - 1) / sms));    // 16-channel tiles per block
+  const int rows = warps * 16;
+  CUtensorMap mw, mw2, ma, ma2;
+  int rc = make_map_k128(&mw, p.w, p.n, p.k, p.w_row_stride, rows);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&mw2, DUAL ? p.w2 : p.w, p.n, p.k, DUAL ? p.w2_row_stride : p.w_row_stride, rows);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&ma, p.a, p.m, p.k, p.a_row_stride, NT * 8);
+  if (rc != LSVD_OK) return rc;
+  rc = make_map_k128(&ma2, SPLIT_B ? p.a2 : p.a, p.m, p.k, SPLIT_B ? p.a2_row_stride : p.a_row_stride, NT * 8);
+  if (rc != LSVD_OK) return rc;
+  const int stage_bytes = NMAT * 2 * rows * 128 + (SPLIT_B ? 2 : 1) * 2 * NT * 8 * 128;
+  const int fixed = 1024 + 2 * kTgMaxStages * 8 + 16;
+  const int budget = device_max_smem_optin() - 4096;
+  const int tiles = (p.n + rows - 1) / rows;
+  const int ksteps = (p.k + kWideStageK - 1) / kWideStageK;
+  const int grid = std::min(tiles, sms);
+  const int per_block = ((tiles + grid - 1) / grid) * ksteps;
+  const int stages = std::max(1, std::min(std::min((budget - fixed) / stage_bytes, kTgMaxStages), per_block));
+  if (fixed + stage_bytes > budget) return LSVD_ERR_UNSUPPORTED;
+  const int smem = fixed + stages * stage_bytes;
+  auto kern = w8a8_gemv_wide_kernel<NT, DUAL, SPLIT_B>;
+  LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
+  LSVD_CUDA_TRY(launch_chained(kern, dim3(grid), dim3((kWideMaxWarps + 1) * 32), smem, st, 1, false, mw, mw2, ma, ma2, p,
+                               stages, warps));
+  return LSVD_OK;
+}
+
+int launch_gemv_wide(const GemvParams& p, bool dual, bool split, cudaStream_t st) {
+  if (p.m <= 32) {
+    if (!dual) return launch_wide<4, false, false>(p, st);
+    return split ? launch_wide<4, true, true>(p, st) : launch_wide<4, true, false>(p, st);
+  }
+  if (!dual) return launch_wide<8, false, false>(p, st);
+  return split ? launch_wide<8, true, true>(p, st) : launch_wide<8, true, false>(p, st);
+}
+
 template <int NT, bool DUAL, bool SPLIT_B>
 static int launch_tg(const GemvParams& p, cudaStream_t st) {
   using L = TgLayout<NT, DUAL, SPLIT_B>;

@@ -110,6 +110,23 @@ def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rot
     return q, scale, y
 
 
+def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False):
+    """Hadamard across heads (rows ``[rows, heads * head_dim]``, heads a power of two) + per-token int8 quantisation:
+    the online rotation in front of ``o_proj``.  Returns (codes, scale fp32 [rows], rotated fp16 or None)."""
+    _require_cuda(x)
+    if x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] % heads:
+        raise ValueError("x must be a 2-D fp16 tensor [rows, heads * head_dim] with unit inner stride")
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    y = torch.empty(rows, cols, dtype=torch.float16, device=x.device) if want_rotated else None
+    a = _lib.HeadsHadamardQuantArgs()
+    a.rows, a.heads, a.head_dim = rows, heads, cols // heads
+    a.x, a.x_row_stride, a.q, a.q_row_stride, a.scale, a.y = x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), scale.data_ptr(), _ptr(y)
+    _lib.check(_lib.load().lsvd_heads_hadamard_quant(C.byref(a), _stream_ptr(x)))
+    return q, scale, y
+
+
 def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a2_scale=None, out=None, out_col=0,
               want_acc=False, want_out=True, residual=None, form=0, status_word=None):
     """acc = a_q @ w_q^T (int32, exact) for 1..64 tokens, dequantised to fp16; with (w2, a2) a gate/up pair whose

@@ -43,6 +43,20 @@ def fwht(x: torch.Tensor) -> torch.Tensor:
     return y.reshape(x.shape)
 
 
+def partial_hadamard_heads(x16: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """Hadamard across heads: rows ``[..., H * head_dim]`` seen as ``[H, head_dim]``, each of the head_dim columns
+    transformed over its H entries (H a power of two), scale 1/sqrt(H), fp32 inside and fp16 out.
+
+    fake_quant/utils/quant_utils.py:302-317 with K == 1 (the ``fast_hadamard_transform`` call on the transposed
+    view): the online rotation in front of ``o_proj``.
+    """
+    n = x16.shape[-1]
+    H = n // head_dim
+    x = x16.float().reshape(-1, H, head_dim).transpose(1, 2)          # [.., head_dim, H]
+    y = (fwht(x.contiguous()) * (1.0 / math.sqrt(H))).to(x16.dtype)
+    return y.transpose(1, 2).reshape(x16.shape)
+
+
 def hadamard_full(x16: torch.Tensor, had_K, K: int) -> torch.Tensor:
     """(H_K kron H_{n/K}) x / sqrt(n) on the last axis, with the reference's two fp16 roundings.
 

@@ -319,7 +319,36 @@ def gen_fake_quant_side():
          g_rtn=cap["grtn_out"], u_rtn=cap["urtn_out"], h=cap["down_in"], h_fakeq=cap["downlin_in"], **wts)
 
 
+def gen_partial_hadamard():
+    """ActQuantWrapper with online_partial_had (the Hadamard across heads in front of o_proj,
+    fake_quant/utils/quant_utils.py:302-317) followed by its A8 input quantiser: the tensor the wrapped Linear sees."""
+    for m in [k for k in sys.modules if k == "utils" or k.startswith("utils.")]:
+        del sys.modules[m]
+    sys.path.insert(0, os.path.join(REF, "fake_quant"))
+    import torch.nn as nn
+    from utils import quant_utils
+    g = torch.Generator().manual_seed(5)
+    H, D = 32, 16
+    x = torch.randn(6, H * D, generator=g).half()
+    x[2] = 0
+    lin = nn.Linear(H * D, 8, bias=False).half()
+    wrap = quant_utils.ActQuantWrapper(lin)
+    wrap.online_partial_had, wrap.had_dim, wrap.K = True, D, 1
+    seen = {}
+    lin.register_forward_pre_hook(lambda mod, inp: seen.__setitem__("x", inp[0].detach().clone()))
+    wrap.quantizer.configure(bits=16)
+    wrap(x)
+    rotated = seen["x"]
+    wrap.quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+    wrap(x)
+    save("partial_hadamard", x=x, heads=np.int64(H), head_dim=np.int64(D), rotated=rotated, fake_quant=seen["x"])
+
+
 if __name__ == "__main__":
     with torch.no_grad():
+        if len(sys.argv) > 2 and sys.argv[2] == "partial_hadamard":
+            gen_partial_hadamard()
+            sys.exit(0)
         gen_kernels_side()
         gen_fake_quant_side()
+        gen_partial_hadamard()

@@ -10,7 +10,8 @@ import torch
 from conftest import load_golden, unpack_had, rel_to_norm
 from oracle import ffn as offn, quant
 from lsvd_b200 import synth
-from lsvd_b200.ffn import HybridFFN, act_quant, hadamard_quant, hadamard_pack, w8a8_gemv, quantize_weight_rtn
+from lsvd_b200.ffn import (HybridFFN, act_quant, hadamard_quant, hadamard_pack, w8a8_gemv, quantize_weight_rtn,
+                           heads_hadamard_quant)
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-3
@@ -263,3 +264,47 @@ def test_13b_shape_chain_hadamard_108_x_128():
     xb = torch.randn(80, 5120, generator=gen).half().cuda()
     yb = ffn(xb)
     assert torch.equal(yb[:64], ffn(xb[:64])) and torch.equal(yb[64:], ffn(xb[64:]))
+
+
+def test_hadamard_across_heads_reference_fixture_and_7b_shape():
+    g = load_golden("partial_hadamard")
+    q, s, y = heads_hadamard_quant(g["x"].cuda(), g["heads"], want_rotated=True)
+    assert (y.cpu().float() - g["rotated"].float()).abs().max() <= 2 ** -10 * g["rotated"].float().abs().max()
+    q_ref, s_ref = quant.act_quant(y.cpu())
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(16, 32 * 128, generator=gen).half()
+    q, s, y = heads_hadamard_quant(x.cuda(), 32, want_rotated=True)
+    y_ref = offn.partial_hadamard_heads(x, 128)
+    assert torch.equal(y.cpu(), y_ref)
+    q_ref, s_ref = quant.act_quant(y_ref)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+
+
+@pytest.mark.parametrize("m,n,k,kind", [(17, 1024, 4096, "single"), (64, 4096, 11008, "single"), (33, 48, 1376 + 16, "single"),
+                                        (64, 5504, 4096, "dual"), (40, 688, 4096, "dual"), (64, 5504, 512, "split"),
+                                        (20, 80, 48, "split"), (5, 4096, 512, "single")])
+def test_gemv_wide_form_equals_register_form(m, n, k, kind):
+    """form 2 (token rows shared through shared memory, the default beyond 16 tokens) against form 3 (register-fed)
+    and the oracle: same integers, same fp16."""
+    gen = torch.Generator().manual_seed(m * 13 + n + k)
+    a = torch.randint(-128, 128, (m, k), generator=gen, dtype=torch.int8).cuda()
+    w = torch.randint(-128, 128, (n, k), generator=gen, dtype=torch.int8).cuda()
+    sa = (torch.rand(m, generator=gen) * 0.02 + 1e-3).cuda()
+    sw = (torch.rand(n, generator=gen) * 0.002 + 1e-4).cuda()
+    kw = {}
+    if kind != "single":
+        kw["w2_q"] = torch.randint(-128, 128, (n, k), generator=gen, dtype=torch.int8).cuda()
+        kw["w2_scale"] = (torch.rand(n, generator=gen) * 0.002 + 1e-4).cuda()
+    if kind == "split":
+        kw["a2_q"] = torch.randint(-128, 128, (m, k), generator=gen, dtype=torch.int8).cuda()
+        kw["a2_scale"] = (torch.rand(m, generator=gen) * 0.02 + 1e-3).cuda()
+    res = (torch.randn(m, n, generator=gen).half().cuda()) if kind == "single" else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o3, acc3, acc3b = w8a8_gemv(a, sa, w, sw, want_acc=True, form=3, residual=res, **kw)
+    o2, acc2, acc2b = w8a8_gemv(a, sa, w, sw, want_acc=True, form=2, residual=res, status_word=status, **kw)
+    assert int(status.item()) == 0
+    assert torch.equal(acc2.cpu(), offn._i32_matmul(a.cpu(), w.cpu()))
+    assert torch.equal(acc3, acc2) and torch.equal(o3, o2)
+    if kind != "single":
+        assert torch.equal(acc3b, acc2b)

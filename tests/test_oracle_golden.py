@@ -148,3 +148,11 @@ def test_hybrid_ffn_stage_isolation_is_exact():
     acc = ffn.stage_from("i32", w, a_q=q, w_q=w["Wd_q"])["acc"]
     y = ((acc.float() * s[:, None]) * w["Wd_s"][None, :]).half()
     assert rel_to_norm(y.float(), g["y"].float()) < 1e-3
+
+
+def test_partial_hadamard_across_heads_matches_reference_wrapper():
+    g = load_golden("partial_hadamard")
+    y = ffn.partial_hadamard_heads(g["x"], g["head_dim"])
+    assert (y.float() - g["rotated"].float()).abs().max() <= 2 ** -10 * g["rotated"].float().abs().max()
+    q, s = quant.act_quant(g["rotated"])
+    assert torch.equal((q.float() * s[:, None]).half(), g["fake_quant"])
