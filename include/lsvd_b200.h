@@ -298,7 +298,7 @@ typedef struct lsvd_gemv_args {
   int64_t residual_row_stride;
   int32_t* status_word;          /* device int32 or NULL: LSVD_ERR_TIMEOUT if a pipeline wait of the   */
                                  /* TMA-fed form ran out; the output is then incomplete               */
-  int32_t form;                  /* 0: chosen by batch size (register-fed up to 16 tokens, 2 beyond);   */
+  int32_t form;                  /* 0: chosen by size (2 beyond 32 tokens on large matrices, else 3);    */
                                  /* 1: persistent TMA-fed kernel with K split over warps, m <= 16 only   */
                                  /*    (LSVD_ERR_UNSUPPORTED beyond); 2: TMA-fed kernel whose warps      */
                                  /*    share the token rows (built for 17..64 tokens, valid for any m);   */

@@ -290,15 +290,72 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
     // ---- complete sums of channels (g, g + 8) x tokens (8 j + 2 t, + 1): dequantise and store ----
+    // Scales and residuals are requested for all of a lane's 4 NT values before the first one is used: an
+    // epilogue that waits on a global load per value costs more than the tile's whole stream.
     const int row_base = tile * rows + warp * 16;
+    const int r0 = row_base + g, r1 = r0 + 8;
+    const bool ok0 = r0 < p.n, ok1 = r1 < p.n;
+    if (p.acc_out != nullptr || (DUAL && p.acc2_out != nullptr)) {
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
+      for (int j = 0; j < NT; ++j)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int row = row_base + g + 8 * (c >> 1);
-        const int tok = j * 8 + 2 * t + (c & 1);
-        if (row < p.n && tok < p.m) gemv_store<DUAL, SPLIT_B>(p, tok, row, acc[0][j][c], acc[NMAT - 1][j][c]);
+        for (int c = 0; c < 4; ++c) {
+          const int row = (c >> 1) ? r1 : r0, tok = j * 8 + 2 * t + (c & 1);
+          if (row < p.n && tok < p.m) {
+            if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = acc[0][j][c];
+            if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = acc[NMAT - 1][j][c];
+          }
+        }
+    }
+    if (p.out != nullptr) {
+      float sw[2] = {0.f, 0.f}, sw2[2] = {0.f, 0.f};
+      if (ok0) sw[0] = p.w_scale[r0];
+      if (ok1) sw[1] = p.w_scale[r1];
+      if (DUAL) {
+        if (ok0) sw2[0] = p.w2_scale[r0];
+        if (ok1) sw2[1] = p.w2_scale[r1];
       }
+      float sa[NT][2], sb[NT][2];
+      __half res[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = j * 8 + 2 * t + e;
+          sa[j][e] = sb[j][e] = 0.f;
+          if (tok < p.m) {
+            sa[j][e] = p.a_scale[tok * p.a_scale_stride];
+            sb[j][e] = (DUAL && SPLIT_B) ? p.a2_scale[tok * p.a2_scale_stride] : sa[j][e];
+          }
+        }
+      if (p.residual != nullptr) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int row = (c >> 1) ? r1 : r0, tok = j * 8 + 2 * t + (c & 1);
+            res[j][c] = __float2half(0.f);
+            if (row < p.n && tok < p.m) res[j][c] = p.residual[static_cast<int64_t>(tok) * p.residual_row_stride + row];
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int hi = c >> 1, e = c & 1;
+          const int row = hi ? r1 : r0, tok = j * 8 + 2 * t + e;
+          if (row >= p.n || tok >= p.m) continue;
+          const __half v0 = __float2half_rn((static_cast<float>(acc[0][j][c]) * sa[j][e]) * sw[hi]);
+          __half out = v0;
+          if (DUAL) {
+            const __half u = __float2half_rn((static_cast<float>(acc[NMAT - 1][j][c]) * sb[j][e]) * sw2[hi]);
+            const __half sg = __float2half_rn(silu_f(__half2float(v0)));
+            out = __float2half_rn(__half2float(sg) * __half2float(u));
+          }
+          if (p.residual != nullptr) out = __float2half_rn(__half2float(out) + __half2float(res[j][c]));
+          p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = out;
+        }
+    }
   }
 }
 
