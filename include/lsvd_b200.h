@@ -262,8 +262,8 @@ int lsvd_hadamard_pack(const void* had_K, int32_t K, void* packed, void* stream)
 /* Hadamard across heads followed by per-token int8 quantisation: a row [heads * head_dim] is seen as
  * [heads][head_dim] and every column is transformed over its `heads` entries (a power of two up to 64), scale
  * 1 / sqrt(heads), fp32 inside and fp16 out; then the row is quantised as in lsvd_act_quant.  The online
- * rotation in front of o_proj: ActQuantWrapper.forward with online_partial_had and K == 1
- * (fake_quant/utils/quant_utils.py:302-322).  head_dim even, <= 256. */
+ * rotation in front of o_proj: ActQuantWrapper.forward with online_partial_had
+ * (fake_quant/utils/quant_utils.py:302-322; K == 1 without had_K, K == heads with it).  head_dim even, <= 256. */
 typedef struct lsvd_heads_hadamard_quant_args {
   int32_t rows, heads, head_dim;
   const void* x;                 /* device fp16 [rows, heads * head_dim]                            */
@@ -272,6 +272,8 @@ typedef struct lsvd_heads_hadamard_quant_args {
   int64_t q_row_stride;
   float* scale;                  /* device fp32 [rows]                                              */
   void* y;                       /* optional device fp16 [rows, heads * head_dim] (contiguous): the rotated row */
+  const void* had_K;             /* NULL, or device fp16 [heads, heads] (+-1): y = (had_K x) / sqrt(heads) with the     */
+                                 /* reference's two fp16 roundings, for head counts that are not a power of two (<= 64) */
 } lsvd_heads_hadamard_quant_args;
 int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* args, void* stream);
 

@@ -98,7 +98,7 @@ class HeadsHadamardQuantArgs(C.Structure):
     _fields_ = [
         ("rows", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
         ("x", C.c_void_p), ("x_row_stride", C.c_int64), ("q", C.c_void_p), ("q_row_stride", C.c_int64),
-        ("scale", C.c_void_p), ("y", C.c_void_p),
+        ("scale", C.c_void_p), ("y", C.c_void_p), ("had_K", C.c_void_p),
     ]
 
 

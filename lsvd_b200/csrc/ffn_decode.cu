@@ -318,6 +318,67 @@ __global__ void __launch_bounds__(128) heads_hadamard_quant_kernel(const __grid_
   }
 }
 
+// The same for a head count that is not a power of two (H = K, e.g. 28): y = fp16(fp16(had_K x) / sqrt(H)), the
+// reference's fp16 matmul followed by its fp16-tensor-by-scalar division.  A thread owns two adjacent columns,
+// keeps their 2 H inputs in registers, reads had_K (staged as +-1 floats) from shared memory, and parks the fp16
+// results in shared memory until the row's scale is known.
+constexpr int kHeadsMax = 64;
+
+__global__ void __launch_bounds__(128) heads_hadk_quant_kernel(const __grid_constant__ HeadsHadParams p, const __half* had_K) {
+  extern __shared__ __align__(16) uint8_t hh_smem[];
+  float* hk = reinterpret_cast<float*>(hh_smem);                       // [H][H]
+  __half2* ys = reinterpret_cast<__half2*>(hk + p.heads * p.heads);    // [H][D / 2]
+  __shared__ float red[8];
+  grid_dependency_sync();
+  const int r = blockIdx.x, D = p.head_dim, H = p.heads;
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x) hk[i] = __half2float(had_K[i]);
+  const __half* x = p.x + r * p.x_row_stride;
+  const int c = 2 * threadIdx.x;
+  const bool on = c < D;
+  float e0[kHeadsMax], e1[kHeadsMax];
+#pragma unroll
+  for (int h = 0; h < kHeadsMax; ++h) {
+    e0[h] = e1[h] = 0.f;
+    if (on && h < H) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(x + h * D + c));
+      e0[h] = f.x;
+      e1[h] = f.y;
+    }
+  }
+  __syncthreads();
+  float amax = 0.f;
+  const float root = sqrtf(static_cast<float>(H));
+  if (on) {
+    for (int o = 0; o < H; ++o) {
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int h = 0; h < kHeadsMax; ++h)
+        if (h < H) {
+          const float w = hk[o * H + h];
+          a0 = fmaf(w, e0[h], a0);
+          a1 = fmaf(w, e1[h], a1);
+        }
+      const float y0 = __half2float(__float2half_rn(__fdiv_rn(__half2float(__float2half_rn(a0)), root)));
+      const float y1 = __half2float(__float2half_rn(__fdiv_rn(__half2float(__float2half_rn(a1)), root)));
+      amax = fmaxf(amax, fmaxf(fabsf(y0), fabsf(y1)));
+      ys[o * (D >> 1) + threadIdx.x] = __floats2half2_rn(y0, y1);
+    }
+  }
+  amax = block_max(amax, red);
+  const float s = act_scale_of(amax);
+  if (threadIdx.x == 0) p.scale[r] = s;
+  if (!on) return;
+  int8_t* q = p.q + r * p.q_row_stride;
+  for (int o = 0; o < H; ++o) {
+    const __half2 v = ys[o * (D >> 1) + threadIdx.x];               // written by this thread
+    const float2 f = __half22float2(v);
+    const uint16_t packed = static_cast<uint16_t>(static_cast<uint8_t>(act_code(f.x, s))) |
+                            (static_cast<uint16_t>(static_cast<uint8_t>(act_code(f.y, s))) << 8);
+    *reinterpret_cast<uint16_t*>(q + o * D + c) = packed;
+    if (p.y != nullptr) *reinterpret_cast<__half2*>(p.y + static_cast<int64_t>(r) * H * D + o * D + c) = v;
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
 // (H_K kron H_nb) rotation + per-token quantisation: a thread-block cluster per token
 // ----------------------------------------------------------------------------------------------
@@ -875,8 +936,17 @@ extern "C" int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* a
     case 16: kern = heads_hadamard_quant_kernel<16>; break;
     case 32: kern = heads_hadamard_quant_kernel<32>; break;
     case 64: kern = heads_hadamard_quant_kernel<64>; break;
-    default: return LSVD_ERR_UNSUPPORTED;       // a head count that is not a power of two needs the had_K form
+    default: break;
   }
+  if (a->had_K != nullptr) {                    // the had_K @ x form (head counts that are not a power of two)
+    if (a->heads > kHeadsMax) return LSVD_ERR_UNSUPPORTED;
+    const int smem = a->heads * a->heads * 4 + a->heads * a->head_dim * 2;
+    if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(heads_hadk_quant_kernel), smem));
+    LSVD_CUDA_TRY(launch_chained(heads_hadk_quant_kernel, dim3(a->rows), dim3(128), smem, static_cast<cudaStream_t>(stream), 1,
+                                 false, p, static_cast<const __half*>(a->had_K)));
+    return LSVD_OK;
+  }
+  if (kern == nullptr) return LSVD_ERR_UNSUPPORTED;       // not a power of two and no had_K given
   LSVD_CUDA_TRY(launch_chained(kern, dim3(a->rows), dim3(128), 0, static_cast<cudaStream_t>(stream), 1, false, p));
   return LSVD_OK;
 }

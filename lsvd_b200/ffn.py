@@ -110,9 +110,10 @@ def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rot
     return q, scale, y
 
 
-def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False):
-    """Hadamard across heads (rows ``[rows, heads * head_dim]``, heads a power of two) + per-token int8 quantisation:
-    the online rotation in front of ``o_proj``.  Returns (codes, scale fp32 [rows], rotated fp16 or None)."""
+def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False, had_K: Optional[torch.Tensor] = None):
+    """Hadamard across heads (rows ``[rows, heads * head_dim]``) + per-token int8 quantisation: the online rotation in
+    front of ``o_proj``.  ``heads`` a power of two, or any count up to 64 with its ``had_K [heads, heads]`` (+-1).
+    Returns (codes, scale fp32 [rows], rotated fp16 or None)."""
     _require_cuda(x)
     if x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] % heads:
         raise ValueError("x must be a 2-D fp16 tensor [rows, heads * head_dim] with unit inner stride")
@@ -123,6 +124,9 @@ def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False
     a = _lib.HeadsHadamardQuantArgs()
     a.rows, a.heads, a.head_dim = rows, heads, cols // heads
     a.x, a.x_row_stride, a.q, a.q_row_stride, a.scale, a.y = x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), scale.data_ptr(), _ptr(y)
+    if had_K is not None:
+        had_K = had_K.to(device=x.device, dtype=torch.float16).contiguous()
+        a.had_K = had_K.data_ptr()
     _lib.check(_lib.load().lsvd_heads_hadamard_quant(C.byref(a), _stream_ptr(x)))
     return q, scale, y
 

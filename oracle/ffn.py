@@ -43,6 +43,19 @@ def fwht(x: torch.Tensor) -> torch.Tensor:
     return y.reshape(x.shape)
 
 
+def partial_hadamard_heads_hadk(x16: torch.Tensor, head_dim: int, had_K: torch.Tensor) -> torch.Tensor:
+    """Hadamard across heads for a head count H that is not a power of two (H = K, e.g. 28):
+    ``(had_K @ x.reshape(-1, H, head_dim)) / sqrt(H)`` as fp16 tensor operations, i.e. an fp16 matmul (fp32
+    accumulation, one rounding) followed by the division of an fp16 tensor by a Python scalar (evaluated in fp32,
+    rounded to fp16) (fake_quant/utils/quant_utils.py:312-313)."""
+    n = x16.shape[-1]
+    H = n // head_dim
+    x = x16.reshape(-1, H, head_dim)
+    y = (had_K.float() @ x.float()).to(x16.dtype)
+    y = (y.float() / torch.tensor(math.sqrt(H), dtype=torch.float32)).to(x16.dtype)
+    return y.reshape(x16.shape)
+
+
 def partial_hadamard_heads(x16: torch.Tensor, head_dim: int) -> torch.Tensor:
     """Hadamard across heads: rows ``[..., H * head_dim]`` seen as ``[H, head_dim]``, each of the head_dim columns
     transformed over its H entries (H a power of two), scale 1/sqrt(H), fp32 inside and fp16 out.

@@ -341,7 +341,21 @@ def gen_partial_hadamard():
     rotated = seen["x"]
     wrap.quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
     wrap(x)
-    save("partial_hadamard", x=x, heads=np.int64(H), head_dim=np.int64(D), rotated=rotated, fake_quant=seen["x"])
+    # a head count that is not a power of two (28: Qwen2-VL-7B): the had_K @ x form of the same wrapper
+    from utils import hadamard_utils
+    H2 = 28
+    hk, K2 = hadamard_utils.get_hadK(H2)
+    assert K2 == H2
+    x2 = torch.randn(5, H2 * D, generator=g).half()
+    lin2 = nn.Linear(H2 * D, 8, bias=False).half()
+    wrap2 = quant_utils.ActQuantWrapper(lin2)
+    wrap2.online_partial_had, wrap2.had_dim, wrap2.K, wrap2.had_K = True, D, K2, hk
+    seen2 = {}
+    lin2.register_forward_pre_hook(lambda mod, inp: seen2.__setitem__("x", inp[0].detach().clone()))
+    wrap2.quantizer.configure(bits=16)
+    wrap2(x2)
+    save("partial_hadamard", x=x, heads=np.int64(H), head_dim=np.int64(D), rotated=rotated, fake_quant=seen["x"],
+         x28=x2, had28=hk.to(torch.int8), rotated28=seen2["x"])
 
 
 if __name__ == "__main__":

@@ -279,6 +279,15 @@ def test_hadamard_across_heads_reference_fixture_and_7b_shape():
     assert torch.equal(y.cpu(), y_ref)
     q_ref, s_ref = quant.act_quant(y_ref)
     assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+    # 28 heads (not a power of two): the had_K @ x form
+    q, s, y = heads_hadamard_quant(g["x28"].cuda(), 28, want_rotated=True, had_K=g["had28"].float())
+    assert torch.equal(y.cpu(), g["rotated28"])
+    q_ref, s_ref = quant.act_quant(g["rotated28"])
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+    x28 = torch.randn(9, 28 * 128, generator=gen).half()
+    q, s, y = heads_hadamard_quant(x28.cuda(), 28, want_rotated=True, had_K=g["had28"].float())
+    y_ref = offn.partial_hadamard_heads_hadk(x28, 128, g["had28"].float())
+    assert (y.cpu().float() - y_ref.float()).abs().max() <= 2 ** -10 * y_ref.float().abs().max()
 
 
 @pytest.mark.parametrize("m,n,k,kind", [(17, 1024, 4096, "single"), (64, 4096, 11008, "single"), (33, 48, 1376 + 16, "single"),

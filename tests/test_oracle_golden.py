@@ -156,3 +156,5 @@ def test_partial_hadamard_across_heads_matches_reference_wrapper():
     assert (y.float() - g["rotated"].float()).abs().max() <= 2 ** -10 * g["rotated"].float().abs().max()
     q, s = quant.act_quant(g["rotated"])
     assert torch.equal((q.float() * s[:, None]).half(), g["fake_quant"])
+    y28 = ffn.partial_hadamard_heads_hadk(g["x28"], g["head_dim"], g["had28"].float())
+    assert (y28.float() - g["rotated28"].float()).abs().max() <= 2 ** -10 * g["rotated28"].float().abs().max()
