@@ -93,25 +93,36 @@ __global__ void __launch_bounds__(128) absorb_query_kernel(const __grid_constant
   __shared__ float qs[256];
   __shared__ float qt[LSVD_MAX_RANK];
   __shared__ float wmax[4];
-  grid_dependency_sync();
+  grid_dependency_release();
   const int h = blockIdx.x, b = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (h == 0 && b == 0 && threadIdx.x == 0) *p.queue = 0;
   const int r0 = p.k_off[h], r = p.k_off[h + 1] - r0;
+  // one thread per latent entry: its up-factor row is head_dim contiguous fp16 values.  The factor is a weight:
+  // its first eight 16-byte pieces are requested before this kernel waits for the one before it.
+  const __half* row = p.up_k + static_cast<int64_t>(r0 + min(static_cast<int>(threadIdx.x), r - 1)) * p.up_k_row_stride;
+  uint4 v0[8];
+  const bool pre = p.up_k_vec16 && threadIdx.x < r;
+  if (pre) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      v0[c] = (c < (p.head_dim >> 3)) ? __ldg(reinterpret_cast<const uint4*>(row) + c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  grid_dependency_wait();
+  if (h == 0 && b == 0 && threadIdx.x == 0) *p.queue = 0;
   const __half* qp = p.q + b * p.q_stride_b + h * p.q_stride_h;
   for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) qs[d] = __half2float(qp[d]);
   __syncthreads();
-  // one thread per latent entry: its up-factor row is head_dim contiguous fp16 values, read with 16-byte
-  // loads that are all in flight together
   if (threadIdx.x < r) {
-    const __half* row = p.up_k + static_cast<int64_t>(r0 + threadIdx.x) * p.up_k_row_stride;
     float acc = 0.f;
     if (p.up_k_vec16) {
       const uint4* rv = reinterpret_cast<const uint4*>(row);
       for (int c0 = 0; c0 < (p.head_dim >> 3); c0 += 8) {
         uint4 v[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) v[c] = (c0 + c < (p.head_dim >> 3)) ? __ldg(rv + c0 + c) : make_uint4(0u, 0u, 0u, 0u);
+        for (int c = 0; c < 8; ++c) {
+          if (c0 == 0) v[c] = v0[c];
+          else v[c] = (c0 + c < (p.head_dim >> 3)) ? __ldg(rv + c0 + c) : make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           if (c0 + c < (p.head_dim >> 3)) {
