@@ -33,10 +33,14 @@ sys.path.insert(0, ROOT)
 import torch
 
 WORKLOADS = {
-    "c3_layer": dict(batch=16, heads=32, head_dim=128, context=4096, ragged=True, ffn=True,
-                     desc="BASELINE config 3 decode hot path of one LLaVA-Next-7B-shape layer: batch 16, context 4096, "
-                          "ragged per-head K/V ranks (multiples of 16 in [16,128], mean 64); hybrid FFN 4096/11008, "
-                          "rank 512, 50 % SVD channels, Hadamard 64 x 172"),
+    "c3_layer": dict(batch=16, heads=32, head_dim=128, context=4096, ragged=True, ffn=True, full=True,
+                     desc="BASELINE config 3: the full LSVD W8A8 decoder layer at the LLaVA-Next-7B shape (hidden 4096, "
+                          "32 heads x 128, intermediate 11008), batch 16, context 4096, ragged per-head K/V ranks "
+                          "(multiples of 16 in [16,128], mean 64), query latents of rank 64 per head; hybrid FFN rank 512, "
+                          "50 % SVD channels, Hadamard 64 x 172"),
+    "c3_attention_ffn": dict(batch=16, heads=32, head_dim=128, context=4096, ragged=True, ffn=True,
+                             desc="BASELINE config 3 without the projections: cache append + attention (absorb, V "
+                                  "up-projection) + hybrid FFN on the attention output"),
     "c2_ffn": dict(batch=8, heads=0, head_dim=0, context=0, ragged=False, ffn=True, ffn_only=True,
                    desc="BASELINE config 2: hybrid FFN decode block 4096/11008, rank 512, 50 % SVD channels, input "
                         "rotation + Hadamard 64 x 172, batch of --tokens tokens (1/8/64)"),
@@ -160,7 +164,7 @@ FFN_BYTES = 2 * 4096 * 512 + 2 * 512 * 5504 + 2 * 5504 * 4096 + 11008 * 4096    
 FFN_RTN_PAIR_BYTES = 2 * 5504 * 4096                                               # its largest launch
 
 
-def make_ffn(device, seed, copies):
+def make_ffn(device, seed, copies, input_had=True):
     """`copies` hybrid FFNs with different seeded weights (cycled so that weights never sit in L2 between steps)."""
     from lsvd_b200 import synth
     from lsvd_b200.ffn import HybridFFN
@@ -168,7 +172,7 @@ def make_ffn(device, seed, copies):
     out = []
     for c in range(copies):
         w = synth.ffn_weights(FFN_SHAPE["d_in"], FFN_SHAPE["d_ffn"], FFN_SHAPE["rank"], FFN_SHAPE["n_svd"],
-                              seed=seed + c, had_K=hk, K=FFN_SHAPE["K"])
+                              seed=seed + c, had_K=hk, K=FFN_SHAPE["K"], input_had=input_had)
         out.append(HybridFFN({k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}))
     return out
 
@@ -194,19 +198,30 @@ def run_ours(args, rank, world, local):
     host_in, dev_in, stage_in = [], [], []
     launches = 0
 
+    full = w.get("full", False)
     if has_attn:
         wl = make_workload(w, dev, seed=1000 + rank)
         lay, st, H, D = wl["layout"], wl["state"], wl["H"], wl["D"]
         ws = torch.empty(attn_decode_workspace_bytes(B, lay, wl["seq"]), dtype=torch.uint8, device=dev)
         attn_out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
-        shapes = [(B, H, D), (B, lay.sum_k), (B, lay.sum_v)]
-        launches += 4
+        shapes = [(B, H * D)] if full else [(B, H, D), (B, lay.sum_k), (B, lay.sum_v)]
+        launches += 8 if full else 4
     else:
         shapes = [(B, FFN_SHAPE["d_in"])]
     if has_ffn:
-        ffns = make_ffn(dev, seed=50 + rank, copies=1 if has_attn else 3)
+        ffns = make_ffn(dev, seed=50 + rank, copies=1 if has_attn else 3, input_had=not full)
         ffn_out = torch.empty(B, FFN_SHAPE["d_in"], dtype=torch.float16, device=dev)
         launches += 7
+    layer = None
+    if full:
+        # the whole decoder layer: RMSNorm + A8 quantiser, int8 latent projection (query, K and V latents), cache
+        # append, attention with the query up-factor folded into the K factor, fused W_uv W_o int8 projection +
+        # residual, hybrid FFN with its RMSNorm prologue + residual
+        from lsvd_b200.layer import LSVDDecoderLayer, make_layer_weights
+        RANK_Q = 64
+        lw = make_layer_weights(H * D, H, D, RANK_Q, lay.k_ranks, lay.v_ranks, seed=70 + rank)
+        layer = LSVDDecoderLayer(lay, D, RANK_Q, {k: v.to(dev) for k, v in lw.items()}, ffns[0])
+        proj_bytes = lw["W_lat_q"].numel() + lw["W_uvo_q"].numel()
     # per-step inputs; host copies live in pinned memory for the end-to-end leg
     # A step's inputs (query + the new token's K and V latents) sit in ONE buffer, so a step costs one copy:
     # n_in such buffers in pinned host memory, their copies in HBM, and the staging buffer the graph reads.
@@ -233,6 +248,9 @@ def run_ours(args, rank, world, local):
     def step(inputs, i, ev=None):
         """One decode step of the layer's hot path.  The FFN takes the attention output's heads flattened
         (hidden = heads x head_dim) as its input: the data dependency of the layer without the projections."""
+        if full:
+            layer(inputs[0], wl["ck"], wl["sk"], wl["cv"], wl["sv"], st, out=ffn_out, timing_events=ev)
+            return
         if has_attn:
             q, lk, lv = inputs
             cache_append(lay, lk, lv, st.mem_index, wl["ck"], wl["sk"], wl["cv"], wl["sv"])
@@ -357,11 +375,14 @@ def run_ours(args, rank, world, local):
     else:
         abytes, kname = FFN_RTN_PAIR_BYTES + B * 4096 + 2 * 5504 * 4, "w8a8_gemv_kernel (RTN gate/up pair)"
     achieved = abytes / (k_ms * 1e-3) / 1e9
-    step_bytes = (algorithmic_bytes(wl) if has_attn else 0) + (FFN_BYTES if has_ffn else 0)
+    step_bytes = (algorithmic_bytes(wl) if has_attn else 0) + (FFN_BYTES if has_ffn else 0) + (proj_bytes if full else 0)
     h2d = stage_pack.numel() * stage_pack.element_size()
     d2h = host_out.numel() * host_out.element_size()
     what = []
-    if has_attn:
+    if full:
+        what.append("RMSNorm + A8 quantiser + int8 latent projection (Q, K, V latents) + cache append (K+V) + int8 latent "
+                    "decode attention (absorb, query up-factor folded into K) + fused W_uv W_o int8 projection + residual")
+    elif has_attn:
         what.append("cache append (K+V) + int8 latent decode attention (absorb) + V up-projection")
     if has_ffn:
         what.append("hybrid SVD/RTN FFN (input rotation, A8 quantisers, SVD and RTN gate/up, Hadamard 64x172, down)")
@@ -561,6 +582,15 @@ def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
                                had_K=synth.sign_matrix(FFN_SHAPE["K"]).float(), K=FFN_SHAPE["K"])
         x = torch.randn(bs, FFN_SHAPE["d_in"], generator=torch.Generator().manual_seed(1)).half()
         fns.append(lambda: offn.hybrid_ffn_stages(x, fw))
+    if w.get("full"):
+        # the two int8 projections of the full layer (latent projection, fused output projection) on the same sample
+        from oracle import layer as olayer
+        from lsvd_b200.layer import make_layer_weights
+        lw = make_layer_weights(H * D, H, D, 64, kr, vr, seed=70)
+        xl = torch.randn(bs, H * D, generator=torch.Generator().manual_seed(2)).half()
+        ol = torch.randn(bs, sum(vr), generator=torch.Generator().manual_seed(3)).half()
+        fns.append(lambda: (olayer.linear_a8w8(olayer.rms_norm(xl, lw["ln1"], 1e-5), lw["W_lat_q"], lw["W_lat_s"]),
+                            olayer.linear_a8w8(ol, lw["W_uvo_q"], lw["W_uvo_s"], residual=xl)))
 
     def once():
         for f in fns:

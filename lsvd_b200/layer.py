@@ -39,8 +39,11 @@ class LSVDDecoderLayer(nn.Module):
         self._ws = None
 
     @torch.no_grad()
-    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages: Optional[dict] = None):
-        """x [B, hidden] fp16 (one token per request).  Mutates the cache rows ``infer_state.mem_index`` in place."""
+    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages: Optional[dict] = None, out=None,
+                timing_events=None):
+        """x [B, hidden] fp16 (one token per request).  Mutates the cache rows ``infer_state.mem_index`` in place.
+        ``out`` receives the result if given; ``timing_events`` (a CUDA event pair) is recorded around the attention's
+        streaming kernel."""
         lay, H, B = self.layout, self.layout.num_heads, x.shape[0]
         xq, xs, xn = act_quant(x, want_rotated=True, norm_weight=self.ln1, norm_eps=1e-5)
         lat, _, _ = w8a8_gemv(xq, xs, self.W_lat_q, self.W_lat_s)
@@ -54,10 +57,10 @@ class LSVDDecoderLayer(nn.Module):
         q = lat[:, :self.Rq].unflatten(1, (H, self.rank_q))
         token_decode_attention_int8_latent_absorb(q, infer_state, H, self.rank_q, cache_k, scale_k, cache_v, scale_v,
                                                   self.C, None, layout=lay, out_latent=o_lat, workspace=self._ws,
-                                                  sm_scale=1.0 / math.sqrt(self.head_dim))
+                                                  sm_scale=1.0 / math.sqrt(self.head_dim), timing_events=timing_events)
         oq, os_, _ = act_quant(o_lat)
         y1, _, _ = w8a8_gemv(oq, os_, self.W_uvo_q, self.W_uvo_s, residual=xn)
-        out = self.ffn(y1, norm_weight=self.ln2, norm_eps=1e-6, residual=y1)
+        out = self.ffn(y1, out=out, norm_weight=self.ln2, norm_eps=1e-6, residual=y1)
         if stages is not None:
             stages.update(xn=xn, lat=lat, o_lat=o_lat, y1=y1, out=out)
         return out
