@@ -211,6 +211,25 @@ class HybridFFN(nn.Module):
             w[name + "_q"], w[name + "_s"] = quantize_weight_rtn(t, mse)
         return cls(w)
 
+    @classmethod
+    def from_module(cls, mlp, mse: bool = False):
+        """Build from a module laid out like the reference's ``HybridSVDQuantFFN``
+        (fake_quant/utils/hybrid_ffn_utils.py:923-984): ``gate_svd`` / ``up_svd`` with ``BLinear`` (latent factor,
+        possibly inside an ``ActQuantWrapper``: its Linear is then ``.module``) and ``ALinear``; ``gate_quant`` /
+        ``up_quant`` / ``down_proj`` wrappers around Linears whose weights already follow the module's channel order
+        ([SVD | RTN] input columns for ``down_proj``); ``had_K``, ``K``, ``online_had``.  The fp16
+        weights of a module that went through ``rtn_fwrd`` are integer codes times a per-row scale with the largest
+        code at +-127, so quantising them again reproduces the same codes and scales."""
+        def weight(m):
+            return getattr(m, "module", m).weight.data
+
+        return cls.from_float(
+            U=torch.cat([weight(mlp.gate_svd.BLinear), weight(mlp.up_svd.BLinear)]),
+            Vg=weight(mlp.gate_svd.ALinear), Vu=weight(mlp.up_svd.ALinear),
+            Wg=weight(mlp.gate_quant), Wu=weight(mlp.up_quant), Wd=weight(mlp.down_proj),
+            had_K=getattr(mlp, "had_K", None), K=int(getattr(mlp, "K", 1)), mse=mse,
+            online_had=bool(getattr(mlp, "online_had", getattr(mlp, "had_K", None) is not None)))
+
     @torch.no_grad()
     def forward_stages(self, x: torch.Tensor, want_acc: bool = False) -> dict:
         shape = x.shape

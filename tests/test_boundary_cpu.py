@@ -77,3 +77,37 @@ def test_ragged_ranks_meet_the_budget():
         r = synth.ragged_ranks(H, 64, seed=H)
         assert len(r) == H and sum(r) == 64 * H and all(16 <= x <= 128 and x % 16 == 0 for x in r)
         assert len(set(r)) > 3
+
+
+def test_hybrid_ffn_from_module_reads_the_reference_layout():
+    """HybridFFN.from_module on a stand-in with HybridSVDQuantFFN's attribute names: fake-quantised fp16 weights
+    (codes x scale, as rtn_fwrd leaves them) come back as the same int8 codes and scales."""
+    import types
+    import torch
+    from torch import nn
+    from lsvd_b200.ffn import HybridFFN, quantize_weight_rtn
+    g = torch.Generator().manual_seed(0)
+    d_in, r, n_svd, n_q = 64, 16, 32, 48
+
+    def fake(out_f, in_f):
+        w = torch.randn(out_f, in_f, generator=g) * 0.05
+        q, s = quantize_weight_rtn(w)
+        lin = nn.Linear(in_f, out_f, bias=False)
+        lin.weight.data = (q.float() * s[:, None]).half()
+        return lin, q, s
+
+    wrap = lambda lin: types.SimpleNamespace(module=lin)             # ActQuantWrapper keeps its Linear in .module
+    parts = {k: fake(*shape) for k, shape in dict(Ug=(r, d_in), Uu=(r, d_in), Vg=(n_svd, r), Vu=(n_svd, r), Wg=(n_q, d_in),
+                                                   Wu=(n_q, d_in), Wd=(d_in, n_svd + n_q)).items()}
+    mlp = types.SimpleNamespace(
+        gate_svd=types.SimpleNamespace(BLinear=wrap(parts["Ug"][0]), ALinear=parts["Vg"][0]),
+        up_svd=types.SimpleNamespace(BLinear=wrap(parts["Uu"][0]), ALinear=parts["Vu"][0]),
+        gate_quant=wrap(parts["Wg"][0]), up_quant=wrap(parts["Wu"][0]), down_proj=wrap(parts["Wd"][0]),
+        had_K=None, K=1, online_had=False, n_svd=n_svd)
+    ffn = HybridFFN.from_module(mlp)
+    assert torch.equal(ffn.U_q, torch.cat([parts["Ug"][1], parts["Uu"][1]]))
+    for name in ("Vg", "Vu", "Wg", "Wu", "Wd"):
+        assert torch.equal(getattr(ffn, name + "_q"), parts[name][1])
+        # fp16 storage of code x scale moves the recovered scale by at most one fp16 rounding
+        assert torch.allclose(getattr(ffn, name + "_s"), parts[name][2], rtol=2e-3)
+    assert ffn.n_svd == n_svd and ffn.rank == r and ffn.online_had is False
