@@ -317,3 +317,29 @@ def test_gemv_wide_form_equals_register_form(m, n, k, kind):
     assert torch.equal(acc3, acc2) and torch.equal(o3, o2)
     if kind != "single":
         assert torch.equal(acc3b, acc2b)
+
+
+def test_provider_converts_a_swiglu_module_and_matches_the_oracle():
+    """The "b200" FFN provider on a stand-in for the reference's SwiGLUFFN (norm + three Linears + residual)."""
+    import types
+    from torch import nn
+    from oracle import layer as olayer
+    from lsvd_b200.provider import b200_ffn, get_b200_ffn
+    gen = torch.Generator().manual_seed(9)
+    hidden, inter = 256, 512
+    mod = types.SimpleNamespace(
+        norm=types.SimpleNamespace(weight=nn.Parameter(torch.randn(hidden, generator=gen).half().cuda()), variance_epsilon=1e-6),
+        up_proj=nn.Linear(hidden, inter, bias=False).half().cuda(), gate_proj=nn.Linear(hidden, inter, bias=False).half().cuda(),
+        down_proj=nn.Linear(inter, hidden, bias=False).half().cuda())
+    x = torch.randn(2, 3, hidden, generator=gen).half().cuda()
+    y = b200_ffn(x, mod)
+    assert y.shape == x.shape
+    ffn, norm_w, eps = get_b200_ffn(mod)
+    assert get_b200_ffn(mod)[0] is ffn                      # cached
+    w = {k: v.cpu() for k, v in ffn.state_dict().items() if v is not None}
+    w.update(K=1, had_K=None, had_sign=None, online_had=False)
+    x2 = x.reshape(-1, hidden).cpu()
+    xn = olayer.rms_norm(x2, norm_w.cpu(), eps)
+    ref = offn.hybrid_ffn_stages(xn, w)["out"]
+    ref = (ref.float() + x2.float()).half()
+    assert rel_to_norm(y.reshape(-1, hidden).cpu().float(), ref.float()) < TOL
