@@ -56,6 +56,10 @@ WORKLOADS = {
     "c3_attention_rope": dict(batch=16, heads=32, head_dim=128, context=4096, aux="rope",
                               desc="BASELINE config 3 batch/context with uniform rank 64 in the reference's own attention "
                                    "form (int8 K up-factor, rotary keys)"),
+    "c1_attention_block": dict(batch=1, heads=32, head_dim=128, context=2048, aux="block",
+                               desc="BASELINE config 1 through the module that takes the place of the reference's "
+                                    "Int8AttentionBlock: RMSNorm, fp16 latent projections (library GEMMs, as in the "
+                                    "reference), append, rotary int8 latent attention, composed output projection"),
     "c5_prefill_ffn": dict(batch=8, context=4096, aux="prefill_ffn",
                            desc="BASELINE config 5 prefill, FFN block of one layer: 8 x 4096 tokens through the hybrid "
                                 "SVD/RTN FFN 4096/11008 (rank 512, 50 % SVD channels) on the tcgen05 int8 GEMM"),
@@ -456,6 +460,37 @@ def run_aux(args, rank, world, local):
         h2d, d2h = q_in.numel() * 2, out.numel() * 2
         l2 = "the cache (%.0f MB) %s L2" % (abytes / 1e6, "exceeds" if abytes > 126e6 else "fits in")
         what = "cos/sin table + rotary reconstruct attention + merge"
+    elif w["aux"] == "block":
+        from lsvd_b200.attention import InferState
+        from lsvd_b200.block import Int8AttentionBlock
+        B, H, D, L = w["batch"], w["heads"], w["head_dim"], w["context"]
+        torch.manual_seed(21 + rank)
+        blk = Int8AttentionBlock(H * D, H, D, 0.5, device=dev)
+        R = blk.rank_head
+        n_slots = B * L
+        ck = torch.randint(-128, 128, (n_slots, H, R), dtype=torch.int8, device=dev, generator=g)
+        cv = torch.randint(-128, 128, (n_slots, H, R), dtype=torch.int8, device=dev, generator=g)
+        sk = (torch.rand(n_slots, H, device=dev, generator=g) * 0.02 + 0.01).half()
+        sv = (torch.rand(n_slots, H, device=dev, generator=g) * 0.02 + 0.01).half()
+        st = InferState(B, L, [L] * B, device=dev)
+        xs_host = [torch.randn(B, 1, H * D).half().pin_memory() for _ in range(8)]
+        xs = [t.to(dev) for t in xs_host]
+        x_in = torch.empty_like(xs[0])
+        box = {}
+        host_out = torch.empty(B, 1, H * D, dtype=torch.float16).pin_memory()
+        out = torch.empty(B, 1, H * D, dtype=torch.float16, device=dev)
+
+        def step():
+            out.copy_(blk(x_in, ck, sk, cv, sv, st))
+        feed = lambda i, host: x_in.copy_((xs_host if host else xs)[i % 8], non_blocking=True)
+        units, metric, launches = B, "decode_tokens_per_s", 5
+        wbytes = (3 * H * R * H * D + R * H * D + H * R * H * D) * 2 + R * H * D
+        abytes = n_slots * H * R * 2 + n_slots * H * 4 + n_slots * 4 + wbytes
+        roof = dict(kernel="whole block step (5 library launches of this package + 4 of the fp16 GEMM / elementwise library)",
+                    bound="hbm", peak=float(peaks.get("hbm_gbs", 6650.0)), unit="GB/s", work=abytes)
+        h2d, d2h = x_in.numel() * 2, out.numel() * 2
+        l2 = "cache + weights (%.0f MB) fit in L2: the figure is a warm-L2 one" % (abytes / 1e6)
+        what = "RMSNorm + fp16 latent GEMM + query up-projection + append + rotary attention (3 launches) + fp16 output GEMM + residual"
     else:
         M = w["batch"] * w["context"]
         ffn = make_ffn(dev, seed=50 + rank, copies=1)[0]
@@ -614,7 +649,7 @@ def cpu_baseline_aux(w, seconds_hint, threads):
     from oracle import attention as oattn, ffn as offn, quant
     from lsvd_b200 import synth
     gen = torch.Generator().manual_seed(0)
-    if w["aux"] == "rope":
+    if w["aux"] in ("rope", "block"):
         H, D, L, R, hs = w["heads"], w["head_dim"], w["context"], 64, 4
         ck, sk = quant.latent_quant(torch.randn(L, hs, R, generator=gen).half())
         cv, sv = quant.latent_quant(torch.randn(L, hs, R, generator=gen).half())
@@ -624,7 +659,7 @@ def cpu_baseline_aux(w, seconds_hint, threads):
         one = torch.tensor([0], dtype=torch.int32)
         fn = lambda: oattn.decode_rope_recon(q, ck, sk, cv, sv, wk, wks, r2t, one, torch.tensor([L], dtype=torch.int32))
         per_call = hs / H                      # requests' worth of work per call
-        sample = f"1 request, {hs} of {H} heads, context {L}"
+        sample = f"1 request, {hs} of {H} heads, context {L}" + (" (attention only, projections left out)" if w["aux"] == "block" else "")
     else:
         fw = synth.ffn_weights(FFN_SHAPE["d_in"], FFN_SHAPE["d_ffn"], FFN_SHAPE["rank"], FFN_SHAPE["n_svd"], seed=0,
                                had_K=synth.sign_matrix(FFN_SHAPE["K"]).float(), K=FFN_SHAPE["K"])

@@ -93,3 +93,29 @@ def decoder_layer_tp_rank(x16, lw, fw, info, head_dim, rank_q, world, cache_k, s
     down = ((acc.float() * hs[:, None]) * fw["Wd_s"][None, :]).half()
     out = (down.float() + y1.float()).half()
     return out, dict(y1=y1, h_q=hq, down_acc=acc, out=out)
+
+
+def int8_attention_block(x16, w, cache_k, scale_k, cache_v, scale_v, req_to_token, b_req_idx, b_seq_len, mem_index,
+                         num_heads, head_dim, theta=10000.0):
+    """One decode step of the reference's Int8AttentionBlock (kernels/layer_bench/ffn_kernel/baseline_kernel.py:107-145).
+
+    ``w`` holds its parameters by name plus ``wuk_q``, ``wuk_scale`` and ``wuvout``.  fp16 GEMMs are computed in fp32
+    and rounded once, as a library GEMM with fp32 accumulation does; the append uses the Triton kernel's rounding
+    (the block imports fd_kernel/destindex_copy_quantize_latent.py).  Mutates the caches like the block; returns
+    ``[B, 1, hidden]`` fp16.
+    """
+    B = x16.shape[0]
+    H, D = num_heads, head_dim
+    xn = rms_norm(x16.view(B, -1), w["input_layernorm_weight"], 1e-5)                       # :119-120
+    R = w["up_proj_q"].shape[0]
+    lat_q = (xn.float() @ w["down_proj_q"].float().t()).half().view(B, H, R)                # :122
+    wuq = w["up_proj_q"].view(H, R, D)                                                      # :123 (a plain reshape)
+    q = torch.einsum("bhr,hrd->bhd", lat_q.float(), wuq.float()).half()                     # :124
+    lat_kv = (xn.float() @ w["down_proj_kv"].float().t()).half().view(B, 2, H * R)          # :128
+    offs = [h * R for h in range(H + 1)]
+    attention.cache_append(lat_kv[:, 0], mem_index, offs, cache_k.view(cache_k.shape[0], -1), scale_k, "triton")   # :129
+    attention.cache_append(lat_kv[:, 1], mem_index, offs, cache_v.view(cache_v.shape[0], -1), scale_v, "triton")   # :130
+    o = attention.decode_rope_recon(q, cache_k, scale_k, cache_v, scale_v, w["wuk_q"], w["wuk_scale"],
+                                    req_to_token, b_req_idx, b_seq_len, theta=theta)        # :132-143
+    y = (o.reshape(B, H * R).float() @ w["wuvout"].float()).half()                          # :145
+    return (y.float() + xn.float()).half().view(B, 1, -1)

@@ -132,13 +132,31 @@ def edge_latents(T, H, R, g):
 
 
 # ------------------------------------------------------------------ kernels/ side
-def gen_kernels_side():
-    sys.path.insert(0, os.path.join(REF, "kernels", "layer_bench"))
-    sys.path.insert(0, os.path.join(REF, "kernels", "layer_bench", "fd_kernel"))
+class Fixed:
+    """Stands in for a triton.autotune object: launches the wrapped kernel with one fixed configuration."""
+
+    def __init__(self, auto, **cfg):
+        self.fn = auto.fn
+        self.cfg = cfg
+        self.best_config = types.SimpleNamespace(kwargs=cfg)
+
+    def __getitem__(self, grid):
+        gr = grid(self.cfg) if callable(grid) else grid
+        return lambda *a, **k: self.fn[gr](*a, **k, **self.cfg)
+
+
+def _kernels_side_imports():
+    for d in ("layer_bench", os.path.join("layer_bench", "fd_kernel")):
+        path = os.path.join(REF, "kernels", d)
+        if path not in sys.path:
+            sys.path.insert(0, path)
     tl.extra.cuda.libdevice.fast_powf = _powf
     tl.extra.cuda.libdevice.fast_cosf = _cosf
     tl.extra.cuda.libdevice.fast_sinf = _sinf
 
+
+def gen_kernels_side():
+    _kernels_side_imports()
     import benchmark_triton_int8_layer as bench
     from ffn_kernel import baseline_kernel
     import destindex_copy_quantize_latent as dcq
@@ -164,16 +182,6 @@ def gen_kernels_side():
     save("wuk_quant", wuk=wuk, wuk_q=wq, wuk_scale=ws)
 
     # 3. decode attention: stage 1 + stage 2 in the interpreter, two fixed block configurations
-    class Fixed:
-        def __init__(self, auto, **cfg):
-            self.fn = auto.fn
-            self.cfg = cfg
-            self.best_config = types.SimpleNamespace(kwargs=cfg)
-
-        def __getitem__(self, grid):
-            gr = grid(self.cfg) if callable(grid) else grid
-            return lambda *a, **k: self.fn[gr](*a, **k, **self.cfg)
-
     auto = s1._fwd_kernel_flash_int8_latent_decode_rope_stage1
     B, Hq, Hkv, D, Rk, Rv, S = 3, 4, 2, 32, 16, 32, 300
     q = torch.randn(B, Hq, D, generator=g).half()
@@ -199,6 +207,55 @@ def gen_kernels_side():
         outs["o_" + tag] = o
     save("attn_rope_recon", q=q, cache_k=kq, scale_k=ks, cache_v=vq, scale_v=vs, wk_q=wq, wk_scale=ws,
          req_to_token=slots, b_req_idx=b_req, b_seq_len=b_len, **outs)
+
+
+def gen_attention_block():
+    """One decode step of the reference's whole Int8AttentionBlock (kernels/layer_bench/ffn_kernel/baseline_kernel.py:
+    56-145) on the CPU: fp16 projections by PyTorch, append and attention kernels in the Triton interpreter.  The
+    wrapper's scratch buffers, which it places on "cuda", are given to it on the CPU instead."""
+    _kernels_side_imports()
+    import functools
+    import benchmark_triton_int8_layer as bench
+    from ffn_kernel import baseline_kernel
+    import flash_int8_latent_per_head_decoding_rope_stage1 as s1
+
+    torch.manual_seed(11)
+    g = torch.Generator().manual_seed(11)
+    hidden, H, D, ratio = 128, 4, 32, 0.5
+    blk = baseline_kernel.Int8AttentionBlock(hidden, H, D, ratio, device="cpu")
+    blk.input_layernorm_weight.data = (1 + 0.1 * torch.randn(hidden, generator=g)).half()
+    R = blk.rank_head
+    lens = [40, 17, 1]
+    B, S = len(lens), max(lens)
+    N = B * S + 5
+
+    class State:
+        pass
+    st = State()
+    st.batch_size, st.max_len_in_batch = B, S
+    st.b_seq_len = torch.tensor(lens, dtype=torch.int32)
+    st.b_req_idx = torch.tensor([1, 2, 0], dtype=torch.int32)
+    st.req_manager = State()
+    st.req_manager.req_to_token_indexs = torch.randperm(N, generator=g)[:B * S].to(torch.int32).view(B, S)
+    st.mem_index = st.req_manager.req_to_token_indexs[st.b_req_idx.long(), st.b_seq_len.long() - 1].contiguous()
+
+    kq, ks, _ = bench.quantize_latent_tensor(torch.randn(N, H, R, generator=g).half(), return_dequantized=False)
+    vq, vs, _ = bench.quantize_latent_tensor(torch.randn(N, H, R, generator=g).half(), return_dequantized=False)
+    before = dict(cache_k=kq.clone(), scale_k=ks.clone(), cache_v=vq.clone(), scale_v=vs.clone())
+    x = torch.randn(B, 1, hidden, generator=g).half()
+
+    s1._fwd_kernel_flash_int8_latent_decode_rope_stage1 = Fixed(s1._fwd_kernel_flash_int8_latent_decode_rope_stage1,
+                                                                BLOCK_N=16, BLOCK_SEQ=256)
+    on_cpu = lambda shape, dtype, device=None: torch.zeros(*shape, dtype=dtype)
+    baseline_kernel.token_decode_attention_flash_int8_latent_per_head_decoding_rope = functools.partial(
+        baseline_kernel.token_decode_attention_flash_int8_latent_per_head_decoding_rope, alloc_tensor_func=on_cpu)
+    y = blk(x, kq, ks, vq, vs, st)
+    save("attention_block", x=x, y=y, num_heads=np.int64(H), head_dim=np.int64(D), rank_head=np.int64(R),
+         down_proj_q=blk.down_proj_q.weight, down_proj_kv=blk.down_proj_kv.weight, o_proj=blk.o_proj.weight,
+         up_proj_q=blk.up_proj_q, up_proj_k=blk.up_proj_k, up_proj_v=blk.up_proj_v,
+         input_layernorm_weight=blk.input_layernorm_weight, wuk_q=blk.wuk_q, wuk_scale=blk.wuk_scale, wuvout=blk.wuvout,
+         req_to_token=st.req_manager.req_to_token_indexs, b_req_idx=st.b_req_idx, b_seq_len=st.b_seq_len,
+         mem_index=st.mem_index, cache_k_after=kq, scale_k_after=ks, cache_v_after=vq, scale_v_after=vs, **before)
 
 
 # ------------------------------------------------------------------ fake_quant/ side
@@ -360,9 +417,11 @@ def gen_partial_hadamard():
 
 if __name__ == "__main__":
     with torch.no_grad():
-        if len(sys.argv) > 2 and sys.argv[2] == "partial_hadamard":
-            gen_partial_hadamard()
+        only = {"partial_hadamard": gen_partial_hadamard, "attention_block": gen_attention_block}
+        if len(sys.argv) > 2 and sys.argv[2] in only:
+            only[sys.argv[2]]()
             sys.exit(0)
         gen_kernels_side()
+        gen_attention_block()
         gen_fake_quant_side()
         gen_partial_hadamard()

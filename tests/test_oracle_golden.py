@@ -158,3 +158,38 @@ def test_partial_hadamard_across_heads_matches_reference_wrapper():
     assert torch.equal((q.float() * s[:, None]).half(), g["fake_quant"])
     y28 = ffn.partial_hadamard_heads_hadk(g["x28"], g["head_dim"], g["had28"].float())
     assert (y28.float() - g["rotated28"].float()).abs().max() <= 2 ** -10 * g["rotated28"].float().abs().max()
+
+
+def test_int8_attention_block_against_the_reference_module():
+    """The oracle's restatement of the whole attention block against one decode step of the reference's module
+    (projections by PyTorch on the CPU, append and attention kernels in the Triton interpreter)."""
+    from oracle import layer as olayer
+    g = load_golden("attention_block")
+    ck, sk, cv, sv = (g[k].clone() for k in ("cache_k", "scale_k", "cache_v", "scale_v"))
+    y = olayer.int8_attention_block(g["x"], g, ck, sk, cv, sv, g["req_to_token"], g["b_req_idx"], g["b_seq_len"],
+                                    g["mem_index"], int(g["num_heads"]), int(g["head_dim"]))
+    # the appended rows: bit-exact codes and scales; every other row untouched
+    assert torch.equal(ck, g["cache_k_after"]) and torch.equal(cv, g["cache_v_after"])
+    assert torch.equal(sk, g["scale_k_after"]) and torch.equal(sv, g["scale_v_after"])
+    rows = g["mem_index"].long()
+    assert not torch.equal(g["cache_k"][rows], g["cache_k_after"][rows])
+    assert rel_to_norm(y.float(), g["y"].float()) < 5e-4
+
+
+def test_attention_block_derived_buffers_match_the_reference():
+    """lsvd_b200.block.Int8AttentionBlock derives wuk_q / wuk_scale / wuvout from the parameters as the reference does."""
+    from lsvd_b200.block import Int8AttentionBlock
+    g = load_golden("attention_block")
+    H, D, R = int(g["num_heads"]), int(g["head_dim"]), int(g["rank_head"])
+    blk = Int8AttentionBlock(H * D, H, D, (R + 0.5) / D, device="cpu")
+    assert blk.rank_head == R
+    with torch.no_grad():
+        for name in ("up_proj_q", "up_proj_k", "up_proj_v", "input_layernorm_weight"):
+            getattr(blk, name).copy_(g[name])
+        for name in ("down_proj_q", "down_proj_kv", "o_proj"):
+            getattr(blk, name).weight.copy_(g[name])
+    blk.refresh()
+    assert torch.equal(blk.wuk_q, g["wuk_q"]) and torch.equal(blk.wuk_scale, g["wuk_scale"])
+    assert rel_to_norm(blk.wuvout.float(), g["wuvout"].float()) < 1e-3
+    same = Int8AttentionBlock.from_module(blk)
+    assert torch.equal(same.wuk_q, blk.wuk_q) and torch.equal(same.w_latent, blk.w_latent)
