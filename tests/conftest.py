@@ -26,7 +26,8 @@ def pytest_collection_modifyitems(config, items):
 
 def load_golden(name):
     with np.load(os.path.join(GOLDEN, name + ".npz")) as z:
-        return {k: torch.from_numpy(z[k]) if z[k].shape != () else int(z[k]) for k in z.files}
+        return {k: torch.from_numpy(z[k]) if z[k].shape != () else (float(z[k]) if z[k].dtype.kind == 'f' else int(z[k]))
+                for k in z.files}
 
 
 def unpack_had(bits, K):

@@ -258,6 +258,39 @@ def gen_attention_block():
          mem_index=st.mem_index, cache_k_after=kq, scale_k_after=ks, cache_v_after=vq, scale_v_after=vs, **before)
 
 
+def gen_mixffn():
+    """The reference's mixffn W8A8 FFN (kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py): a SwiGLUFFN from its seeded
+    generator converted by ``MixedFFNGateUpDenseLatentFused.from_float`` and run through ``forward_stages`` with all
+    eleven Triton kernels in the interpreter.  Each autotuned kernel runs the configuration with the smallest row-max
+    tile, the one the wrappers size their scratch rows for."""
+    _kernels_side_imports()
+    from triton.runtime.autotuner import Autotuner
+
+    def run_fixed(self, *args, **kwargs):
+        cfg = min(self.configs, key=lambda c: (c.kwargs.get("BLOCK_R", 0) if "BLOCK_N" not in c.kwargs else 0,
+                                               c.kwargs.get("BLOCK_N", 0), c.kwargs.get("BLOCK_M", 0)))
+        self.best_config = cfg
+        return self.fn.run(*args, **kwargs, **cfg.kwargs)
+    Autotuner.run = run_fixed
+    from ffn_kernel import mix_ffn_kernel as mk
+
+    hidden, d_ffn, M = 512, 1024, 5
+    torch.manual_seed(23)                      # the low-rank factors come from the global generator (:545-554)
+    x, module = mk.make_ffn_inputs(1, M, hidden, d_ffn, seed=7, device="cpu", svd_ratio=0.5, rank_ratio=0.5, round_to=64)
+    x[0, 3] = 0                                # a token of zeros: every scale falls to its floor
+    mixed = mk.MixedFFNGateUpDenseLatentFused.from_float(module, 0.5, 0.5, 64)
+    st = mixed.forward_stages(x)
+    wts = {"norm_weight": mixed.norm_weight}
+    for name in ("up", "gate", "down"):
+        proj = getattr(mixed, name + "_proj")
+        wts.update({name + "_a_q": proj.svd_branch.a_q, name + "_a_scale": proj.svd_branch.a_scale,
+                    name + "_b_q": proj.svd_branch.b_q, name + "_b_scale": proj.svd_branch.b_scale,
+                    name + "_q": proj.dense_branch.q, name + "_scale": proj.dense_branch.scale})
+    stages = {"st_" + k: v for k, v in st.items() if isinstance(v, torch.Tensor)}
+    save("mixffn", x=x, eps=np.float64(mixed.eps), fp16_up_w=module.up_proj.weight, fp16_gate_w=module.gate_proj.weight,
+         fp16_down_w=module.down_proj.weight, **wts, **stages)
+
+
 # ------------------------------------------------------------------ fake_quant/ side
 def gen_fake_quant_side():
     for m in [k for k in sys.modules if k == "utils" or k.startswith("utils.")]:
@@ -417,11 +450,12 @@ def gen_partial_hadamard():
 
 if __name__ == "__main__":
     with torch.no_grad():
-        only = {"partial_hadamard": gen_partial_hadamard, "attention_block": gen_attention_block}
+        only = {"partial_hadamard": gen_partial_hadamard, "attention_block": gen_attention_block, "mixffn": gen_mixffn}
         if len(sys.argv) > 2 and sys.argv[2] in only:
             only[sys.argv[2]]()
             sys.exit(0)
         gen_kernels_side()
         gen_attention_block()
+        gen_mixffn()
         gen_fake_quant_side()
         gen_partial_hadamard()

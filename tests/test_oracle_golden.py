@@ -193,3 +193,40 @@ def test_attention_block_derived_buffers_match_the_reference():
     assert rel_to_norm(blk.wuvout.float(), g["wuvout"].float()) < 1e-3
     same = Int8AttentionBlock.from_module(blk)
     assert torch.equal(same.wuk_q, blk.wuk_q) and torch.equal(same.w_latent, blk.w_latent)
+
+
+def _mix_weights(g):
+    return {k: v for k, v in g.items() if not k.startswith(("st_", "fp16_")) and k not in ("x", "eps")}
+
+
+def test_mixffn_pipeline_against_the_reference_stage_by_stage():
+    """oracle.mixffn.forward_stages against the reference's forward_stages (its eleven Triton kernels, interpreter)."""
+    from oracle import mixffn
+    g = load_golden("mixffn")
+    x = g["x"].reshape(-1, g["x"].shape[-1])
+    st = mixffn.forward_stages(x, _mix_weights(g), eps=float(g["eps"]))
+    exact = ["x_q", "x_scale", "up_svd_rank_fp", "gate_svd_rank_fp", "up_svd_rank_scale", "gate_svd_rank_scale",
+             "up_svd_rank_q", "gate_svd_rank_q", "up_dense_out_acc", "gate_dense_out_acc", "svd_mid_scale",
+             "dense_mid_scale", "mid_scale", "mid_q", "down_svd_rank_acc", "down_svd_rank_scale", "down_svd_rank_q",
+             "down_svd_out_fp", "down_dense_out_fp", "down_fp"]
+    for name in exact:
+        assert torch.equal(st[name], g["st_" + name]), name
+    # SwiGLU outputs: sigmoid implementations may differ in the last bit of fp32, visible as one fp16 ulp at most
+    for name in ("svd_mid_fp", "dense_mid_fp"):
+        a, b = st[name].float(), g["st_" + name].float()
+        assert ((a - b).abs() <= 1e-3 * b.abs() + 1e-7).all(), name
+    assert torch.equal(st["out"], g["st_out"].reshape(st["out"].shape))
+    # the token of zeros: scales at their floor, the residual passes through
+    assert st["x_scale"][3] == 0 and (st["out"][3] == 0).all()
+
+
+def test_mixffn_weight_conversion_matches_the_reference():
+    from oracle import mixffn
+    g = load_golden("mixffn")
+    for name, key in (("up", "fp16_up_w"), ("gate", "fp16_gate_w"), ("down", "fp16_down_w")):
+        w = g[key]
+        s = mixffn.svd_out_from_ratio(w.shape[0], 0.5, 64)
+        assert s == g[name + "_b_q"].shape[0]
+        assert mixffn.rounded_rank(w.shape[1], s, 0.5, 64) == g[name + "_a_q"].shape[0]
+        q, sc = mixffn.quantize_weights_per_channel(w[s:].contiguous())
+        assert torch.equal(q, g[name + "_q"]) and torch.equal(sc, g[name + "_scale"])
