@@ -281,6 +281,11 @@ int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* args, void* 
  * optionally for a second weight matrix w2 (with its own activations a2, or the same ones) in the same pass.
  *   epilogue 0: out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n])              (a quantised Linear)
  *   epilogue 1: g = that for (w, a), u = that for (w2, a2); out = fp16(fp16(silu(g)) * u) (gate/up pair)
+ *   epilogue 2: the same pair with g, u kept in fp32: out = fp16(u * (g * sigmoid(g))), the convention of
+ *               kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:353-362,1885-1889 (forms 0 and 3 only)
+ * With row_absmax the call also folds max |fp32 value before the fp16 rounding| of every token into a device
+ * word per token (atomic maximum on the float's bit pattern; the caller zeroes it), which is what the reference's
+ * tiled kernels hand to their next quantiser (mix_ffn_kernel.py:1229-1232, 1894-1895).
  * n and k multiples of 16, rows 16-byte aligned.  Replaces the reference's fp16 Linear on
  * fake-quantised tensors (ActQuantWrapper.forward, fake_quant/utils/quant_utils.py:319-333) and, on the kernel
  * side, the w8a8 matmul + dequant kernels of kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:968-1021,1292-1338. */
@@ -305,6 +310,10 @@ typedef struct lsvd_gemv_args {
                                  /*    (LSVD_ERR_UNSUPPORTED beyond); 2: TMA-fed kernel whose warps      */
                                  /*    share the token rows (built for 17..64 tokens, valid for any m);   */
                                  /* 3: register-fed kernel for any m.  Same values in every form.        */
+  uint32_t* row_absmax;          /* optional device words [m * row_absmax_stride]: see above (forms 0, 3)  */
+  int64_t row_absmax_stride;     /* words between two tokens                                              */
+  int32_t absmax_split;          /* 0: one word per token; else channels >= absmax_split (a multiple of  */
+                                 /* 16) go to the token's second word                                     */
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 
@@ -375,6 +384,60 @@ typedef struct lsvd_i8gemm_args {
   int64_t a2_scale_stride;
 } lsvd_i8gemm_args;
 int lsvd_i8gemm_prefill(const lsvd_i8gemm_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Quantisers of the reference's "mixffn" W8A8 pipeline (kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py), whose
+ * conventions differ from the fake_quant ones: scale = max(absmax / 127, 1e-8) with the absmax of the fp32 values,
+ * codes = clamp(trunc(v / scale +- 0.5), -128, 127) (round half away from zero), divisions in fp32.
+ * Together with lsvd_w8a8_gemv (epilogue 2, row_absmax) they replace its eleven Triton kernels:
+ *   lsvd_mix_rmsnorm_quant   _rmsnorm_quant_kernel (:101-165)
+ *   lsvd_w8a8_gemv           the tl.dot kernels and their dequantising / SwiGLU epilogues (:324-375, :1156-1342, :1822-1895)
+ *   lsvd_mix_group_quant     _dual_quantize_with_scale_vec_kernel, _dual_quantize_with_shared_scale_vec_kernel (:1070-1150)
+ *   lsvd_mix_acc_quant       _svd_rank_dequant_quant_down_kernel (:795-837)
+ * ------------------------------------------------------------------------------------------- */
+typedef struct lsvd_mix_rmsnorm_quant_args {
+  int32_t rows, cols;
+  const void* x;                 /* device fp16 [rows, cols]                                                     */
+  int64_t x_row_stride;
+  const void* norm_weight;       /* device fp16 [cols]                                                           */
+  float eps;
+  int8_t* q;                     /* codes of (x * rsqrt(mean x^2 + eps)) * weight, all in fp32                    */
+  int64_t q_row_stride;
+  float* scale;                  /* device fp32 [rows]: the scale after its rounding to fp16, which is the value  */
+                                 /* the reference stores and later stages dequantise with (:34, :149-150)         */
+  uint32_t* clear_words;         /* optional: clear_per_row words per row are set to zero (the row_absmax words   */
+  int32_t clear_per_row;         /* of the products that follow)                                                  */
+} lsvd_mix_rmsnorm_quant_args;
+int lsvd_mix_rmsnorm_quant(const lsvd_mix_rmsnorm_quant_args* args, void* stream);
+
+typedef struct lsvd_mix_group_quant_args {
+  int32_t rows, cols;
+  int32_t split;                 /* columns [0, split) use the token's first absmax word, [split, cols) the second */
+                                 /* (split == cols: one group)                                                    */
+  int32_t shared;                /* non-zero: both groups use the larger of the two maxima (:2075)                 */
+  const void* x;                 /* device fp16 [rows, cols]                                                      */
+  int64_t x_row_stride;
+  const uint32_t* absmax;        /* device words written through lsvd_gemv_args.row_absmax                         */
+  int64_t absmax_stride;         /* words between two tokens                                                      */
+  int8_t* q;
+  int64_t q_row_stride;
+  float* scale;                  /* device fp32: scale[row * scale_stride + group] (group 0 only when shared)      */
+  int64_t scale_stride;
+} lsvd_mix_group_quant_args;
+int lsvd_mix_group_quant(const lsvd_mix_group_quant_args* args, void* stream);
+
+typedef struct lsvd_mix_acc_quant_args {
+  int32_t rows, cols;
+  const int32_t* acc;            /* device int32 [rows, cols] accumulators                                        */
+  int64_t acc_row_stride;
+  const float* row_scale;        /* value = (fp32(acc) * row_scale[row]) * col_scale[col], quantised from fp32     */
+  int64_t row_scale_stride;
+  const float* col_scale;
+  int8_t* q;
+  int64_t q_row_stride;
+  float* scale;                  /* device fp32 [rows]                                                            */
+} lsvd_mix_acc_quant_args;
+int lsvd_mix_acc_quant(const lsvd_mix_acc_quant_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -10,10 +10,11 @@ from .attention import (LatentCacheLayout, destindex_copy_quantize_latent, cache
                         token_decode_attention_int8_latent_absorb,
                         token_decode_attention_flash_int8_latent_per_head_decoding_rope, LatentDecodeAttention, InferState)
 from .block import Int8AttentionBlock
+from .mixffn import MixedFFNGateUpDenseLatentFused, b200_mixffn
 from .ffn import (HybridFFN, quantize_weight_rtn, act_quant, hadamard_pack, hadamard_quant, heads_hadamard_quant, w8a8_gemv,
                   i8gemm)
 
 __all__ = ["LsvdError", "LatentCacheLayout", "destindex_copy_quantize_latent", "cache_append",
            "token_decode_attention_int8_latent_absorb", "token_decode_attention_flash_int8_latent_per_head_decoding_rope",
-           "LatentDecodeAttention", "InferState", "Int8AttentionBlock", "HybridFFN", "quantize_weight_rtn", "act_quant", "hadamard_pack",
+           "LatentDecodeAttention", "InferState", "Int8AttentionBlock", "MixedFFNGateUpDenseLatentFused", "b200_mixffn", "HybridFFN", "quantize_weight_rtn", "act_quant", "hadamard_pack",
            "hadamard_quant", "heads_hadamard_quant", "w8a8_gemv", "i8gemm"]

@@ -112,6 +112,31 @@ class GemvArgs(C.Structure):
         ("epilogue", C.c_int32), ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("out_col", C.c_int32),
         ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
         ("status_word", C.c_void_p), ("form", C.c_int32),
+        ("row_absmax", C.c_void_p), ("row_absmax_stride", C.c_int64), ("absmax_split", C.c_int32),
+    ]
+
+
+class MixRmsnormQuantArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("cols", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
+        ("norm_weight", C.c_void_p), ("eps", C.c_float), ("q", C.c_void_p), ("q_row_stride", C.c_int64),
+        ("scale", C.c_void_p), ("clear_words", C.c_void_p), ("clear_per_row", C.c_int32),
+    ]
+
+
+class MixGroupQuantArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("cols", C.c_int32), ("split", C.c_int32), ("shared", C.c_int32),
+        ("x", C.c_void_p), ("x_row_stride", C.c_int64), ("absmax", C.c_void_p), ("absmax_stride", C.c_int64),
+        ("q", C.c_void_p), ("q_row_stride", C.c_int64), ("scale", C.c_void_p), ("scale_stride", C.c_int64),
+    ]
+
+
+class MixAccQuantArgs(C.Structure):
+    _fields_ = [
+        ("rows", C.c_int32), ("cols", C.c_int32), ("acc", C.c_void_p), ("acc_row_stride", C.c_int64),
+        ("row_scale", C.c_void_p), ("row_scale_stride", C.c_int64), ("col_scale", C.c_void_p),
+        ("q", C.c_void_p), ("q_row_stride", C.c_int64), ("scale", C.c_void_p),
     ]
 
 
@@ -165,6 +190,9 @@ SIGNATURES = {
     "lsvd_hadamard_pack": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),
     "lsvd_i8gemm_prefill": (C.c_int, [C.POINTER(I8GemmArgs), C.c_void_p]),
+    "lsvd_mix_rmsnorm_quant": (C.c_int, [C.POINTER(MixRmsnormQuantArgs), C.c_void_p]),
+    "lsvd_mix_group_quant": (C.c_int, [C.POINTER(MixGroupQuantArgs), C.c_void_p]),
+    "lsvd_mix_acc_quant": (C.c_int, [C.POINTER(MixAccQuantArgs), C.c_void_p]),
     "lsvd_attn_decode_plan": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
                                         C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
 }

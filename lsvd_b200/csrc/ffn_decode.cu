@@ -851,8 +851,16 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
       sum0 += red[wi * (NMAT * NT * 4 * 32) + e];
       if (DUAL) sum1 += red[wi * (NMAT * NT * 4 * 32) + NT * 4 * 32 + e];
     }
-    if (tok >= p.m) continue;
-    gemv_store<DUAL, SPLIT_B>(p, tok, row, sum0, sum1);
+    float av = 0.f;
+    if (tok < p.m) av = gemv_store<DUAL, SPLIT_B>(p, tok, row, sum0, sum1);
+    if (p.row_absmax != nullptr) {
+      // the eight lanes that share (el & 3) hold one token's values of eight channels (e >> 5 is uniform in a warp)
+      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 4));
+      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 8));
+      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 16));
+      if (el < 4 && tok < p.m)
+        atomicMax(p.row_absmax + tok * p.row_absmax_stride + (row0 >= p.absmax_split ? 1 : 0), __float_as_uint(av));
+    }
   }
 }
 
@@ -1028,7 +1036,10 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   if (!a->w || !a->a) return LSVD_ERR_INVALID_ARG;
   if (a->out != nullptr && (!a->w_scale || !a->a_scale)) return LSVD_ERR_INVALID_ARG;
   const bool dual = a->w2 != nullptr;
-  if (dual != (a->epilogue == 1)) return LSVD_ERR_INVALID_ARG;
+  if (dual != (a->epilogue == 1 || a->epilogue == 2) || a->epilogue < 0 || a->epilogue > 2) return LSVD_ERR_INVALID_ARG;
+  const bool fp32_form = a->epilogue == 2 || a->row_absmax != nullptr;     // built into the register-fed kernel only
+  if (fp32_form && (a->form == 1 || a->form == 2)) return LSVD_ERR_UNSUPPORTED;
+  if (a->row_absmax != nullptr && (a->out == nullptr || a->absmax_split < 0 || (a->absmax_split % 16))) return LSVD_ERR_INVALID_ARG;
   if (dual && a->out != nullptr && !a->w2_scale) return LSVD_ERR_INVALID_ARG;
   const bool split = dual && a->a2 != nullptr;
   if (split && a->out != nullptr && !a->a2_scale) return LSVD_ERR_INVALID_ARG;
@@ -1045,6 +1056,8 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   p.acc_out = a->acc_out; p.acc2_out = a->acc2_out;
   p.status_word = a->status_word;
   p.m = a->m; p.n = a->n; p.k = a->k; p.epilogue = a->epilogue;
+  p.row_absmax = a->row_absmax; p.row_absmax_stride = a->row_absmax_stride;
+  p.absmax_split = a->absmax_split > 0 ? a->absmax_split : a->n;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->form == 1) return a->m <= 16 ? launch_gemv_streamed(p, dual, split, st) : LSVD_ERR_UNSUPPORTED;
   if (a->form == 2) return launch_gemv_wide(p, dual, split, st);
@@ -1052,7 +1065,7 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   // more than 32 tokens and a large matrix: the form that shares the token rows between a block's warps
   // (measured: 35.6 vs 48.9 us for the 45 MB gate/up pair at 64 tokens; no gain at 32 tokens or below 16 MB)
   const int64_t weight_bytes = static_cast<int64_t>(a->n) * a->k * (dual ? 2 : 1);
-  if (a->form == 0 && a->m > 32 && weight_bytes >= (16ll << 20)) return launch_gemv_wide(p, dual, split, st);
+  if (a->form == 0 && !fp32_form && a->m > 32 && weight_bytes >= (16ll << 20)) return launch_gemv_wide(p, dual, split, st);
   if (a->m <= 8) return launch_gemv_nt<1>(p, dual, split, st);
   if (a->m <= 16) return launch_gemv_nt<2>(p, dual, split, st);
   if (a->m <= 32) return launch_gemv_nt<4>(p, dual, split, st);

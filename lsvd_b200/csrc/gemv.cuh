@@ -15,6 +15,9 @@ struct GemvParams {
   int32_t* acc_out; int32_t* acc2_out;
   int32_t* status_word;
   int32_t m, n, k, epilogue;
+  // optional per-token maximum of |fp32 value| over the output channels, kept as the bit pattern of a non-negative
+  // float (ordered like an unsigned integer): slot 0 for channels below absmax_split, slot 1 from there on
+  uint32_t* row_absmax; int64_t row_absmax_stride; int32_t absmax_split;
 };
 
 // The TMA-fed persistent form (gemv_tma.cu), for at most 16 tokens.
@@ -35,24 +38,34 @@ __device__ __forceinline__ uint4 ldg_u4(const int8_t* p) { return __ldg(reinterp
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 // Dequantise, gate, add the residual and store one element; sum1 / the second scales are used by gate/up pairs.
+// Returns |fp32 value| before it is rounded to fp16 (the quantity the all-fp32 pipeline takes its next scale from).
 template <bool DUAL, bool SPLIT_B>
-__device__ __forceinline__ void gemv_store(const GemvParams& p, int tok, int row, int sum0, int sum1) {
+__device__ __forceinline__ float gemv_store(const GemvParams& p, int tok, int row, int sum0, int sum1) {
   if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = sum0;
   if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = sum1;
-  if (p.out == nullptr) return;
+  if (p.out == nullptr) return 0.f;
   const float sa = p.a_scale[tok * p.a_scale_stride];
-  const __half v0 = __float2half_rn((static_cast<float>(sum0) * sa) * p.w_scale[row]);
-  __half res = v0;
+  const float f0 = (static_cast<float>(sum0) * sa) * p.w_scale[row];
+  float f = f0;
+  __half res = __float2half_rn(f0);
   if (DUAL) {
     const float sb = SPLIT_B ? p.a2_scale[tok * p.a2_scale_stride] : sa;
-    const __half u = __float2half_rn((static_cast<float>(sum1) * sb) * p.w2_scale[row]);
-    // silu in fp32 rounded to fp16, then an fp16 product: how PyTorch evaluates F.silu(g) * u on fp16 tensors
-    const __half sg = __float2half_rn(silu_f(__half2float(v0)));
-    res = __float2half_rn(__half2float(sg) * __half2float(u));
+    const float f1 = (static_cast<float>(sum1) * sb) * p.w2_scale[row];
+    if (p.epilogue == 2) {
+      // all in fp32, one rounding: up * (gate * sigmoid(gate))
+      f = f1 * (f0 * (1.0f / (1.0f + expf(-f0))));
+      res = __float2half_rn(f);
+    } else {
+      const __half u = __float2half_rn(f1);
+      // silu in fp32 rounded to fp16, then an fp16 product: how PyTorch evaluates F.silu(g) * u on fp16 tensors
+      const __half sg = __float2half_rn(silu_f(__half2float(res)));
+      res = __float2half_rn(__half2float(sg) * __half2float(u));
+    }
   }
   if (p.residual != nullptr)       // fp16 add of the fp16 result and the residual, as the reference's `x @ W + residual`
     res = __float2half_rn(__half2float(res) + __half2float(p.residual[static_cast<int64_t>(tok) * p.residual_row_stride + row]));
   p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = res;
+  return fabsf(f);
 }
 #endif
 

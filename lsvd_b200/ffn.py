@@ -132,11 +132,14 @@ def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False
 
 
 def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a2_scale=None, out=None, out_col=0,
-              want_acc=False, want_out=True, residual=None, form=0, status_word=None):
+              want_acc=False, want_out=True, residual=None, form=0, status_word=None, fp32_swiglu=False,
+              row_absmax=None, absmax_split=0):
     """acc = a_q @ w_q^T (int32, exact) for 1..64 tokens, dequantised to fp16; with (w2, a2) a gate/up pair whose
     result is silu(gate) * up.  Returns (out fp16 [m, n] or the passed tensor, acc int32 or None, acc2 or None).
     ``form`` 0 is the register-fed kernel, 1 the persistent TMA-fed one (at most 16 tokens); ``status_word`` (int32
-    device tensor) receives LSVD_ERR_TIMEOUT if a pipeline wait of form 1 gives up."""
+    device tensor) receives LSVD_ERR_TIMEOUT if a pipeline wait of form 1 gives up.  ``fp32_swiglu`` selects the
+    all-fp32 gate/up epilogue ``up * (gate * sigmoid(gate))``; ``row_absmax`` (int32 view of the words, strided by
+    token) collects max |fp32 value| per token, channels from ``absmax_split`` on in the token's second word."""
     _require_cuda(a_q, w_q)
     m, k = a_q.shape
     n = w_q.shape[0]
@@ -156,7 +159,9 @@ def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a
     if a2_q is not None:
         g.a2, g.a2_row_stride, g.a2_scale = a2_q.data_ptr(), a2_q.stride(0), _ptr(a2_scale)
         g.a2_scale_stride = a2_scale.stride(0) if a2_scale is not None else 1
-    g.epilogue = 1 if dual else 0
+    g.epilogue = (2 if fp32_swiglu else 1) if dual else 0
+    if row_absmax is not None:
+        g.row_absmax, g.row_absmax_stride, g.absmax_split = row_absmax.data_ptr(), row_absmax.stride(0), absmax_split
     if out is not None:
         g.out, g.out_row_stride, g.out_col = out.data_ptr(), out.stride(0), out_col
     g.acc_out, g.acc2_out = _ptr(acc), _ptr(acc2)

@@ -79,4 +79,8 @@ def b200_ffn(x: torch.Tensor, module) -> torch.Tensor:
     return ffn(x2, norm_weight=norm_w, norm_eps=eps, residual=x2).view_as(x)
 
 
-NAME = {"b200": b200_ffn}
+from .mixffn import b200_mixffn  # noqa: E402  (the mixffn-structure provider lives beside its module)
+
+# "b200": the hybrid SVD/RTN FFN of fake_quant (Hadamard in front of the down projection);
+# "b200_mixffn": the reference's own mixffn structure and arithmetic, for a head-to-head with its "mixffn" provider
+NAME = {"b200": b200_ffn, "b200_mixffn": b200_mixffn}

@@ -88,11 +88,15 @@ def swiglu32(up: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     return up * (gate * torch.sigmoid(gate))
 
 
-def forward_stages(x16: torch.Tensor, w: dict, eps: float = 1e-6) -> dict:
+def forward_stages(x16: torch.Tensor, w: dict, eps: float = 1e-6, given: dict | None = None) -> dict:
     """``x16 [M, hidden]`` fp16.  ``w``: ``norm_weight`` fp16 and, for p in up/gate/down, ``{p}_a_q``, ``{p}_a_scale``,
     ``{p}_b_q``, ``{p}_b_scale`` (the low-rank branch of the first ``svd_out`` output columns) and ``{p}_q``,
-    ``{p}_scale`` (the dense branch of the remaining ones).  Returns the stage tensors under the reference's names."""
+    ``{p}_scale`` (the dense branch of the remaining ones).  Returns the stage tensors under the reference's names.
+    ``given`` may supply ``svd_mid_fp``, ``svd_mid_scale``, ``dense_mid_fp``, ``dense_mid_scale`` (the outputs of the two
+    SwiGLU stages, the only ones that depend on a transcendental function): the stages after them then start from those
+    values, which lets a test check everything downstream of another implementation's SwiGLU bit for bit."""
     st = {}
+    given = given or {}
     x_q, x_scale = rmsnorm_quantize_per_token(x16, w["norm_weight"], eps)
     st["x_q"], st["x_scale"] = x_q, x_scale
     # K5: both low-rank "A" products, dequantised; scales from the fp32 values (:1156-1232, :1689-1692)
@@ -107,12 +111,17 @@ def forward_stages(x16: torch.Tensor, w: dict, eps: float = 1e-6) -> dict:
     gate = dequant(i32_matmul(st["gate_svd_rank_q"], w["gate_b_q"]), st["gate_svd_rank_scale"], w["gate_b_scale"])
     sw = swiglu32(up, gate)
     st["svd_mid_fp"], st["svd_mid_scale"] = sw.half(), scale_from_absmax(sw.abs().amax(-1))
+    st["svd_mid_fp32"] = sw
     # K8 + K9 (:967-1021, :324-375): dense gate/up, SwiGLU in fp32
     st["up_dense_out_acc"] = i32_matmul(x_q, w["up_q"])
     st["gate_dense_out_acc"] = i32_matmul(x_q, w["gate_q"])
     sw = swiglu32(dequant(st["up_dense_out_acc"], x_scale, w["up_scale"]),
                   dequant(st["gate_dense_out_acc"], x_scale, w["gate_scale"]))
     st["dense_mid_fp"], st["dense_mid_scale"] = sw.half(), scale_from_absmax(sw.abs().amax(-1))
+    st["dense_mid_fp32"] = sw
+    for k in ("svd_mid_fp", "svd_mid_scale", "dense_mid_fp", "dense_mid_scale"):
+        if k in given:
+            st[k] = given[k]
     # K10 (:1114-1150): one scale for both halves (:2075)
     st["mid_scale"] = torch.maximum(st["svd_mid_scale"], st["dense_mid_scale"])
     st["mid_q"] = torch.cat([rha_codes(st["svd_mid_fp"].float(), st["mid_scale"][:, None]),
