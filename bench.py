@@ -60,6 +60,10 @@ WORKLOADS = {
                                desc="BASELINE config 1 through the module that takes the place of the reference's "
                                     "Int8AttentionBlock: RMSNorm, fp16 latent projections (library GEMMs, as in the "
                                     "reference), append, rotary int8 latent attention, composed output projection"),
+    "fig5_mixffn": dict(batch=32, context=0, aux="mixffn", hidden=4096, d_ffn=14336,
+                        desc="the reference's mixffn W8A8 FFN (its own structure and fp32 conventions) at the shape of "
+                             "its layer benchmark: hidden 4096, intermediate 14336, 32 tokens, svd_ratio 0.5, "
+                             "rank_ratio 0.5, round_to 64"),
     "c5_prefill_ffn": dict(batch=8, context=4096, aux="prefill_ffn",
                            desc="BASELINE config 5 prefill, FFN block of one layer: 8 x 4096 tokens through the hybrid "
                                 "SVD/RTN FFN 4096/11008 (rank 512, 50 % SVD channels) on the tcgen05 int8 GEMM"),
@@ -491,6 +495,48 @@ def run_aux(args, rank, world, local):
         h2d, d2h = x_in.numel() * 2, out.numel() * 2
         l2 = "cache + weights (%.0f MB) fit in L2: the figure is a warm-L2 one" % (abytes / 1e6)
         what = "RMSNorm + fp16 latent GEMM + query up-projection + append + rotary attention (3 launches) + fp16 output GEMM + residual"
+    elif w["aux"] == "mixffn":
+        from types import SimpleNamespace
+        from lsvd_b200.mixffn import MixedFFNGateUpDenseLatentFused
+        M, hid, dff = w["batch"], w["hidden"], w["d_ffn"]
+        lin = lambda o, i: SimpleNamespace(weight=(torch.randn(o, i, device=dev, generator=g) / i ** 0.5).half())
+        src = SimpleNamespace(norm=SimpleNamespace(weight=torch.randn(hid, device=dev, generator=g).half(), variance_epsilon=1e-6),
+                              up_proj=lin(dff, hid), gate_proj=lin(dff, hid), down_proj=lin(hid, dff))
+        mods = [MixedFFNGateUpDenseLatentFused.from_float(src, 0.5, 0.5, 64, seed=s) for s in range(2)]   # 2 x 131 MB > L2
+        del src
+        xs_host = [torch.randn(M, hid).half().pin_memory() for _ in range(8)]
+        xs = [t.to(dev) for t in xs_host]
+        x_in = torch.empty_like(xs[0])
+        out = torch.empty(M, hid, dtype=torch.float16, device=dev)
+        host_out = torch.empty(out.shape, dtype=torch.float16).pin_memory()
+        graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for mod in mods:
+                for _ in range(2):
+                    mod(x_in, out=out)
+        torch.cuda.current_stream().wait_stream(side)
+        for mod in mods:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                mod(x_in, out=out)
+            graphs.append(gr)
+        turn = [0]
+
+        def step():
+            graphs[turn[0] % 2].replay()
+            turn[0] += 1
+        feed = lambda i, host: x_in.copy_((xs_host if host else xs)[i % 8], non_blocking=True)
+        units, metric, launches = M, "decode_tokens_per_s", 10
+        m0 = mods[0]
+        wbytes = sum(getattr(m0, n).numel() for n in ("ab_a_q", "up_b_q", "gate_b_q", "up_q", "gate_q", "down_a_q", "down_b_q", "down_q"))
+        abytes = wbytes + M * hid * 4
+        roof = dict(kernel="whole mixffn step (10 launches: 7 weight-streaming products, 3 quantisers)", bound="hbm",
+                    peak=float(peaks.get("hbm_gbs", 6650.0)), unit="GB/s", work=abytes)
+        h2d, d2h = x_in.numel() * 2, out.numel() * 2
+        l2 = "two weight sets of %.0f MB alternate, so every step streams its weights from HBM" % (wbytes / 1e6)
+        what = "RMSNorm quantiser + low-rank and dense gate/up (fp32 SwiGLU) + shared quantiser + low-rank and dense down + residual; CUDA graph replay"
     else:
         M = w["batch"] * w["context"]
         ffn = make_ffn(dev, seed=50 + rank, copies=1)[0]
@@ -569,7 +615,7 @@ def run_aux(args, rank, world, local):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp16 out", "data": "synthetic",
         "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": w["batch"], "layers": 1, "step": what,
-                   "launch": "eager launches on one stream", "l2": l2},
+                   "launch": "CUDA graph replay of the step" if w["aux"] == "mixffn" else "eager launches on one stream", "l2": l2},
         "e2e": {"value": units * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * args.steps,
@@ -660,6 +706,15 @@ def cpu_baseline_aux(w, seconds_hint, threads):
         fn = lambda: oattn.decode_rope_recon(q, ck, sk, cv, sv, wk, wks, r2t, one, torch.tensor([L], dtype=torch.int32))
         per_call = hs / H                      # requests' worth of work per call
         sample = f"1 request, {hs} of {H} heads, context {L}" + (" (attention only, projections left out)" if w["aux"] == "block" else "")
+    elif w["aux"] == "mixffn":
+        from oracle import mixffn as omix
+        hid, dff, M = w["hidden"], w["d_ffn"], w["batch"]
+        mk = lambda o, i: (torch.randn(o, i, generator=gen) / i ** 0.5).half()
+        mw = omix.convert_swiglu(mk(dff, hid), mk(dff, hid), mk(hid, dff), torch.randn(hid, generator=gen).half(), 0.5, 0.5, 64, gen)
+        x = torch.randn(M, hid, generator=gen).half()
+        fn = lambda: omix.forward_stages(x, mw, 1e-6)
+        per_call = M
+        sample = f"all {M} tokens of a step"
     else:
         fw = synth.ffn_weights(FFN_SHAPE["d_in"], FFN_SHAPE["d_ffn"], FFN_SHAPE["rank"], FFN_SHAPE["n_svd"], seed=0,
                                had_K=synth.sign_matrix(FFN_SHAPE["K"]).float(), K=FFN_SHAPE["K"])
