@@ -60,6 +60,11 @@ WORKLOADS = {
                                desc="BASELINE config 1 through the module that takes the place of the reference's "
                                     "Int8AttentionBlock: RMSNorm, fp16 latent projections (library GEMMs, as in the "
                                     "reference), append, rotary int8 latent attention, composed output projection"),
+    "c4_layer_tp": dict(batch=64, heads=40, head_dim=128, context=8192, aux="tp", hidden=5120, d_ffn=13824,
+                        desc="BASELINE config 4, one decoder layer of the 13B shape (hidden 5120, 40 heads x 128, "
+                             "intermediate 13824 = 108 x 128) tensor-parallel over the ranks: batch 64, context 8192, "
+                             "ragged K/V ranks (mean 64); heads and FFN channels sharded, NCCL all-reduce per block and "
+                             "an all-gather of the FFN hidden vector; needs --gpus >= 2"),
     "fig5_mixffn": dict(batch=32, context=0, aux="mixffn", hidden=4096, d_ffn=14336,
                         desc="the reference's mixffn W8A8 FFN (its own structure and fp32 conventions) at the shape of "
                              "its layer benchmark: hidden 4096, intermediate 14336, 32 tokens, svd_ratio 0.5, "
@@ -628,6 +633,101 @@ def run_aux(args, rank, world, local):
     return line
 
 
+def run_tp(args, rank, world, local):
+    """One tensor-parallel decoder layer step (TPDecoderLayer): total work fixed, sharded over the ranks."""
+    import torch.distributed as dist
+    from lsvd_b200 import _lib, synth
+    from lsvd_b200.attention import InferState
+    from lsvd_b200.layer import TPDecoderLayer, make_layer_weights
+    from lsvd_b200.parallel import shard_layer
+    _lib.load()
+    if world < 2:
+        raise SystemExit("c4_layer_tp shards one layer over the ranks: launch it with --gpus 2, 4 or 8 under torchrun")
+    w = WORKLOADS[args.workload]
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    B, H, D, L, hid, dff, rq = w["batch"], w["heads"], w["head_dim"], w["context"], w["hidden"], w["d_ffn"], 64
+    kr, vr = synth.ragged_ranks(H, 64, seed=0), synth.ragged_ranks(H, 64, seed=1)
+    lw_full = make_layer_weights(hid, H, D, rq, kr, vr, seed=1)                       # same seed: same weights on every rank
+    fw_full = synth.ffn_weights(hid, dff, 640, dff // 2, seed=2, had_K=synth.sign_matrix(108, seed=0).float(), K=108, input_had=False)
+    lw, fw, info = shard_layer(lw_full, fw_full, kr, vr, rq, world, rank)
+    del lw_full, fw_full
+    to = lambda d: {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+    layer = TPDecoderLayer(to(lw), to(fw), info, D, rq, world)
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    n_slots = B * (L + 1)
+    rk_loc, rv_loc, h_loc = sum(info["k_ranks"]), sum(info["v_ranks"]), len(info["k_ranks"])
+    ck = torch.randint(-128, 128, (n_slots, rk_loc), dtype=torch.int8, device=dev, generator=g)
+    cv = torch.randint(-128, 128, (n_slots, rv_loc), dtype=torch.int8, device=dev, generator=g)
+    sk = (torch.rand(n_slots, h_loc, device=dev, generator=g) * 0.02 + 0.01).half()
+    sv = (torch.rand(n_slots, h_loc, device=dev, generator=g) * 0.02 + 0.01).half()
+    st = InferState(B, L + 1, [L + 1] * B, device=dev)
+    gx = torch.Generator().manual_seed(9)                                              # replicated hidden states
+    xs_host = [torch.randn(B, hid, generator=gx).half().pin_memory() for _ in range(4)]
+    xs = [t.to(dev) for t in xs_host]
+    x_in = torch.empty_like(xs[0])
+    host_out = torch.empty(B, hid, dtype=torch.float16).pin_memory()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def loop(n, host):
+        for i in range(n):
+            x_in.copy_((xs_host if host else xs)[i % 4], non_blocking=True)
+            y = layer(x_in, ck, sk, cv, sv, st)
+            if host:
+                host_out.copy_(y, non_blocking=True)
+    loop(max(args.warmup, 3), False)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    times = []
+    for host in (False, True):
+        e0, e1 = ev(), ev()
+        barrier()
+        e0.record()
+        loop(args.steps, host)
+        e1.record()
+        barrier()
+        times.append(e0.elapsed_time(e1))
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor(times, dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = t.tolist()
+    local_bytes = ck.numel() + cv.numel() + (sk.numel() + sv.numel()) * 2 + sum(
+        v.numel() for v in list(lw.values()) + list(fw.values()) if isinstance(v, torch.Tensor) and v.dtype == torch.int8)
+    dist.destroy_process_group()
+    if rank != 0:
+        return None
+    ms_step = ms_total / args.steps
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = local_bytes / (ms_step * 1e-3) / 1e9
+    return {
+        "metric": "decode_tokens_per_s", "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax, fp16 out", "data": "synthetic",
+        "config": {"workload": args.workload, "what": w["desc"], "global_batch": B, "layers": 1, "parallelism": f"tp{world}",
+                   "launch": "eager launches, NCCL collectives on the same stream",
+                   "l2": "each rank streams %.0f MB of cache and weights per step" % (local_bytes / 1e6)},
+        "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": x_in.numel() * 2,
+                "d2h_bytes_per_step": host_out.numel() * 2},
+        "gpu_launches": 17 * args.steps,
+        "roofline": {"kernel": "whole tensor-parallel layer step, per GPU (17 library launches + 3 NCCL collectives)",
+                     "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "of": "measured" if peaks else "fallback", "traffic": None, "bytes_per_gpu_per_step": local_bytes},
+        "clocks": clocks,
+    }
+
+
 def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
     """The oracle (a CPU port of the reference's algorithm: the reference has no CPU implementation of latent
     attention, and its FFN module is fake-quant fp16 GPU code) timed on the host cores on a bounded sample of
@@ -706,6 +806,21 @@ def cpu_baseline_aux(w, seconds_hint, threads):
         fn = lambda: oattn.decode_rope_recon(q, ck, sk, cv, sv, wk, wks, r2t, one, torch.tensor([L], dtype=torch.int32))
         per_call = hs / H                      # requests' worth of work per call
         sample = f"1 request, {hs} of {H} heads, context {L}" + (" (attention only, projections left out)" if w["aux"] == "block" else "")
+    elif w["aux"] == "tp":
+        # the attention of the layer (its dominant part) for one request and a few heads; the projections and the FFN,
+        # a few per cent of the CPU time at this context length, are left out
+        H, D, L, R, hs = w["heads"], w["head_dim"], w["context"] + 1, 64, 4
+        ck, sk = quant.latent_quant(torch.randn(L, hs, R, generator=gen).half())
+        cv, sv = quant.latent_quant(torch.randn(L, hs, R, generator=gen).half())
+        upk = (torch.randn(hs * R, D, generator=gen) / 8).half()
+        q = torch.randn(1, hs, D, generator=gen).half()
+        offs = [i * R for i in range(hs + 1)]
+        r2t = torch.arange(L, dtype=torch.int32)[None]
+        one = torch.tensor([0], dtype=torch.int32)
+        fn = lambda: oattn.decode_absorb(q, ck.view(L, -1), sk, cv.view(L, -1), sv, upk, upk, offs, offs, r2t, one,
+                                         torch.tensor([L], dtype=torch.int32), dtype=torch.float32)
+        per_call = hs / H
+        sample = f"attention only: 1 of {w['batch']} requests, {hs} of {H} heads, context {L}"
     elif w["aux"] == "mixffn":
         from oracle import mixffn as omix
         hid, dff, M = w["hidden"], w["d_ffn"], w["batch"]
@@ -765,7 +880,13 @@ def main():
         if line is not None:
             print(json.dumps(line))
         return
-    line = run_aux(args, rank, world, local) if WORKLOADS[args.workload].get("aux") else run_ours(args, rank, world, local)
+    aux = WORKLOADS[args.workload].get("aux")
+    if aux == "tp":
+        line = run_tp(args, rank, world, local)
+        if line is not None:
+            print(json.dumps(line))
+        return
+    line = run_aux(args, rank, world, local) if aux else run_ours(args, rank, world, local)
     if line is not None:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload, args.tokens)
