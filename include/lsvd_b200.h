@@ -314,6 +314,9 @@ typedef struct lsvd_gemv_args {
   int64_t row_absmax_stride;     /* words between two tokens                                              */
   int32_t absmax_split;          /* 0: one word per token; else channels >= absmax_split (a multiple of  */
                                  /* 16) go to the token's second word                                     */
+  int32_t prefetch_weights;      /* register-fed form: every block asks for its weight rows (L2 prefetch) before */
+                                 /* it waits for the kernel launched before it on the stream; pays when the       */
+                                 /* call follows a short kernel (measured: 126 -> 120 us for the mixffn step)      */
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
 

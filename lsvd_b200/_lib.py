@@ -113,6 +113,7 @@ class GemvArgs(C.Structure):
         ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
         ("status_word", C.c_void_p), ("form", C.c_int32),
         ("row_absmax", C.c_void_p), ("row_absmax_stride", C.c_int64), ("absmax_split", C.c_int32),
+        ("prefetch_weights", C.c_int32),
     ]
 
 

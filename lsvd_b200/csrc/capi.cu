@@ -42,6 +42,14 @@ bool chained_launch_enabled() {
   return on;
 }
 
+bool ffn_chain_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LSVD_CHAIN_FFN");
+    return chained_launch_enabled() && !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+
 int device_sm_count() {
   const DeviceInfo* d = current_device_info();
   return d ? d->sm_count : 0;

@@ -35,8 +35,12 @@ cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
 // with programmatic stream serialisation: the next kernel's blocks may become resident while the previous
 // kernel drains, and wait in grid_dependency_sync() (first statement of every such kernel) until the previous
 // grid has completed and its writes are visible.  LSVD_CHAINED_LAUNCH=0 in the environment turns it off.
-// The attention kernels use it; for the FFN kernels (chain = false) it measured slower inside a whole layer step.
+// The attention kernels use it.  On the FFN side only the mixffn quantisers and the products that ask for a weight
+// prefetch do (LSVD_CHAIN_FFN=0 turns those off): for the other quantisers and products it measured faster at 1..32
+// tokens (FFN block 52.5 / 56.8 instead of 56.9 / 59.2 us at 1 / 16 tokens) but slower at 64 tokens (143 instead of
+// 117 us) and behind the attention kernels (167 instead of 153 us for attention + FFN).
 bool chained_launch_enabled();
+bool ffn_chain_enabled();
 
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>

@@ -761,11 +761,22 @@ constexpr int kGemvWarps = 8;
 template <int NT, bool DUAL, bool SPLIT_B>
 __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) int red[];      // [warp][matrix][NT][4][32]
-  grid_dependency_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * 16;
   constexpr int NMAT = DUAL ? 2 : 1;
+  grid_dependency_release();
+  if (p.prefetch) {
+    // The weights do not depend on the kernel before this one: while that kernel drains, ask for this block's 16
+    // rows (of each matrix) line by line, so that the loads after the wait find them in L2.
+    const int lines = (p.k + 127) >> 7;
+    for (int i = threadIdx.x; i < 16 * lines; i += blockDim.x) {
+      const int r = i / lines, c = i - r * lines;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + (row0 + r) * p.w_row_stride + c * 128));
+      if (DUAL) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w2 + (row0 + r) * p.w2_row_stride + c * 128));
+    }
+  }
+  grid_dependency_wait();
 
   int acc[NMAT][NT][4];
 #pragma unroll
@@ -874,7 +885,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   const int smem = kGemvWarps * (DUAL ? 2 : 1) * NT * 4 * 32 * 4;
   auto kern = w8a8_gemv_kernel<NT, DUAL, SPLIT_B>;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
-  LSVD_CUDA_TRY(launch_chained(kern, dim3(p.n / 16), dim3(kGemvWarps * 32), smem, st, 1, false, p));
+  LSVD_CUDA_TRY(launch_chained(kern, dim3(p.n / 16), dim3(kGemvWarps * 32), smem, st, 1, p.prefetch != 0, p));
   return LSVD_OK;
 }
 
@@ -1058,6 +1069,7 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   p.m = a->m; p.n = a->n; p.k = a->k; p.epilogue = a->epilogue;
   p.row_absmax = a->row_absmax; p.row_absmax_stride = a->row_absmax_stride;
   p.absmax_split = a->absmax_split > 0 ? a->absmax_split : a->n;
+  p.prefetch = (a->prefetch_weights != 0 && ffn_chain_enabled()) ? 1 : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->form == 1) return a->m <= 16 ? launch_gemv_streamed(p, dual, split, st) : LSVD_ERR_UNSUPPORTED;
   if (a->form == 2) return launch_gemv_wide(p, dual, split, st);

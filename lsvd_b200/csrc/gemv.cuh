@@ -18,6 +18,7 @@ struct GemvParams {
   // optional per-token maximum of |fp32 value| over the output channels, kept as the bit pattern of a non-negative
   // float (ordered like an unsigned integer): slot 0 for channels below absmax_split, slot 1 from there on
   uint32_t* row_absmax; int64_t row_absmax_stride; int32_t absmax_split;
+  int32_t prefetch;          // pull the block's weight rows toward L2 before waiting for the previous kernel
 };
 
 // The TMA-fed persistent form (gemv_tma.cu), for at most 16 tokens.

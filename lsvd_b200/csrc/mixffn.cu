@@ -39,6 +39,7 @@ struct RmsParams {
 __global__ void __launch_bounds__(kThreads) mix_rmsnorm_quant_kernel(RmsParams p) {
   __shared__ double red_d[kThreads / 32];
   __shared__ float red_f[kThreads / 32];
+  grid_dependency_sync();
   const int row = blockIdx.x;
   const __half* x = p.x + row * p.x_row_stride;
   if (p.clear_words != nullptr)
@@ -76,6 +77,7 @@ struct GroupParams {
 };
 
 __global__ void __launch_bounds__(kThreads) mix_group_quant_kernel(GroupParams p) {
+  grid_dependency_sync();
   const int row = blockIdx.x;
   const bool two = p.split < p.cols;
   float m0 = __uint_as_float(p.absmax[row * p.absmax_stride]);
@@ -115,6 +117,7 @@ struct AccParams {
 
 __global__ void __launch_bounds__(kThreads) mix_acc_quant_kernel(AccParams p) {
   __shared__ float red_f[kThreads / 32];
+  grid_dependency_sync();
   const int row = blockIdx.x;
   const int32_t* acc = p.acc + row * p.acc_row_stride;
   const float rs = p.row_scale[row * p.row_scale_stride];
@@ -139,7 +142,7 @@ extern "C" int lsvd_mix_rmsnorm_quant(const lsvd_mix_rmsnorm_quant_args* a, void
   RmsParams p{static_cast<const __half*>(a->x), a->x_row_stride, static_cast<const __half*>(a->norm_weight), a->eps,
               a->q, a->q_row_stride, a->scale, a->clear_words, a->clear_per_row, a->cols};
   LSVD_CUDA_TRY(launch_chained(mix_rmsnorm_quant_kernel, dim3(a->rows), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), 1,
-                               false, p));
+                               ffn_chain_enabled(), p));
   return LSVD_OK;
 }
 
@@ -152,7 +155,7 @@ extern "C" int lsvd_mix_group_quant(const lsvd_mix_group_quant_args* a, void* st
   GroupParams p{static_cast<const __half*>(a->x), a->x_row_stride, a->absmax, a->absmax_stride, a->q, a->q_row_stride,
                 a->scale, a->scale_stride, a->cols, a->split, a->shared, vec ? 1 : 0};
   LSVD_CUDA_TRY(launch_chained(mix_group_quant_kernel, dim3(a->rows), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), 1,
-                               false, p));
+                               ffn_chain_enabled(), p));
   return LSVD_OK;
 }
 
@@ -163,6 +166,6 @@ extern "C" int lsvd_mix_acc_quant(const lsvd_mix_acc_quant_args* a, void* stream
   AccParams p{a->acc, a->acc_row_stride, a->row_scale, a->row_scale_stride, a->col_scale, a->q, a->q_row_stride, a->scale,
               a->cols};
   LSVD_CUDA_TRY(launch_chained(mix_acc_quant_kernel, dim3(a->rows), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), 1,
-                               false, p));
+                               ffn_chain_enabled(), p));
   return LSVD_OK;
 }

@@ -133,7 +133,7 @@ def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False
 
 def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a2_scale=None, out=None, out_col=0,
               want_acc=False, want_out=True, residual=None, form=0, status_word=None, fp32_swiglu=False,
-              row_absmax=None, absmax_split=0):
+              row_absmax=None, absmax_split=0, prefetch_weights=False):
     """acc = a_q @ w_q^T (int32, exact) for 1..64 tokens, dequantised to fp16; with (w2, a2) a gate/up pair whose
     result is silu(gate) * up.  Returns (out fp16 [m, n] or the passed tensor, acc int32 or None, acc2 or None).
     ``form`` 0 is the register-fed kernel, 1 the persistent TMA-fed one (at most 16 tokens); ``status_word`` (int32
@@ -168,6 +168,7 @@ def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a
     if residual is not None:
         g.residual, g.residual_row_stride = residual.data_ptr(), residual.stride(0)
     g.form, g.status_word = form, _ptr(status_word)
+    g.prefetch_weights = 1 if prefetch_weights else 0
     _lib.check(_lib.load().lsvd_w8a8_gemv(C.byref(g), _stream_ptr(a_q)))
     return out, acc, acc2
 

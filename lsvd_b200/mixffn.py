@@ -184,24 +184,24 @@ class MixedFFNGateUpDenseLatentFused(nn.Module):
         st = {}
         amax = torch.empty(m, 4, dtype=torch.int32, device=dev)          # float bits: up latent, gate latent, low-rank mid, dense mid
         x_q, x_scale = mix_rmsnorm_quant(x2, self.norm_weight, self.eps, clear_words=amax)
-        lat, _, _ = w8a8_gemv(x_q, x_scale, self.ab_a_q, self.ab_a_scale, row_absmax=amax, absmax_split=r, form=3)
+        lat, _, _ = w8a8_gemv(x_q, x_scale, self.ab_a_q, self.ab_a_scale, row_absmax=amax, absmax_split=r, form=3, prefetch_weights=True)
         lat_q, lat_s = mix_group_quant(lat, amax, split=r, shared=False)
         mid = torch.empty(m, d, dtype=torch.float16, device=dev)
         w8a8_gemv(lat_q[:, r:], lat_s[:, 1], self.gate_b_q, self.gate_b_scale, self.up_b_q, self.up_b_scale,
-                  a2_q=lat_q[:, :r], a2_scale=lat_s[:, 0], out=mid, out_col=0, fp32_swiglu=True, row_absmax=amax[:, 2:], form=3)
+                  a2_q=lat_q[:, :r], a2_scale=lat_s[:, 0], out=mid, out_col=0, fp32_swiglu=True, row_absmax=amax[:, 2:], form=3, prefetch_weights=True)
         _, gacc, uacc = w8a8_gemv(x_q, x_scale, self.gate_q, self.gate_scale, self.up_q, self.up_scale, out=mid, out_col=s,
-                                  fp32_swiglu=True, row_absmax=amax[:, 3:], want_acc=want, form=3)
+                                  fp32_swiglu=True, row_absmax=amax[:, 3:], want_acc=want, form=3, prefetch_weights=True)
         mid_q, mid_s = mix_group_quant(mid, amax[:, 2:], split=s, shared=True)
         mid_s = mid_s.view(m)
-        _, racc, _ = w8a8_gemv(mid_q, None, self.down_a_q, None, want_acc=True, want_out=False, form=3)
+        _, racc, _ = w8a8_gemv(mid_q, None, self.down_a_q, None, want_acc=True, want_out=False, form=3, prefetch_weights=True)
         r_q, r_s = mix_acc_quant(racc, mid_s, self.down_a_scale)
         if out is None:
             out = torch.empty(m, hid, dtype=torch.float16, device=dev)
         so = self.down_svd_out
         res = None if want else x2
         tgt = torch.empty_like(out) if want else out                       # stage dump: the projection before the residual
-        w8a8_gemv(r_q, r_s, self.down_b_q, self.down_b_scale, out=tgt, out_col=0, residual=res, form=3)
-        w8a8_gemv(mid_q, mid_s, self.down_q, self.down_scale, out=tgt, out_col=so, residual=None if want else x2[:, so:], form=3)
+        w8a8_gemv(r_q, r_s, self.down_b_q, self.down_b_scale, out=tgt, out_col=0, residual=res, form=3, prefetch_weights=True)
+        w8a8_gemv(mid_q, mid_s, self.down_q, self.down_scale, out=tgt, out_col=so, residual=None if want else x2[:, so:], form=3, prefetch_weights=True)
         if want:
             torch.add(tgt, x2, out=out)
             maxq = torch.full((m,), 127.0, dtype=torch.float32, device=dev)       # a tensor divisor: true division
