@@ -69,6 +69,9 @@ WORKLOADS = {
                         desc="the reference's mixffn W8A8 FFN (its own structure and fp32 conventions) at the shape of "
                              "its layer benchmark: hidden 4096, intermediate 14336, 32 tokens, svd_ratio 0.5, "
                              "rank_ratio 0.5, round_to 64"),
+    "c5_prefill_append": dict(batch=8, context=4096, heads=32, aux="append",
+                              desc="BASELINE config 5 prefill, cache append of one layer: K and V latents of 8 x 4096 "
+                                   "tokens (32 heads, ragged ranks mean 64) quantised and scattered into the int8 cache"),
     "c5_prefill_ffn": dict(batch=8, context=4096, aux="prefill_ffn",
                            desc="BASELINE config 5 prefill, FFN block of one layer: 8 x 4096 tokens through the hybrid "
                                 "SVD/RTN FFN 4096/11008 (rank 512, 50 % SVD channels) on the tcgen05 int8 GEMM"),
@@ -489,8 +492,18 @@ def run_aux(args, rank, world, local):
         host_out = torch.empty(B, 1, H * D, dtype=torch.float16).pin_memory()
         out = torch.empty(B, 1, H * D, dtype=torch.float16, device=dev)
 
-        def step():
+        def eager_step():
             out.copy_(blk(x_in, ck, sk, cv, sv, st))
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                eager_step()
+        torch.cuda.current_stream().wait_stream(side)
+        block_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(block_graph):
+            eager_step()
+        step = block_graph.replay
         feed = lambda i, host: x_in.copy_((xs_host if host else xs)[i % 8], non_blocking=True)
         units, metric, launches = B, "decode_tokens_per_s", 5
         wbytes = (3 * H * R * H * D + R * H * D + H * R * H * D) * 2 + R * H * D
@@ -500,6 +513,40 @@ def run_aux(args, rank, world, local):
         h2d, d2h = x_in.numel() * 2, out.numel() * 2
         l2 = "cache + weights (%.0f MB) fit in L2: the figure is a warm-L2 one" % (abytes / 1e6)
         what = "RMSNorm + fp16 latent GEMM + query up-projection + append + rotary attention (3 launches) + fp16 output GEMM + residual"
+    elif w["aux"] == "append":
+        from lsvd_b200 import synth
+        from lsvd_b200.attention import LatentCacheLayout, cache_append
+        T, H = w["batch"] * w["context"], w["heads"]
+        lay = LatentCacheLayout(synth.ragged_ranks(H, 64, seed=0), synth.ragged_ranks(H, 64, seed=1))
+        lats_host = None
+        lk = [torch.randn(T, lay.sum_k, device=dev, generator=g).half() for _ in range(2)]
+        lv = [torch.randn(T, lay.sum_v, device=dev, generator=g).half() for _ in range(2)]
+        dest = torch.randperm(T, device=dev, generator=g).to(torch.int32)
+        ck = torch.empty(T, lay.sum_k, dtype=torch.int8, device=dev)
+        cv = torch.empty(T, lay.sum_v, dtype=torch.int8, device=dev)
+        sk = torch.empty(T, H, dtype=torch.float16, device=dev)
+        sv = torch.empty(T, H, dtype=torch.float16, device=dev)
+        out = sk
+        host_out = torch.empty(sk.shape, dtype=torch.float16).pin_memory()
+        hk = lk[0].cpu().pin_memory()
+        hv = lv[0].cpu().pin_memory()
+        turn = [0]
+
+        def step():
+            i = turn[0] % 2
+            turn[0] += 1
+            cache_append(lay, lk[i], lv[i], dest, ck, sk, cv, sv, status_word=status)
+
+        def feed(i, host):
+            if host:                      # the latents of the step come from pinned host memory
+                lk[turn[0] % 2].copy_(hk, non_blocking=True)
+                lv[turn[0] % 2].copy_(hv, non_blocking=True)
+        units, metric, launches = T, "prefill_tokens_per_s", 1
+        abytes = T * (lay.sum_k + lay.sum_v) * 3 + T * H * 4 + T * 4
+        roof = dict(kernel="cache_append_kernel", bound="hbm", peak=float(peaks.get("hbm_gbs", 6650.0)), unit="GB/s", work=abytes)
+        h2d, d2h = (hk.numel() + hv.numel()) * 2, host_out.numel() * 2
+        l2 = "%.0f MB per step (fp16 latents in, int8 rows and fp16 scales out): larger than L2" % (abytes / 1e6)
+        what = "one launch: per (token, head) absmax, scale, int8 codes, scatter to the slot rows (K and V)"
     elif w["aux"] == "mixffn":
         from types import SimpleNamespace
         from lsvd_b200.mixffn import MixedFFNGateUpDenseLatentFused
@@ -620,7 +667,7 @@ def run_aux(args, rank, world, local):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp16 out", "data": "synthetic",
         "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": w["batch"], "layers": 1, "step": what,
-                   "launch": "CUDA graph replay of the step" if w["aux"] == "mixffn" else "eager launches on one stream", "l2": l2},
+                   "launch": "CUDA graph replay of the step" if w["aux"] in ("mixffn", "block") else "eager launches on one stream", "l2": l2},
         "e2e": {"value": units * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * args.steps,
@@ -806,6 +853,21 @@ def cpu_baseline_aux(w, seconds_hint, threads):
         fn = lambda: oattn.decode_rope_recon(q, ck, sk, cv, sv, wk, wks, r2t, one, torch.tensor([L], dtype=torch.int32))
         per_call = hs / H                      # requests' worth of work per call
         sample = f"1 request, {hs} of {H} heads, context {L}" + (" (attention only, projections left out)" if w["aux"] == "block" else "")
+    elif w["aux"] == "append":
+        H, T = w["heads"], 4096
+        kr, vr = synth.ragged_ranks(H, 64, seed=0), synth.ragged_ranks(H, 64, seed=1)
+        offs = lambda r: [sum(r[:i]) for i in range(len(r) + 1)]
+        ko, vo = offs(kr), offs(vr)
+        zk, zv = torch.randn(T, ko[-1], generator=gen).half(), torch.randn(T, vo[-1], generator=gen).half()
+        dest = torch.randperm(T, generator=gen).to(torch.int32)
+        ck, cv = torch.zeros(T, ko[-1], dtype=torch.int8), torch.zeros(T, vo[-1], dtype=torch.int8)
+        sk, sv = torch.zeros(T, H, dtype=torch.float16), torch.zeros(T, H, dtype=torch.float16)
+
+        def fn():
+            oattn.cache_append(zk, dest, ko, ck, sk)
+            oattn.cache_append(zv, dest, vo, cv, sv)
+        per_call = T
+        sample = f"{T} of {w['batch'] * w['context']} tokens"
     elif w["aux"] == "tp":
         # the attention of the layer (its dominant part) for one request and a few heads; the projections and the FFN,
         # a few per cent of the CPU time at this context length, are left out
@@ -854,10 +916,10 @@ def run_reference(args, rank, world):
         return None
     w = WORKLOADS[args.workload]
     B = args.tokens if w.get("ffn_only") else w["batch"]
-    if w.get("aux") == "prefill_ffn":
+    if w.get("aux") in ("prefill_ffn", "append"):
         B = w["batch"] * w["context"]
     cb = cpu_baseline(args.workload, args.tokens, seconds_hint=max(5.0, 3.0 * args.steps))
-    return {"impl": "reference", "metric": "prefill_tokens_per_s" if w.get("aux") == "prefill_ffn" else "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
+    return {"impl": "reference", "metric": "prefill_tokens_per_s" if w.get("aux") in ("prefill_ffn", "append") else "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * B / cb["value"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32/fp64 (CPU)", "data": "synthetic",
             "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B}, "cpu_baseline": cb,

@@ -102,3 +102,29 @@ def test_append_prefill_sized_batch_checksum():
     sk_ref = torch.empty(T, H, dtype=torch.float16)
     sk_ref[dest.long()] = s
     assert torch.equal(sk.cpu(), sk_ref)
+
+
+@pytest.mark.parametrize("rounding", ["torch", "triton"])
+def test_append_many_tokens_ragged_both_sides(rounding):
+    """Thousands of tokens with ragged ranks, K and V in one launch, strided latents (views of one wider tensor) and
+    slots scattered over a larger cache."""
+    gen = torch.Generator().manual_seed(21)
+    k_ranks, v_ranks = [16, 128, 48, 64, 32], [64, 16, 16, 112, 128]
+    lay = LatentCacheLayout(k_ranks, v_ranks)
+    T, N = 4001, 4100
+    both = torch.randn(T, lay.sum_k + lay.sum_v, generator=gen).half()
+    both[7] = 0
+    lk, lv = both[:, :lay.sum_k], both[:, lay.sum_k:]                # views with a row stride of both widths
+    dest = torch.randperm(N, generator=gen)[:T].to(torch.int32)
+    ck = torch.zeros(N, lay.sum_k, dtype=torch.int8, device="cuda")
+    cv = torch.zeros(N, lay.sum_v, dtype=torch.int8, device="cuda")
+    sk = torch.zeros(N, 5, dtype=torch.float16, device="cuda")
+    sv = torch.zeros(N, 5, dtype=torch.float16, device="cuda")
+    gb = both.cuda()
+    cache_append(lay, gb[:, :lay.sum_k], gb[:, lay.sum_k:], dest.cuda(), ck, sk, cv, sv, rounding=rounding)
+    torch.cuda.synchronize()
+    for lat, offs, cache, scale in ((lk, lay.k_off, ck, sk), (lv, lay.v_off, cv, sv)):
+        c_ref = torch.zeros(N, lat.shape[1], dtype=torch.int8)
+        s_ref = torch.zeros(N, 5, dtype=torch.float16)
+        oattn.cache_append(lat.contiguous(), dest, list(offs), c_ref, s_ref, rounding=rounding)
+        assert torch.equal(cache.cpu(), c_ref) and torch.equal(scale.cpu(), s_ref)
