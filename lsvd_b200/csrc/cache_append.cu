@@ -10,6 +10,8 @@
 // Mapping: one warp per (token, head, K|V).  A lane owns 4 consecutive latent entries (ranks are
 // multiples of 16, at most 128), loads them with one 8-byte access and stores 4 codes with one
 // 4-byte access, so a warp moves a head with one coalesced load and one coalesced store.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace lsvd {
@@ -110,6 +112,83 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant
   if (lane == 0) s.scale[static_cast<int64_t>(dest) * s.scale_row_stride + h] = s16;
 }
 
+// Prefill-sized calls: L lanes per (token, head) unit (L = 8 when no head is wider than 64, else 16), 32 / L units per
+// warp, a lane owning 8 consecutive entries (16-byte load, 8-byte store).  The one-unit-per-warp kernel above issues
+// about twice (L = 16) to four times (L = 8) as many warp instructions per byte, and at these sizes instruction
+// issue, not memory, is what bounds it.  Same arithmetic, so the same bits.
+template <int kRounding, int L>
+__global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_constant__ AppendParams p) {
+  grid_dependency_sync();
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (L - 1);
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t per_side = static_cast<int64_t>(p.num_tokens) * p.num_heads;
+  const int64_t total = per_side * ((p.side_mask == 3) ? 2 : 1);
+  const int64_t unit = warp_id * (32 / L) + lane / L;
+  const bool live = unit < total;
+  int64_t u = live ? unit : 0;
+  int side = (p.side_mask & 1) == 0 ? 1 : 0;
+  if (u >= per_side) {
+    side = 1;
+    u -= per_side;
+  }
+  const int t = static_cast<int>(u / p.num_heads);
+  const int h = static_cast<int>(u - static_cast<int64_t>(t) * p.num_heads);
+  const AppendSide& s = p.side[side];
+  const int r0 = s.rank_off[h];
+  const int rank = s.rank_off[h + 1] - r0;
+  const int i0 = sub * 8;
+  const bool active = live && i0 < rank;
+
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = 0.f;
+  if (active) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(s.latent + static_cast<int64_t>(t) * s.token_stride + s.head_off[h] + i0);
+    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      x[2 * j] = __low2float(h2[j]);
+      x[2 * j + 1] = __high2float(h2[j]);
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+#pragma unroll
+  for (int o = L / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  __half s16 = __float2half_rn(amax * 0.0078125f);
+  const __half floor16 = __float2half_rn(1e-4f);
+  if (__half2float(s16) < __half2float(floor16)) s16 = floor16;
+  const float sf = __half2float(s16);
+  if (!live) return;
+  const int dest = p.dest_loc[t];
+  if (dest < 0 || dest >= p.num_slots) {
+    if (sub == 0) report_status(p.status_word, LSVD_ERR_BOUNDS);
+    return;
+  }
+  if (active) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo |= (static_cast<uint32_t>(quantise_one<kRounding>(x[j], sf)) & 0xffu) << (8 * j);
+      hi |= (static_cast<uint32_t>(quantise_one<kRounding>(x[4 + j], sf)) & 0xffu) << (8 * j);
+    }
+    *reinterpret_cast<uint2*>(s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0 + i0) = make_uint2(lo, hi);
+  }
+  if (sub == 0) s.scale[static_cast<int64_t>(dest) * s.scale_row_stride + h] = s16;
+}
+
+// The wide kernel's accesses: 16-byte loads of the latents, 8-byte stores of the codes.
+static bool side_is_wide_ok(const lsvd_append_tensor& t, int num_heads) {
+  if (!aligned(t.latent, 16) || (t.token_stride % 8) != 0 || !aligned(t.cache, 8) || (t.cache_row_stride % 8) != 0) return false;
+  for (int h = 0; h < num_heads; ++h) {
+    const int64_t off = t.head_off ? t.head_off[h] : t.rank_off[h];
+    if ((off % 8) != 0) return false;
+  }
+  return true;
+}
+
 static int fill_side(AppendSide& dst, const lsvd_append_tensor& src, int num_heads) {
   if (src.rank_off == nullptr || src.cache == nullptr || src.cache_scale == nullptr) return LSVD_ERR_INVALID_ARG;
   if (src.rank_off[0] != 0) return LSVD_ERR_INVALID_ARG;
@@ -164,11 +243,32 @@ extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
   if (p.side_mask == 0) return LSVD_OK;
 
   const int sides = (p.side_mask == 3) ? 2 : 1;
-  const int64_t warps = static_cast<int64_t>(a->num_tokens) * a->num_heads * sides;
-  const int warps_per_block = 4;
-  const int64_t blocks = (warps + warps_per_block - 1) / warps_per_block;
-  if (blocks > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
+  const int64_t units = static_cast<int64_t>(a->num_tokens) * a->num_heads * sides;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int warps_per_block = 4;
+  bool wide = units >= 32768;
+  int max_rank = 0;
+  for (int sd = 0; sd < 2 && wide; ++sd) {
+    if (((p.side_mask >> sd) & 1) == 0) continue;
+    const lsvd_append_tensor& t = sd == 0 ? a->k : a->v;
+    wide = side_is_wide_ok(t, a->num_heads);
+    for (int h = 0; h < a->num_heads; ++h) max_rank = std::max(max_rank, t.rank_off[h + 1] - t.rank_off[h]);
+  }
+  if (wide) {
+    const int lanes = max_rank <= 64 ? 8 : 16;
+    const int64_t warps = (units + 32 / lanes - 1) / (32 / lanes);
+    const int64_t blocks = (warps + warps_per_block - 1) / warps_per_block;
+    if (blocks > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
+    void (*kern)(AppendParams);
+    if (a->rounding == LSVD_ROUND_TORCH)
+      kern = lanes == 8 ? cache_append_wide_kernel<LSVD_ROUND_TORCH, 8> : cache_append_wide_kernel<LSVD_ROUND_TORCH, 16>;
+    else
+      kern = lanes == 8 ? cache_append_wide_kernel<LSVD_ROUND_TRITON, 8> : cache_append_wide_kernel<LSVD_ROUND_TRITON, 16>;
+    LSVD_CUDA_TRY(launch_chained(kern, dim3(static_cast<unsigned>(blocks)), dim3(warps_per_block * 32), 0, st, 1, true, p));
+    return LSVD_OK;
+  }
+  const int64_t blocks = (units + warps_per_block - 1) / warps_per_block;
+  if (blocks > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
   const dim3 grid(static_cast<unsigned>(blocks)), block(warps_per_block * 32);
   if (a->rounding == LSVD_ROUND_TORCH)
     LSVD_CUDA_TRY(launch_chained(cache_append_kernel<LSVD_ROUND_TORCH>, grid, block, 0, st, 1, true, p));
