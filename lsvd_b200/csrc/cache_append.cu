@@ -38,10 +38,18 @@ struct AppendParams {
 template <int kRounding>
 __device__ __forceinline__ int quantise_one(float x, float s) {
   if (kRounding == LSVD_ROUND_TORCH) {
-    // fp16 division = exact quotient rounded once to fp16; then round half to even.
-    float y = __half2float(__float2half_rn(__fdiv_rn(x, s)));
-    y = rintf(y);
-    return static_cast<int>(fminf(fmaxf(y, -128.f), 127.f));
+    // fp16 division = exact quotient rounded once to fp16; then round half to even.  Both roundings are done with
+    // additions instead of conversions (the conversion unit is what bounds this kernel at prefill sizes):
+    //   * to 11 significant bits: add and subtract 1.5 * 2^(e + 13), e the exponent of y -- the sum lies in the binade
+    //     whose spacing is 2^(e - 10), the spacing of fp16 numbers around y, and fp32 addition rounds ties to even.
+    //     (Below 2^-14, where fp16 is coarser than that, the code is 0 either way.)  Quotients beyond +-256 end at a
+    //     clamp bound whatever their rounding, so they are clamped first, which also keeps e + 13 in range;
+    //   * to an integer: add 1.5 * 2^23 and read the low mantissa bits.
+    float y = fminf(fmaxf(__fdiv_rn(x, s), -256.f), 256.f);
+    const float c = __uint_as_float(((__float_as_uint(y) & 0x7f800000u) + (13u << 23)) | 0x00400000u);
+    y = __fsub_rn(__fadd_rn(y, c), c);
+    const int q = __float_as_int(__fadd_rn(y, 12582912.f)) - 0x4b400000;
+    return min(max(q, -128), 127);
   } else {
     float y = __fdiv_rn(x, s);
     int r = static_cast<int>(y >= 0.f ? y + 0.5f : y - 0.5f);   // conversion truncates toward zero
