@@ -35,8 +35,9 @@ struct AppendParams {
   int32_t side_mask;                   // bit 0: K present, bit 1: V present
 };
 
+// `r` = the correctly rounded reciprocal of the scale (__frcp_rn), used by the fp16-division form only.
 template <int kRounding>
-__device__ __forceinline__ int quantise_one(float x, float s) {
+__device__ __forceinline__ int quantise_one(float x, float s, float r) {
   if (kRounding == LSVD_ROUND_TORCH) {
     // fp16 division = exact quotient rounded once to fp16; then round half to even.  Both roundings are done with
     // additions instead of conversions (the conversion unit is what bounds this kernel at prefill sizes):
@@ -45,7 +46,14 @@ __device__ __forceinline__ int quantise_one(float x, float s) {
     //     (Below 2^-14, where fp16 is coarser than that, the code is 0 either way.)  Quotients beyond +-256 end at a
     //     clamp bound whatever their rounding, so they are clamped first, which also keeps e + 13 in range;
     //   * to an integer: add 1.5 * 2^23 and read the low mantissa bits.
-    float y = fminf(fmaxf(__fdiv_rn(x, s), -256.f), 256.f);
+    // The quotient: x and s are fp16 numbers, so x / s is a ratio of two 11-bit integers and stays at least two fp32
+    // spacings away from every fp16 rounding boundary it does not hit exactly.  A quotient within one spacing of the
+    // exact one therefore rounds to the same fp16 number as the IEEE quotient: q0 = x r, one residual, one correction
+    // (three FMA-pipe operations instead of a division per entry); a boundary that is hit exactly is representable
+    // and comes out exact.
+    const float q0 = __fmul_rn(x, r);
+    float y = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
+    y = fminf(fmaxf(y, -256.f), 256.f);
     const float c = __uint_as_float(((__float_as_uint(y) & 0x7f800000u) + (13u << 23)) | 0x00400000u);
     y = __fsub_rn(__fadd_rn(y, c), c);
     const int q = __float_as_int(__fadd_rn(y, 12582912.f)) - 0x4b400000;
@@ -101,6 +109,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant
   const __half floor16 = __float2half_rn(1e-4f);
   if (__half2float(s16) < __half2float(floor16)) s16 = floor16;
   const float sf = __half2float(s16);
+  const float rsf = __frcp_rn(sf);
 
   const int dest = p.dest_loc[t];
   if (dest < 0 || dest >= p.num_slots) {
@@ -111,7 +120,7 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant
     uint32_t packed = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int q = quantise_one<kRounding>(x[j], sf);
+      const int q = quantise_one<kRounding>(x[j], sf, rsf);
       packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * j);
     }
     int8_t* dst = s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0 + i0;
@@ -169,6 +178,7 @@ __global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_con
   const __half floor16 = __float2half_rn(1e-4f);
   if (__half2float(s16) < __half2float(floor16)) s16 = floor16;
   const float sf = __half2float(s16);
+  const float rsf = __frcp_rn(sf);
   if (!live) return;
   const int dest = p.dest_loc[t];
   if (dest < 0 || dest >= p.num_slots) {
@@ -179,8 +189,8 @@ __global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_con
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      lo |= (static_cast<uint32_t>(quantise_one<kRounding>(x[j], sf)) & 0xffu) << (8 * j);
-      hi |= (static_cast<uint32_t>(quantise_one<kRounding>(x[4 + j], sf)) & 0xffu) << (8 * j);
+      lo |= (static_cast<uint32_t>(quantise_one<kRounding>(x[j], sf, rsf)) & 0xffu) << (8 * j);
+      hi |= (static_cast<uint32_t>(quantise_one<kRounding>(x[4 + j], sf, rsf)) & 0xffu) << (8 * j);
     }
     *reinterpret_cast<uint2*>(s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0 + i0) = make_uint2(lo, hi);
   }
