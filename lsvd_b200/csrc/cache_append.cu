@@ -129,31 +129,37 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant
   if (lane == 0) s.scale[static_cast<int64_t>(dest) * s.scale_row_stride + h] = s16;
 }
 
-// Prefill-sized calls: L lanes per (token, head) unit (L = 8 when no head is wider than 64, else 16), 32 / L units per
-// warp, a lane owning 8 consecutive entries (16-byte load, 8-byte store).  The one-unit-per-warp kernel above issues
-// about twice (L = 16) to four times (L = 8) as many warp instructions per byte, and at these sizes instruction
-// issue, not memory, is what bounds it.  Same arithmetic, so the same bits.
-template <int kRounding, int L>
-__global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_constant__ AppendParams p) {
+// Prefill-sized calls.  Units are ordered head by head (all tokens of head 0 of K, then head 1, ...), so a warp works
+// on ONE head and its lanes can be dealt by that head's rank: L = 2, 4, 8 or 16 lanes per (token, head) unit for ranks
+// up to 16, 32, 64, 128, a lane owning 8 consecutive entries (16-byte load, 8-byte store), 32 / L tokens per warp.
+// The one-unit-per-warp kernel above issues two to sixteen times as many warp instructions per byte, and at these
+// sizes instruction issue, not memory, is what bounds it.  Same arithmetic, so the same bits.
+struct WideTable {
+  int32_t warp_begin[2 * LSVD_MAX_HEADS + 1];   // first warp of every (side, head) segment, in launch order
+  int32_t seg_side_head[2 * LSVD_MAX_HEADS];    // side * LSVD_MAX_HEADS + head
+  int32_t nseg;
+};
+
+template <int kRounding>
+__global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_constant__ AppendParams p,
+                                                                const __grid_constant__ WideTable w) {
   grid_dependency_sync();
   const int lane = threadIdx.x & 31;
-  const int sub = lane & (L - 1);
-  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int64_t per_side = static_cast<int64_t>(p.num_tokens) * p.num_heads;
-  const int64_t total = per_side * ((p.side_mask == 3) ? 2 : 1);
-  const int64_t unit = warp_id * (32 / L) + lane / L;
-  const bool live = unit < total;
-  int64_t u = live ? unit : 0;
-  int side = (p.side_mask & 1) == 0 ? 1 : 0;
-  if (u >= per_side) {
-    side = 1;
-    u -= per_side;
+  const int warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= w.warp_begin[w.nseg]) return;
+  int lo_seg = 0, hi_seg = w.nseg;                   // last segment whose first warp is <= warp_id
+  while (hi_seg - lo_seg > 1) {
+    const int mid = (lo_seg + hi_seg) >> 1;
+    if (w.warp_begin[mid] <= warp_id) lo_seg = mid; else hi_seg = mid;
   }
-  const int t = static_cast<int>(u / p.num_heads);
-  const int h = static_cast<int>(u - static_cast<int64_t>(t) * p.num_heads);
+  const int side = w.seg_side_head[lo_seg] / LSVD_MAX_HEADS, h = w.seg_side_head[lo_seg] % LSVD_MAX_HEADS;
   const AppendSide& s = p.side[side];
   const int r0 = s.rank_off[h];
   const int rank = s.rank_off[h + 1] - r0;
+  const int lg = rank <= 16 ? 1 : (rank <= 32 ? 2 : (rank <= 64 ? 3 : 4));     // log2 of the lanes per unit
+  const int sub = lane & ((1 << lg) - 1);
+  const int t = (warp_id - w.warp_begin[lo_seg]) * (32 >> lg) + (lane >> lg);
+  const bool live = t < p.num_tokens;
   const int i0 = sub * 8;
   const bool active = live && i0 < rank;
 
@@ -173,7 +179,8 @@ __global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_con
 #pragma unroll
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
 #pragma unroll
-  for (int o = L / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int o = 8; o > 0; o >>= 1)
+    if (o < (1 << lg)) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));     // lg is uniform in the warp
   __half s16 = __float2half_rn(amax * 0.0078125f);
   const __half floor16 = __float2half_rn(1e-4f);
   if (__half2float(s16) < __half2float(floor16)) s16 = floor16;
@@ -265,24 +272,32 @@ extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int warps_per_block = 4;
   bool wide = units >= 32768;
-  int max_rank = 0;
   for (int sd = 0; sd < 2 && wide; ++sd) {
     if (((p.side_mask >> sd) & 1) == 0) continue;
-    const lsvd_append_tensor& t = sd == 0 ? a->k : a->v;
-    wide = side_is_wide_ok(t, a->num_heads);
-    for (int h = 0; h < a->num_heads; ++h) max_rank = std::max(max_rank, t.rank_off[h + 1] - t.rank_off[h]);
+    wide = side_is_wide_ok(sd == 0 ? a->k : a->v, a->num_heads);
   }
   if (wide) {
-    const int lanes = max_rank <= 64 ? 8 : 16;
-    const int64_t warps = (units + 32 / lanes - 1) / (32 / lanes);
+    WideTable wt{};
+    int64_t warps = 0;
+    for (int sd = 0; sd < 2; ++sd) {
+      if (((p.side_mask >> sd) & 1) == 0) continue;
+      const lsvd_append_tensor& t = sd == 0 ? a->k : a->v;
+      for (int h = 0; h < a->num_heads; ++h) {
+        const int rank = t.rank_off[h + 1] - t.rank_off[h];
+        const int lanes = rank <= 16 ? 2 : (rank <= 32 ? 4 : (rank <= 64 ? 8 : 16));
+        const int per_warp = 32 / lanes;
+        wt.warp_begin[wt.nseg] = static_cast<int32_t>(warps);
+        wt.seg_side_head[wt.nseg] = sd * LSVD_MAX_HEADS + h;
+        ++wt.nseg;
+        warps += (a->num_tokens + per_warp - 1) / per_warp;
+      }
+    }
+    if (warps > 0x7fffffffLL - 8) return LSVD_ERR_UNSUPPORTED;
+    wt.warp_begin[wt.nseg] = static_cast<int32_t>(warps);
     const int64_t blocks = (warps + warps_per_block - 1) / warps_per_block;
-    if (blocks > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
-    void (*kern)(AppendParams);
-    if (a->rounding == LSVD_ROUND_TORCH)
-      kern = lanes == 8 ? cache_append_wide_kernel<LSVD_ROUND_TORCH, 8> : cache_append_wide_kernel<LSVD_ROUND_TORCH, 16>;
-    else
-      kern = lanes == 8 ? cache_append_wide_kernel<LSVD_ROUND_TRITON, 8> : cache_append_wide_kernel<LSVD_ROUND_TRITON, 16>;
-    LSVD_CUDA_TRY(launch_chained(kern, dim3(static_cast<unsigned>(blocks)), dim3(warps_per_block * 32), 0, st, 1, true, p));
+    auto kern = a->rounding == LSVD_ROUND_TORCH ? cache_append_wide_kernel<LSVD_ROUND_TORCH>
+                                                : cache_append_wide_kernel<LSVD_ROUND_TRITON>;
+    LSVD_CUDA_TRY(launch_chained(kern, dim3(static_cast<unsigned>(blocks)), dim3(warps_per_block * 32), 0, st, 1, true, p, wt));
     return LSVD_OK;
   }
   const int64_t blocks = (units + warps_per_block - 1) / warps_per_block;
