@@ -128,3 +128,28 @@ def test_append_many_tokens_ragged_both_sides(rounding):
         s_ref = torch.zeros(N, 5, dtype=torch.float16)
         oattn.cache_append(lat.contiguous(), dest, list(offs), c_ref, s_ref, rounding=rounding)
         assert torch.equal(cache.cpu(), c_ref) and torch.equal(scale.cpu(), s_ref)
+
+
+def test_append_many_tokens_out_of_range_slots_are_skipped_and_reported():
+    """The same guard in the form used for thousands of tokens: bad slots are skipped, every other row is written."""
+    lay = LatentCacheLayout([16, 64, 128], [32, 48, 16])
+    T, N = 6000, 6000
+    gen = torch.Generator().manual_seed(33)
+    lk = torch.randn(T, lay.sum_k, generator=gen).half()
+    lv = torch.randn(T, lay.sum_v, generator=gen).half()
+    dest = torch.arange(T, dtype=torch.int32)
+    dest[17], dest[4242] = N + 5, -1
+    ck = torch.zeros(N, lay.sum_k, dtype=torch.int8, device="cuda")
+    cv = torch.zeros(N, lay.sum_v, dtype=torch.int8, device="cuda")
+    sk = torch.zeros(N, 3, dtype=torch.float16, device="cuda")
+    sv = torch.zeros(N, 3, dtype=torch.float16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cache_append(lay, lk.cuda(), lv.cuda(), dest.cuda(), ck, sk, cv, sv, status_word=status)
+    torch.cuda.synchronize()
+    assert status.item() == 6
+    good = torch.ones(T, dtype=torch.bool)
+    good[17] = good[4242] = False
+    for lat, offs, cache, scale in ((lk, lay.k_off, ck, sk), (lv, lay.v_off, cv, sv)):
+        q, s = quant.latent_quant_ragged(lat, list(offs))
+        assert torch.equal(cache.cpu()[good], q[good]) and torch.equal(scale.cpu()[good], s[good])
+        assert (cache.cpu()[~good] == 0).all() and (scale.cpu()[~good] == 0).all()
