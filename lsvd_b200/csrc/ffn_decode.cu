@@ -758,8 +758,10 @@ constexpr int kGemvWarps = 8;
 
 // NT = token tiles of 8 (tokens beyond m read as zero); DUAL = a gate/up pair of matrices in one pass;
 // SPLIT_B = the second matrix has its own activations.
-template <int NT, bool DUAL, bool SPLIT_B>
-__global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid_constant__ GemvParams p) {
+// MIX = the all-fp32 epilogue conventions and the per-token maxima (their own instantiations: the other products keep
+// their register budget, which for 17..32 tokens is capped so that three blocks share an SM -- 78 -> 68 us per FFN call).
+template <int NT, bool DUAL, bool SPLIT_B, bool MIX>
+__global__ void __launch_bounds__(kGemvWarps * 32, (NT == 4 && !MIX) ? 3 : 0) w8a8_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) int red[];      // [warp][matrix][NT][4][32]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -863,8 +865,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
       if (DUAL) sum1 += red[wi * (NMAT * NT * 4 * 32) + NT * 4 * 32 + e];
     }
     float av = 0.f;
-    if (tok < p.m) av = gemv_store<DUAL, SPLIT_B>(p, tok, row, sum0, sum1);
-    if (p.row_absmax != nullptr) {
+    if (tok < p.m) av = gemv_store<DUAL, SPLIT_B, MIX>(p, tok, row, sum0, sum1);
+    if (MIX && p.row_absmax != nullptr) {
       // the eight lanes that share (el & 3) hold one token's values of eight channels (e >> 5 is uniform in a warp)
       av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 4));
       av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 8));
@@ -880,20 +882,26 @@ __global__ void __launch_bounds__(kGemvWarps * 32) w8a8_gemv_kernel(const __grid
 // ----------------------------------------------------------------------------------------------
 static bool is_pow2(int n) { return n > 0 && (n & (n - 1)) == 0; }
 
-template <int NT, bool DUAL, bool SPLIT_B>
+template <int NT, bool DUAL, bool SPLIT_B, bool MIX>
 static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   const int smem = kGemvWarps * (DUAL ? 2 : 1) * NT * 4 * 32 * 4;
-  auto kern = w8a8_gemv_kernel<NT, DUAL, SPLIT_B>;
+  auto kern = w8a8_gemv_kernel<NT, DUAL, SPLIT_B, MIX>;
   if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
   LSVD_CUDA_TRY(launch_chained(kern, dim3(p.n / 16), dim3(kGemvWarps * 32), smem, st, 1, p.prefetch != 0, p));
   return LSVD_OK;
 }
 
+template <int NT, bool MIX>
+static int launch_gemv_form(const GemvParams& p, bool dual, bool split, cudaStream_t st) {
+  if (!dual) return launch_gemv<NT, false, false, MIX>(p, st);
+  if (split) return launch_gemv<NT, true, true, MIX>(p, st);
+  return launch_gemv<NT, true, false, MIX>(p, st);
+}
+
 template <int NT>
 static int launch_gemv_nt(const GemvParams& p, bool dual, bool split, cudaStream_t st) {
-  if (!dual) return launch_gemv<NT, false, false>(p, st);
-  if (split) return launch_gemv<NT, true, true>(p, st);
-  return launch_gemv<NT, true, false>(p, st);
+  const bool mix = p.epilogue == 2 || p.row_absmax != nullptr;
+  return mix ? launch_gemv_form<NT, true>(p, dual, split, st) : launch_gemv_form<NT, false>(p, dual, split, st);
 }
 
 }  // namespace lsvd

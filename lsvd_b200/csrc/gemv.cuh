@@ -40,7 +40,8 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g));
 
 // Dequantise, gate, add the residual and store one element; sum1 / the second scales are used by gate/up pairs.
 // Returns |fp32 value| before it is rounded to fp16 (the quantity the all-fp32 pipeline takes its next scale from).
-template <bool DUAL, bool SPLIT_B>
+// MIX: the all-fp32 conventions (epilogue 2 for a pair; the returned maximum is used).
+template <bool DUAL, bool SPLIT_B, bool MIX = false>
 __device__ __forceinline__ float gemv_store(const GemvParams& p, int tok, int row, int sum0, int sum1) {
   if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = sum0;
   if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = sum1;
@@ -52,7 +53,7 @@ __device__ __forceinline__ float gemv_store(const GemvParams& p, int tok, int ro
   if (DUAL) {
     const float sb = SPLIT_B ? p.a2_scale[tok * p.a2_scale_stride] : sa;
     const float f1 = (static_cast<float>(sum1) * sb) * p.w2_scale[row];
-    if (p.epilogue == 2) {
+    if (MIX) {
       // all in fp32, one rounding: up * (gate * sigmoid(gate))
       f = f1 * (f0 * (1.0f / (1.0f + expf(-f0))));
       res = __float2half_rn(f);
