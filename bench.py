@@ -142,14 +142,11 @@ def make_workload(w, device, seed):
     B, H, D, L = w["batch"], w["heads"], w["head_dim"], w["context"]
     kr = synth.ragged_ranks(H, 64, seed=0) if w["ragged"] else [64] * H
     vr = synth.ragged_ranks(H, 64, seed=1) if w["ragged"] else [64] * H
-    lay = LatentCacheLayout(kr, vr)
+    lay = LatentCacheLayout(kr, vr, head_major=w.get("cache_layout", "head") == "head")
     seq = L + 1                      # context plus the slot of the decoding token, as the reference's benchmark
     n_slots = B * seq
     g = torch.Generator(device=device).manual_seed(seed)
-    ck = torch.empty(n_slots, lay.sum_k, dtype=torch.int8, device=device)
-    cv = torch.empty(n_slots, lay.sum_v, dtype=torch.int8, device=device)
-    sk = torch.empty(n_slots, H, dtype=torch.float16, device=device)
-    sv = torch.empty(n_slots, H, dtype=torch.float16, device=device)
+    ck, sk, cv, sv = lay.alloc(n_slots, device)
     chunk = 8192
     for s0 in range(0, n_slots, chunk):
         n = min(chunk, n_slots - s0)
@@ -203,6 +200,7 @@ def run_ours(args, rank, world, local):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     w = dict(WORKLOADS[args.workload])
+    w["cache_layout"] = args.cache_layout
     has_attn = not w.get("ffn_only", False)
     has_ffn = w.get("ffn", False)
     if w.get("ffn_only"):
@@ -935,6 +933,9 @@ def main():
     ap.add_argument("--workload", default="c3_layer", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step of the c2_ffn workload (1..64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cache-layout", default="head", choices=["head", "slot"],
+                    help="latent cache stored head by head ([H][slots][r_h], the layout the streaming kernel prefers) or "
+                         "slot by slot ([slots][sum r], the reference's)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":

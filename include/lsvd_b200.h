@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define LSVD_ABI_VERSION 1
+#define LSVD_ABI_VERSION 2
 #define LSVD_MAX_HEADS 128      /* heads per call (per GPU shard)                     */
 #define LSVD_MAX_RANK 128       /* latent entries per head; ranks are multiples of 16 */
 
@@ -49,6 +49,16 @@ int lsvd_last_cuda_error(void);
  *   LSVD_ROUND_TRITON : x/scale in fp32, round half away from zero -- the reference's Triton append kernel
  *                       (kernels/layer_bench/fd_kernel/destindex_copy_quantize_latent.py:26-29).        */
 enum { LSVD_ROUND_TORCH = 0, LSVD_ROUND_TRITON = 1 };
+
+/* Layout of the int8 latent cache (K and V alike) and of its fp16 scales.
+ *   LSVD_CACHE_SLOT_MAJOR : cache [N_slots][sum r] (head h in bytes rank_off[h] .. rank_off[h+1]-1 of a row), scales
+ *                           [N_slots][H] -- with a uniform rank the reference's [N_slots, H, R] / [N_slots, H] tensors
+ *                           (kernels/layer_bench/benchmark_triton_int8_layer.py:116-149).
+ *   LSVD_CACHE_HEAD_MAJOR : cache [H][N_slots][r_h] (head h starts at byte rank_off[h] * N_slots, slot s of it at
+ *                           + s * r_h), scales [H][N_slots].  The rows a head reads for consecutive slots are then
+ *                           contiguous, which is what the streaming kernel's loads want; same values either way.
+ *                           Row strides of the argument blocks are ignored in this layout.                          */
+enum { LSVD_CACHE_SLOT_MAJOR = 0, LSVD_CACHE_HEAD_MAJOR = 1 };
 
 /* ---------------------------------------------------------------------------------------------
  * Latent KV-cache append / quantise.
@@ -78,6 +88,7 @@ typedef struct lsvd_append_args {
   lsvd_append_tensor k;          /* k.latent == NULL skips K                                                       */
   lsvd_append_tensor v;          /* v.latent == NULL skips V                                                       */
   int32_t* status_word;          /* device int32 or NULL; receives LSVD_ERR_BOUNDS (never cleared by the library)  */
+  int32_t cache_layout;          /* LSVD_CACHE_*                                                                   */
 } lsvd_append_args;
 
 int lsvd_cache_append(const lsvd_append_args* args, void* stream);
@@ -130,6 +141,7 @@ typedef struct lsvd_attn_decode_args {
   int32_t* status_word;          /* device int32 or NULL                                                           */
   void* ev_stream_begin;         /* optional cudaEvent_t pair recorded around the streaming kernel alone (the      */
   void* ev_stream_end;           /* launch that reads the cache), for roofline measurements; NULL = not recorded   */
+  int32_t cache_layout;          /* LSVD_CACHE_*                                                                   */
 } lsvd_attn_decode_args;
 
 /* Bytes of workspace lsvd_attn_decode needs for this problem on the current device. */
@@ -351,12 +363,27 @@ typedef struct lsvd_ffn_decode_args {
   int64_t residual_row_stride;
   void* out;                     /* device fp16 [m, d_out]                                                        */
   int64_t out_row_stride;
-  void* workspace;               /* device, 256-byte aligned, lsvd_ffn_decode_workspace_bytes(m, d_in, d_ffn, rank) */
+  void* workspace;               /* device, 256-byte aligned, lsvd_ffn_decode_workspace_bytes(m, d_in, d_ffn, rank, d_out) */
   size_t workspace_bytes;
   int32_t* status_word;          /* device int32 or NULL                                                          */
+  int32_t fused;                 /* non-zero: run the block as ONE persistent kernel (at most 16 tokens, rank a       */
+                                 /* multiple of 128 and <= 1024, d_in <= 4096, Hadamard factor of 64-entry blocks):   */
+                                 /* weights stream through a TMA ring into tcgen05.mma (weights as the 128-row        */
+                                 /* operand, tokens as 16 columns), stages meet at grid barriers with bounded waits.   */
+                                 /* Shapes outside its forms take the chain of launches.  The workspace must then     */
+                                 /* have been set to zero once, before its first use (it holds the barrier counters,   */
+                                 /* which the kernel maintains from call to call); calls that share a workspace must   */
+                                 /* be ordered on a stream.  `overlap` is ignored.  Same values as the chain; slower   */
+                                 /* than the chain on B200 at the 7B shape as measured, hence opt-in.  */
 } lsvd_ffn_decode_args;
-size_t lsvd_ffn_decode_workspace_bytes(int32_t m, int32_t d_in, int32_t d_ffn, int32_t rank);
+size_t lsvd_ffn_decode_workspace_bytes(int32_t m, int32_t d_in, int32_t d_ffn, int32_t rank, int32_t d_out);
 int lsvd_ffn_decode(const lsvd_ffn_decode_args* args, void* stream);
+/* 1 when lsvd_ffn_decode would run these arguments as the single persistent kernel, 0 when it would take the chain. */
+int lsvd_ffn_decode_is_fused(const lsvd_ffn_decode_args* args);
+/* Performance analysis of the persistent kernels: with a device buffer of [SM count][16] 64-bit words set here, every
+ * block writes the GPU's global timer (ns) at each stage boundary of every later launch (last launch wins); NULL turns
+ * it off.  Process-wide, not thread-safe: a tool for benchmarks, not for serving. */
+void lsvd_fused_set_profile(void* device_buffer);
 
 /* ---------------------------------------------------------------------------------------------
  * W8A8 GEMM for prefill / large batches on tcgen05 (kind::i8, accumulators in tensor memory, TMA-fed).

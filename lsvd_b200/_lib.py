@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(HERE, "liblsvd_b200.so")
 LSVD_MAX_HEADS = 128
 LSVD_MAX_RANK = 128
 ROUND_TORCH, ROUND_TRITON = 0, 1
+CACHE_SLOT_MAJOR, CACHE_HEAD_MAJOR = 0, 1
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_BOUNDS = range(7)
 
 
@@ -36,6 +37,7 @@ class AppendArgs(C.Structure):
     _fields_ = [
         ("num_tokens", C.c_int32), ("num_heads", C.c_int32), ("rounding", C.c_int32), ("num_slots", C.c_int32),
         ("dest_loc", C.c_void_p), ("k", AppendTensor), ("v", AppendTensor), ("status_word", C.c_void_p),
+        ("cache_layout", C.c_int32),
     ]
 
 
@@ -57,6 +59,7 @@ class AttnDecodeArgs(C.Structure):
         ("out_latent", C.c_void_p), ("out_latent_stride_b", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status_word", C.c_void_p), ("ev_stream_begin", C.c_void_p), ("ev_stream_end", C.c_void_p),
+        ("cache_layout", C.c_int32),
     ]
 
 
@@ -152,7 +155,7 @@ class FfnDecodeArgs(C.Structure):
         ("Wu_q", C.c_void_p), ("Wu_s", C.c_void_p), ("Wd_q", C.c_void_p), ("Wd_s", C.c_void_p),
         ("had_K_packed", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
         ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("status_word", C.c_void_p),
+        ("status_word", C.c_void_p), ("fused", C.c_int32),
     ]
 
 
@@ -181,7 +184,9 @@ SIGNATURES = {
     "lsvd_attn_decode_static_scratch_bytes": (C.c_size_t, []),
     "lsvd_attn_decode_static": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_heads_hadamard_quant": (C.c_int, [C.POINTER(HeadsHadamardQuantArgs), C.c_void_p]),
-    "lsvd_ffn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 4),
+    "lsvd_ffn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "lsvd_ffn_decode_is_fused": (C.c_int, [C.POINTER(FfnDecodeArgs)]),
+    "lsvd_fused_set_profile": (None, [C.c_void_p]),
     "lsvd_ffn_decode": (C.c_int, [C.POINTER(FfnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_rope_workspace_bytes": (C.c_size_t, [C.c_int32] * 6),
     "lsvd_attn_decode_rope": (C.c_int, [C.POINTER(AttnRopeArgs), C.c_void_p]),

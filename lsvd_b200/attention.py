@@ -44,7 +44,12 @@ class LatentCacheLayout:
     R gives exactly the reference's ``[N_slots, H, R]`` tensor.
     """
 
-    def __init__(self, k_ranks: Sequence[int], v_ranks: Optional[Sequence[int]] = None):
+    def __init__(self, k_ranks: Sequence[int], v_ranks: Optional[Sequence[int]] = None, head_major: bool = False):
+        """``head_major``: the cache is stored head by head -- ``cache [H][N_slots][r_h]`` as one flat int8 buffer of
+        ``N_slots * sum(r)`` bytes and scales ``[H, N_slots]`` -- instead of one row per slot (``[N_slots, sum r]``,
+        scales ``[N_slots, H]``, the reference's layout).  Same values; the rows a head reads for consecutive slots are
+        then contiguous in memory, which the streaming kernel's loads prefer."""
+        self.head_major = bool(head_major)
         v_ranks = list(k_ranks if v_ranks is None else v_ranks)
         k_ranks = list(k_ranks)
         if len(k_ranks) != len(v_ranks) or not k_ranks:
@@ -69,6 +74,38 @@ class LatentCacheLayout:
     def uniform(cls, num_heads: int, rank_k: int, rank_v: Optional[int] = None):
         return cls([rank_k] * num_heads, [rank_v if rank_v is not None else rank_k] * num_heads)
 
+    def as_head_major(self):
+        return LatentCacheLayout(self.k_ranks, self.v_ranks, head_major=True)
+
+    def alloc(self, num_slots: int, device="cuda"):
+        """Empty (cache_k, scale_k, cache_v, scale_v) for ``num_slots`` slots in this layout."""
+        if self.head_major:
+            return (torch.empty(num_slots * self.sum_k, dtype=torch.int8, device=device),
+                    torch.empty(self.num_heads, num_slots, dtype=torch.float16, device=device),
+                    torch.empty(num_slots * self.sum_v, dtype=torch.int8, device=device),
+                    torch.empty(self.num_heads, num_slots, dtype=torch.float16, device=device))
+        return (torch.empty(num_slots, self.sum_k, dtype=torch.int8, device=device),
+                torch.empty(num_slots, self.num_heads, dtype=torch.float16, device=device),
+                torch.empty(num_slots, self.sum_v, dtype=torch.int8, device=device),
+                torch.empty(num_slots, self.num_heads, dtype=torch.float16, device=device))
+
+    def num_slots_of(self, cache: torch.Tensor, which: str = "k") -> int:
+        total = self.sum_k if which == "k" else self.sum_v
+        return cache.numel() // total if self.head_major else cache.shape[0]
+
+    def to_head_major(self, cache: torch.Tensor, scale: torch.Tensor, which: str = "k"):
+        """Slot-major ``cache [N, sum r]`` / ``scale [N, H]`` -> the head-major buffers (a copy)."""
+        off = self.k_off if which == "k" else self.v_off
+        flat = torch.cat([cache[:, off[h]:off[h + 1]].contiguous().flatten() for h in range(self.num_heads)])
+        return flat, scale.t().contiguous()
+
+    def from_head_major(self, flat: torch.Tensor, scale_hn: torch.Tensor, which: str = "k"):
+        """The inverse of ``to_head_major``."""
+        off = self.k_off if which == "k" else self.v_off
+        n = scale_hn.shape[1]
+        cols = [flat[off[h] * n:off[h + 1] * n].view(n, off[h + 1] - off[h]) for h in range(self.num_heads)]
+        return torch.cat(cols, dim=1).contiguous(), scale_hn.t().contiguous()
+
     def off_c(self, which: str):
         return self._k_off_c if which == "k" else self._v_off_c
 
@@ -80,8 +117,9 @@ def _rounding_code(rounding: str) -> int:
         raise ValueError(f"rounding must be 'torch' or 'triton', got {rounding!r}")
 
 
-def _append_side(latent, off_c, offs, cache, scale, keep):
-    """Fill one AppendTensor from 2-D views: latent [T, sum r] (unit inner stride), cache [N, >= sum r] int8."""
+def _append_side(latent, off_c, offs, cache, scale, keep, head_major=False):
+    """Fill one AppendTensor from 2-D views: latent [T, sum r] (unit inner stride), cache [N, >= sum r] int8 (or the flat
+    head-major buffer)."""
     side = _lib.AppendTensor()
     if latent is None:
         return side
@@ -89,14 +127,16 @@ def _append_side(latent, off_c, offs, cache, scale, keep):
         raise ValueError("latent and cache_scale must be fp16 and cache int8")
     if latent.stride(-1) != 1 or cache.stride(-1) != 1 or scale.stride(-1) != 1:
         raise ValueError("innermost strides must be 1")
+    if head_major and (not cache.is_contiguous() or not scale.is_contiguous()):
+        raise ValueError("head-major caches and scales must be contiguous")
     side.latent = latent.data_ptr()
     side.token_stride = latent.stride(0)
     side.head_off = None
     side.rank_off = off_c
     side.cache = cache.data_ptr()
-    side.cache_row_stride = cache.stride(0)
+    side.cache_row_stride = 0 if head_major else cache.stride(0)
     side.cache_scale = scale.data_ptr()
-    side.scale_row_stride = scale.stride(0)
+    side.scale_row_stride = 0 if head_major else scale.stride(0)
     keep.extend((latent, cache, scale))
     return side
 
@@ -118,8 +158,9 @@ def cache_append(layout: LatentCacheLayout, latent_k, latent_v, dest_loc, cache_
     args.num_tokens = T
     args.num_heads = layout.num_heads
     args.rounding = _rounding_code(rounding)
-    ref_cache = cache_k if latent_k is not None else cache_v
-    args.num_slots = ref_cache.shape[0]
+    hm = layout.head_major
+    args.cache_layout = _lib.CACHE_HEAD_MAJOR if hm else _lib.CACHE_SLOT_MAJOR
+    args.num_slots = layout.num_slots_of(cache_k, "k") if latent_k is not None else layout.num_slots_of(cache_v, "v")
     args.dest_loc = dest_loc.data_ptr()
     for name, lat, cache, scale, total in (("k", latent_k, cache_k, scale_k, layout.sum_k),
                                             ("v", latent_v, cache_v, scale_v, layout.sum_v)):
@@ -127,11 +168,15 @@ def cache_append(layout: LatentCacheLayout, latent_k, latent_v, dest_loc, cache_
             continue
         if lat.dim() != 2 or lat.shape[0] != T or lat.shape[1] != total:
             raise ValueError(f"latent_{name} must be [{T}, {total}], got {tuple(lat.shape)}")
-        if cache.dim() != 2 or cache.shape[1] != total or scale.shape[1] != layout.num_heads:
-            raise ValueError(f"cache_{name} / scale_{name} do not match the layout")
-        if cache.shape[0] != args.num_slots or scale.shape[0] != args.num_slots:
-            raise ValueError("K and V caches must have the same number of slots")
-        setattr(args, name, _append_side(lat, layout.off_c(name), None, cache, scale, keep))
+        if hm:
+            if cache.numel() != args.num_slots * total or tuple(scale.shape) != (layout.num_heads, args.num_slots):
+                raise ValueError(f"cache_{name} / scale_{name} do not match the head-major layout")
+        else:
+            if cache.dim() != 2 or cache.shape[1] != total or scale.shape[1] != layout.num_heads:
+                raise ValueError(f"cache_{name} / scale_{name} do not match the layout")
+            if cache.shape[0] != args.num_slots or scale.shape[0] != args.num_slots:
+                raise ValueError("K and V caches must have the same number of slots")
+        setattr(args, name, _append_side(lat, layout.off_c(name), None, cache, scale, keep, hm))
     args.status_word = status_word.data_ptr() if status_word is not None else None
     _lib.check(lib.lsvd_cache_append(C.byref(args), _stream_ptr(dest_loc)))
 
@@ -243,7 +288,17 @@ def token_decode_attention_int8_latent_absorb(
         raise ValueError("a LatentCacheLayout is needed for 2-D (ragged) caches")
     if layout.num_heads != q_head_num:
         raise ValueError("only num_q_heads == num_kv_heads is supported")
-    if cache_latent_k.shape[1] != layout.sum_k or cache_latent_v.shape[1] != layout.sum_v:
+    hm = layout.head_major
+    if hm:
+        n_slots = layout.num_slots_of(cache_latent_k, "k")
+        if (cache_latent_k.numel() != n_slots * layout.sum_k or cache_latent_v.numel() != n_slots * layout.sum_v or
+                tuple(cache_latent_k_scale.shape) != (layout.num_heads, n_slots) or
+                tuple(cache_latent_v_scale.shape) != (layout.num_heads, n_slots)):
+            raise ValueError("caches / scales do not match the head-major layout")
+        if not (cache_latent_k.is_contiguous() and cache_latent_v.is_contiguous() and cache_latent_k_scale.is_contiguous()
+                and cache_latent_v_scale.is_contiguous()):
+            raise ValueError("head-major caches and scales must be contiguous")
+    elif cache_latent_k.shape[1] != layout.sum_k or cache_latent_v.shape[1] != layout.sum_v:
         raise ValueError("cache row width does not match the layout")
     if up_k.shape != (layout.sum_k, head_dim) or (up_v is not None and up_v.shape != (layout.sum_v, head_dim)):
         raise ValueError("up-factors must be [sum r, head_dim]")
@@ -260,13 +315,14 @@ def token_decode_attention_int8_latent_absorb(
     a.batch, a.num_heads, a.head_dim = B, q_head_num, head_dim
     a.max_len_in_batch = int(infer_state.max_len_in_batch)
     a.sm_scale = float(sm_scale) if sm_scale is not None else 0.0
-    a.num_slots = cache_latent_k.shape[0]
+    a.num_slots = layout.num_slots_of(cache_latent_k, "k")
+    a.cache_layout = _lib.CACHE_HEAD_MAJOR if hm else _lib.CACHE_SLOT_MAJOR
     a.q, a.q_stride_b, a.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
     a.k_off, a.v_off = layout.off_c("k"), layout.off_c("v")
-    a.cache_k, a.cache_k_row_stride = cache_latent_k.data_ptr(), cache_latent_k.stride(0)
-    a.scale_k, a.scale_k_row_stride = cache_latent_k_scale.data_ptr(), cache_latent_k_scale.stride(0)
-    a.cache_v, a.cache_v_row_stride = cache_latent_v.data_ptr(), cache_latent_v.stride(0)
-    a.scale_v, a.scale_v_row_stride = cache_latent_v_scale.data_ptr(), cache_latent_v_scale.stride(0)
+    a.cache_k, a.cache_k_row_stride = cache_latent_k.data_ptr(), 0 if hm else cache_latent_k.stride(0)
+    a.scale_k, a.scale_k_row_stride = cache_latent_k_scale.data_ptr(), 0 if hm else cache_latent_k_scale.stride(0)
+    a.cache_v, a.cache_v_row_stride = cache_latent_v.data_ptr(), 0 if hm else cache_latent_v.stride(0)
+    a.scale_v, a.scale_v_row_stride = cache_latent_v_scale.data_ptr(), 0 if hm else cache_latent_v_scale.stride(0)
     a.up_k, a.up_k_row_stride = up_k.data_ptr(), up_k.stride(0)
     if up_v is not None:
         a.up_v, a.up_v_row_stride = up_v.data_ptr(), up_v.stride(0)
@@ -317,9 +373,10 @@ class LatentDecodeAttention(nn.Module):
                 raise ValueError(f"latent decode attention only supports query_len=1, got {q.shape[1]}")
             q = q[:, 0]
         if latent_k is not None or latent_v is not None:
+            hm = self.layout.head_major
             cache_append(self.layout, latent_k, latent_v, infer_state.mem_index,
-                         cache_k.view(cache_k.shape[0], -1), scale_k, cache_v.view(cache_v.shape[0], -1), scale_v,
-                         rounding=self.rounding)
+                         cache_k if hm else cache_k.view(cache_k.shape[0], -1), scale_k,
+                         cache_v if hm else cache_v.view(cache_v.shape[0], -1), scale_v, rounding=self.rounding)
         ws = self._ws(infer_state.batch_size, infer_state.max_len_in_batch, q.device)
         return token_decode_attention_int8_latent_absorb(
             q, infer_state, self.layout.num_heads, self.head_dim, cache_k, scale_k, cache_v, scale_v,

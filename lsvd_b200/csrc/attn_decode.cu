@@ -29,7 +29,7 @@
 #include <cstring>
 #include <mutex>
 
-#include "common.cuh"
+#include "attn.cuh"
 
 namespace lsvd {
 
@@ -42,14 +42,6 @@ constexpr int kMaxItemTiles = 8;         // and its largest number of 32-token s
 constexpr int kLimbMax = 63 * (16384 + 128 + 1);   // largest integer three balanced base-128 limbs hold
 constexpr float kLog2e = 1.4426950408889634f;
 
-struct HeadPlan {
-  int32_t k_col, v_col;      // byte offsets of the head inside a K / V cache row
-  int16_t nk, nv;            // 16-entry chunks of K and V
-  int16_t chunk_tiles;       // tiles per work item of this head
-  int16_t parts;             // work items per request (bounded with max_len_in_batch)
-  int32_t part_off;          // first item of this head inside a request's item list
-  int32_t acc_off;           // float offset of this head's partial accumulators inside a request's block
-};
 
 struct StreamParams {
   const int8_t* cache_k;
@@ -69,6 +61,7 @@ struct StreamParams {
   int32_t* status_word;
   int32_t batch, num_heads, num_slots, sum_rk;
   int32_t items_per_request, acc_per_request, total_items;
+  int32_t head_major;        // cache layout: 0 = [slot][sum r] + scales [slot][H]; 1 = [head][slot][r_h] + scales [H][slot]
   HeadPlan head[LSVD_MAX_HEADS];
 };
 
@@ -228,15 +221,18 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
   const int nkb = (nk + 1) >> 1;                 // 32-rank blocks of K
   const int nvg = (nv + 3) >> 2;                 // 64-rank groups of V
   const int g = lane >> 2, t4 = lane & 3;
-  const int8_t* kbase = p.cache_k + H.k_col + t4 * 8;
-  const int8_t* vbase = p.cache_v + H.v_col + g * 8;
+  // head-major layout: a head's rows of consecutive slots are contiguous (r_h bytes apart), and so are its scales
+  const int8_t* kbase = p.cache_k + (p.head_major ? static_cast<int64_t>(H.k_col) * p.num_slots : H.k_col) + t4 * 8;
+  const int8_t* vbase = p.cache_v + (p.head_major ? static_cast<int64_t>(H.v_col) * p.num_slots : H.v_col) + g * 8;
   const bool v_ok0 = g * 8 < nv * 16, v_ok1 = 64 + g * 8 < nv * 16;
-  const __half* ksc = p.scale_k + h;
-  const __half* vsc = p.scale_v + h;
+  const __half* ksc = p.head_major ? p.scale_k + static_cast<int64_t>(h) * p.num_slots : p.scale_k + h;
+  const __half* vsc = p.head_major ? p.scale_v + static_cast<int64_t>(h) * p.num_slots : p.scale_v + h;
+  const int64_t ks_stride = p.head_major ? 1 : p.scale_k_row_stride, vs_stride = p.head_major ? 1 : p.scale_v_row_stride;
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
   const float step = p.qstep[b * p.num_heads + h];
   // row strides fit 32 bits (checked by the host): a row address is one 32 x 32 + 64-bit multiply-add
-  const uint32_t kstride = static_cast<uint32_t>(p.cache_k_row_stride), vstride = static_cast<uint32_t>(p.cache_v_row_stride);
+  const uint32_t kstride = p.head_major ? static_cast<uint32_t>(nk * 16) : static_cast<uint32_t>(p.cache_k_row_stride);
+  const uint32_t vstride = p.head_major ? static_cast<uint32_t>(nv * 16) : static_cast<uint32_t>(p.cache_v_row_stride);
 
   __syncwarp();
   {
@@ -302,7 +298,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     resolve(s0, valid, rslot);
   }
   load_k(rslot);
-  float ks = __half2float(ksc[rslot * p.scale_k_row_stride]);
+  float ks = __half2float(ksc[rslot * ks_stride]);
   int slot_n1 = -1;                  // slot of "my" token of the next step (lane = token role)
   if (tok_begin + kTileTokens + lane < tok_end) slot_n1 = r2t[tok_begin + kTileTokens + lane];
 
@@ -319,7 +315,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
       if (v_ok0) va[i] = ldg64(row);
       if (v_ok1) vb[i] = ldg64(row + 64);
     }
-    const float vs = __half2float(vsc[rslot * p.scale_v_row_stride]);
+    const float vs = __half2float(vsc[rslot * vs_stride]);
 
     // ---- scores ----
     float sc[4];                     // score of token g + 8j, in lanes t = 0, 1 of the quad
@@ -356,7 +352,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     if (tb + kTileTokens < tok_end) {
       resolve(slot_n1, valid, rslot);
       load_k(rslot);
-      ks = __half2float(ksc[rslot * p.scale_k_row_stride]);
+      ks = __half2float(ksc[rslot * ks_stride]);
     }
     // ---- online softmax; the running maximum is shared by the warp ----
     const float mx = fmaxf(m, warp_max_redux(s));
@@ -570,13 +566,6 @@ __global__ void __launch_bounds__(128) merge_up_kernel(const __grid_constant__ M
 // ----------------------------------------------------------------------------------------------
 // host: planning, validation, launch
 // ----------------------------------------------------------------------------------------------
-struct HostPlan {
-  HeadPlan head[LSVD_MAX_HEADS];
-  int item_bytes = 0;
-  int items_per_request = 0, acc_per_request = 0;
-  int64_t total_items = 0;
-  int num_blocks = 0;
-};
 
 static int validate_offsets(const int32_t* off, int num_heads) {
   if (off == nullptr || off[0] != 0) return LSVD_ERR_INVALID_ARG;
@@ -637,9 +626,6 @@ static int make_plan(int batch, int num_heads, const int32_t* k_off, const int32
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-struct WorkspaceLayout {
-  size_t qlimb, qstep, queue, part_ml, part_acc, total;
-};
 
 static WorkspaceLayout workspace_layout(int batch, int num_heads, int sum_rk, int64_t items_per_request,
                                         int64_t acc_per_request) {
@@ -683,8 +669,10 @@ extern "C" int lsvd_attn_decode_plan(int32_t batch, int32_t num_heads, const int
   return LSVD_OK;
 }
 
-extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
-  using namespace lsvd;
+namespace lsvd {
+
+// Argument checks, the plan and the workspace layout of a call.
+int attn_prepare(const lsvd_attn_decode_args* a, AttnLaunch* L) {
   if (a == nullptr) return LSVD_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->head_dim <= 0 || a->head_dim > 256 || (a->head_dim % 8) != 0) return LSVD_ERR_INVALID_ARG;
   if (a->num_slots <= 0 || a->max_len_in_batch < 0) return LSVD_ERR_INVALID_ARG;
@@ -693,76 +681,122 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
     return LSVD_ERR_INVALID_ARG;
   if (a->out == nullptr && a->out_latent == nullptr) return LSVD_ERR_INVALID_ARG;
   if (a->out != nullptr && a->up_v == nullptr) return LSVD_ERR_INVALID_ARG;
-  HostPlan hp;
-  int rc = make_plan(a->batch, a->num_heads, a->k_off, a->v_off, a->max_len_in_batch, &hp);
+  if (a->cache_layout != LSVD_CACHE_SLOT_MAJOR && a->cache_layout != LSVD_CACHE_HEAD_MAJOR) return LSVD_ERR_INVALID_ARG;
+  int rc = make_plan(a->batch, a->num_heads, a->k_off, a->v_off, a->max_len_in_batch, &L->hp);
   if (rc != LSVD_OK) return rc;
   const int sum_rk = a->k_off[a->num_heads], sum_rv = a->v_off[a->num_heads];
-  if (!aligned(a->cache_k, 16) || !aligned(a->cache_v, 16) || (a->cache_k_row_stride % 16) != 0 ||
-      (a->cache_v_row_stride % 16) != 0 || a->cache_k_row_stride < sum_rk || a->cache_v_row_stride < sum_rv)
-    return LSVD_ERR_INVALID_ARG;
-  if (a->cache_k_row_stride > 0x7fffffffLL || a->cache_v_row_stride > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
-  if (a->scale_k_row_stride < a->num_heads || a->scale_v_row_stride < a->num_heads) return LSVD_ERR_INVALID_ARG;
+  if (!aligned(a->cache_k, 16) || !aligned(a->cache_v, 16)) return LSVD_ERR_INVALID_ARG;
+  if (a->cache_layout == LSVD_CACHE_SLOT_MAJOR) {
+    if ((a->cache_k_row_stride % 16) != 0 || (a->cache_v_row_stride % 16) != 0 || a->cache_k_row_stride < sum_rk ||
+        a->cache_v_row_stride < sum_rv)
+      return LSVD_ERR_INVALID_ARG;
+    if (a->cache_k_row_stride > 0x7fffffffLL || a->cache_v_row_stride > 0x7fffffffLL) return LSVD_ERR_UNSUPPORTED;
+    if (a->scale_k_row_stride < a->num_heads || a->scale_v_row_stride < a->num_heads) return LSVD_ERR_INVALID_ARG;
+  }
   if (!aligned(a->q, 2) || !aligned(a->up_k, 2) || !aligned(a->scale_k, 2) || !aligned(a->scale_v, 2))
     return LSVD_ERR_INVALID_ARG;
-  const WorkspaceLayout wl = workspace_layout(a->batch, a->num_heads, sum_rk, hp.items_per_request, hp.acc_per_request);
-  if (a->workspace == nullptr || a->workspace_bytes < wl.total || !aligned(a->workspace, 256)) return LSVD_ERR_WORKSPACE;
-  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / std::sqrt(static_cast<float>(a->head_dim));
+  L->wl = workspace_layout(a->batch, a->num_heads, sum_rk, L->hp.items_per_request, L->hp.acc_per_request);
+  if (a->workspace == nullptr || a->workspace_bytes < L->wl.total || !aligned(a->workspace, 256)) return LSVD_ERR_WORKSPACE;
+  return LSVD_OK;
+}
 
+float attn_score_scale(const lsvd_attn_decode_args* a) {
+  const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / std::sqrt(static_cast<float>(a->head_dim));
+  return sm_scale * kLog2e;
+}
+
+int attn_launch_absorb(const lsvd_attn_decode_args* a, const AttnLaunch& L, cudaStream_t st) {
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
   AbsorbParams ap{};
   ap.q = static_cast<const __half*>(a->q);
   ap.q_stride_b = a->q_stride_b;
   ap.q_stride_h = a->q_stride_h;
   ap.up_k = static_cast<const __half*>(a->up_k);
   ap.up_k_row_stride = a->up_k_row_stride;
-  ap.qlimb = reinterpret_cast<uint4*>(ws + wl.qlimb);
-  ap.qstep = reinterpret_cast<float*>(ws + wl.qstep);
-  ap.queue = reinterpret_cast<int32_t*>(ws + wl.queue);
-  ap.score_scale = sm_scale * kLog2e;
+  ap.qlimb = reinterpret_cast<uint4*>(ws + L.wl.qlimb);
+  ap.qstep = reinterpret_cast<float*>(ws + L.wl.qstep);
+  ap.queue = reinterpret_cast<int32_t*>(ws + L.wl.queue);
+  ap.score_scale = attn_score_scale(a);
   ap.num_heads = a->num_heads;
   ap.head_dim = a->head_dim;
-  ap.sum_rk = sum_rk;
+  ap.sum_rk = a->k_off[a->num_heads];
   ap.up_k_vec16 = (aligned(a->up_k, 16) && (a->up_k_row_stride % 8) == 0) ? 1 : 0;
   std::memcpy(ap.k_off, a->k_off, sizeof(int32_t) * (a->num_heads + 1));
   LSVD_CUDA_TRY(launch_chained(absorb_query_kernel, dim3(a->num_heads, a->batch), dim3(128), 0, st, 1, true, ap));
+  return LSVD_OK;
+}
 
-  if (a->max_len_in_batch > 0) {
-    StreamParams sp{};
-    sp.cache_k = a->cache_k;
-    sp.cache_v = a->cache_v;
-    sp.scale_k = static_cast<const __half*>(a->scale_k);
-    sp.scale_v = static_cast<const __half*>(a->scale_v);
-    sp.cache_k_row_stride = a->cache_k_row_stride;
-    sp.cache_v_row_stride = a->cache_v_row_stride;
-    sp.scale_k_row_stride = a->scale_k_row_stride;
-    sp.scale_v_row_stride = a->scale_v_row_stride;
-    sp.req_to_token = a->req_to_token;
-    sp.req_to_token_stride = a->req_to_token_stride;
-    sp.b_req_idx = a->b_req_idx;
-    sp.b_seq_len = a->b_seq_len;
-    sp.qlimb = ap.qlimb;
-    sp.qstep = ap.qstep;
-    sp.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
-    sp.part_acc = reinterpret_cast<float*>(ws + wl.part_acc);
-    sp.queue = ap.queue;
-    sp.status_word = a->status_word;
-    sp.batch = a->batch;
-    sp.num_heads = a->num_heads;
-    sp.num_slots = a->num_slots;
-    sp.sum_rk = sum_rk;
-    sp.items_per_request = hp.items_per_request;
-    sp.acc_per_request = hp.acc_per_request;
-    sp.total_items = static_cast<int32_t>(hp.total_items);
-    for (int h = 0; h < a->num_heads; ++h) sp.head[h] = hp.head[h];
-    if (a->ev_stream_begin) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_begin), st));
-    LSVD_CUDA_TRY(launch_chained(latent_stream_kernel, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
-    if (a->ev_stream_end) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_end), st));
+int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cudaStream_t st) {
+  if (a->max_len_in_batch <= 0) return LSVD_OK;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const HostPlan& hp = L.hp;
+  StreamParams sp{};
+  sp.cache_k = a->cache_k;
+  sp.cache_v = a->cache_v;
+  sp.scale_k = static_cast<const __half*>(a->scale_k);
+  sp.scale_v = static_cast<const __half*>(a->scale_v);
+  sp.cache_k_row_stride = a->cache_k_row_stride;
+  sp.cache_v_row_stride = a->cache_v_row_stride;
+  sp.scale_k_row_stride = a->scale_k_row_stride;
+  sp.scale_v_row_stride = a->scale_v_row_stride;
+  sp.req_to_token = a->req_to_token;
+  sp.req_to_token_stride = a->req_to_token_stride;
+  sp.b_req_idx = a->b_req_idx;
+  sp.b_seq_len = a->b_seq_len;
+  sp.qlimb = reinterpret_cast<uint4*>(ws + L.wl.qlimb);
+  sp.qstep = reinterpret_cast<float*>(ws + L.wl.qstep);
+  sp.part_ml = reinterpret_cast<float*>(ws + L.wl.part_ml);
+  sp.part_acc = reinterpret_cast<float*>(ws + L.wl.part_acc);
+  sp.queue = reinterpret_cast<int32_t*>(ws + L.wl.queue);
+  sp.status_word = a->status_word;
+  sp.batch = a->batch;
+  sp.num_heads = a->num_heads;
+  sp.num_slots = a->num_slots;
+  sp.sum_rk = a->k_off[a->num_heads];
+  sp.items_per_request = hp.items_per_request;
+  sp.acc_per_request = hp.acc_per_request;
+  sp.total_items = static_cast<int32_t>(hp.total_items);
+  sp.head_major = a->cache_layout == LSVD_CACHE_HEAD_MAJOR ? 1 : 0;
+  for (int h = 0; h < a->num_heads; ++h) sp.head[h] = hp.head[h];
+  if (a->ev_stream_begin) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_begin), st));
+  LSVD_CUDA_TRY(launch_chained(latent_stream_kernel, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
+  if (a->ev_stream_end) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_end), st));
+  return LSVD_OK;
+}
+
+// The merge's view of the plan and the workspace, for the fused kernel that runs the merge as one of its stages.
+void attn_fill_merge(const lsvd_attn_decode_args* a, const AttnLaunch& L, FMerge* mg) {
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  mg->part_ml = reinterpret_cast<const float*>(ws + L.wl.part_ml);
+  mg->part_acc = reinterpret_cast<const float*>(ws + L.wl.part_acc);
+  mg->b_seq_len = a->b_seq_len;
+  mg->out_latent = static_cast<__half*>(a->out_latent);
+  mg->out_latent_stride = a->out_latent_stride_b;
+  mg->num_heads = a->num_heads;
+  mg->items_per_request = L.hp.items_per_request;
+  mg->acc_per_request = L.hp.acc_per_request;
+  std::memcpy(mg->v_off, a->v_off, sizeof(int32_t) * (a->num_heads + 1));
+  for (int h = 0; h < a->num_heads; ++h) {
+    mg->part_off[h] = L.hp.head[h].part_off;
+    mg->acc_off[h] = L.hp.head[h].acc_off;
+    mg->chunk_tiles[h] = L.hp.head[h].chunk_tiles;
+    mg->parts[h] = L.hp.head[h].parts;
   }
+}
 
+void attn_workspace_views(const lsvd_attn_decode_args* a, const AttnLaunch& L, uint4** qlimb, float** qstep, int32_t** queue) {
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  *qlimb = reinterpret_cast<uint4*>(ws + L.wl.qlimb);
+  *qstep = reinterpret_cast<float*>(ws + L.wl.qstep);
+  *queue = reinterpret_cast<int32_t*>(ws + L.wl.queue);
+}
+
+int attn_launch_merge(const lsvd_attn_decode_args* a, const AttnLaunch& L, cudaStream_t st) {
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const HostPlan& hp = L.hp;
   MergeParams mp{};
-  mp.part_ml = reinterpret_cast<const float*>(ws + wl.part_ml);
-  mp.part_acc = reinterpret_cast<const float*>(ws + wl.part_acc);
+  mp.part_ml = reinterpret_cast<const float*>(ws + L.wl.part_ml);
+  mp.part_acc = reinterpret_cast<const float*>(ws + L.wl.part_acc);
   mp.b_seq_len = a->b_seq_len;
   mp.up_v = static_cast<const __half*>(a->up_v);
   mp.up_v_row_stride = a->up_v_row_stride;
@@ -790,6 +824,21 @@ extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
   if (merge_smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(merge_up_kernel), merge_smem));
   LSVD_CUDA_TRY(launch_chained(merge_up_kernel, dim3(a->num_heads, a->batch), dim3(128), merge_smem, st, 1, true, mp));
   return LSVD_OK;
+}
+
+}  // namespace lsvd
+
+extern "C" int lsvd_attn_decode(const lsvd_attn_decode_args* a, void* stream) {
+  using namespace lsvd;
+  AttnLaunch L;
+  int rc = attn_prepare(a, &L);
+  if (rc != LSVD_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = attn_launch_absorb(a, L, st);
+  if (rc != LSVD_OK) return rc;
+  rc = attn_launch_stream(a, L, st);
+  if (rc != LSVD_OK) return rc;
+  return attn_launch_merge(a, L, st);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -13,6 +13,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "devfn.cuh"
 
 namespace lsvd {
 
@@ -33,36 +34,16 @@ struct AppendParams {
   int32_t* status_word;
   int32_t num_tokens, num_heads, num_slots, rounding;
   int32_t side_mask;                   // bit 0: K present, bit 1: V present
+  int32_t head_major;                  // cache layout: 0 = [slot][sum r] (+ scales [slot][H]), 1 = [head][slot][r_h] (+ [H][slot])
 };
 
-// `r` = the correctly rounded reciprocal of the scale (__frcp_rn), used by the fp16-division form only.
-template <int kRounding>
-__device__ __forceinline__ int quantise_one(float x, float s, float r) {
-  if (kRounding == LSVD_ROUND_TORCH) {
-    // fp16 division = exact quotient rounded once to fp16; then round half to even.  Both roundings are done with
-    // additions instead of conversions (the conversion unit is what bounds this kernel at prefill sizes):
-    //   * to 11 significant bits: add and subtract 1.5 * 2^(e + 13), e the exponent of y -- the sum lies in the binade
-    //     whose spacing is 2^(e - 10), the spacing of fp16 numbers around y, and fp32 addition rounds ties to even.
-    //     (Below 2^-14, where fp16 is coarser than that, the code is 0 either way.)  Quotients beyond +-256 end at a
-    //     clamp bound whatever their rounding, so they are clamped first, which also keeps e + 13 in range;
-    //   * to an integer: add 1.5 * 2^23 and read the low mantissa bits.
-    // The quotient: x and s are fp16 numbers, so x / s is a ratio of two 11-bit integers and stays at least two fp32
-    // spacings away from every fp16 rounding boundary it does not hit exactly.  A quotient within one spacing of the
-    // exact one therefore rounds to the same fp16 number as the IEEE quotient: q0 = x r, one residual, one correction
-    // (three FMA-pipe operations instead of a division per entry); a boundary that is hit exactly is representable
-    // and comes out exact.
-    const float q0 = __fmul_rn(x, r);
-    float y = __fmaf_rn(__fmaf_rn(-s, q0, x), r, q0);
-    y = fminf(fmaxf(y, -256.f), 256.f);
-    const float c = __uint_as_float(((__float_as_uint(y) & 0x7f800000u) + (13u << 23)) | 0x00400000u);
-    y = __fsub_rn(__fadd_rn(y, c), c);
-    const int q = __float_as_int(__fadd_rn(y, 12582912.f)) - 0x4b400000;
-    return min(max(q, -128), 127);
-  } else {
-    float y = __fdiv_rn(x, s);
-    int r = static_cast<int>(y >= 0.f ? y + 0.5f : y - 0.5f);   // conversion truncates toward zero
-    return min(max(r, -128), 127);
-  }
+// Where the codes of (slot, head) start and where its scale lives, in either layout.
+__device__ __forceinline__ int8_t* cache_unit(const AppendParams& p, const AppendSide& s, int dest, int r0, int rank) {
+  return p.head_major ? s.cache + static_cast<int64_t>(r0) * p.num_slots + static_cast<int64_t>(dest) * rank
+                      : s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0;
+}
+__device__ __forceinline__ __half* scale_unit(const AppendParams& p, const AppendSide& s, int dest, int h) {
+  return p.head_major ? s.scale + static_cast<int64_t>(h) * p.num_slots + dest : s.scale + static_cast<int64_t>(dest) * s.scale_row_stride + h;
 }
 
 template <int kRounding>
@@ -123,10 +104,10 @@ __global__ void __launch_bounds__(128) cache_append_kernel(const __grid_constant
       const int q = quantise_one<kRounding>(x[j], sf, rsf);
       packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * j);
     }
-    int8_t* dst = s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0 + i0;
+    int8_t* dst = cache_unit(p, s, dest, r0, rank) + i0;
     *reinterpret_cast<uint32_t*>(dst) = packed;
   }
-  if (lane == 0) s.scale[static_cast<int64_t>(dest) * s.scale_row_stride + h] = s16;
+  if (lane == 0) *scale_unit(p, s, dest, h) = s16;
 }
 
 // Prefill-sized calls.  Units are ordered head by head (all tokens of head 0 of K, then head 1, ...), so a warp works
@@ -199,14 +180,14 @@ __global__ void __launch_bounds__(128) cache_append_wide_kernel(const __grid_con
       lo |= (static_cast<uint32_t>(quantise_one<kRounding>(x[j], sf, rsf)) & 0xffu) << (8 * j);
       hi |= (static_cast<uint32_t>(quantise_one<kRounding>(x[4 + j], sf, rsf)) & 0xffu) << (8 * j);
     }
-    *reinterpret_cast<uint2*>(s.cache + static_cast<int64_t>(dest) * s.cache_row_stride + r0 + i0) = make_uint2(lo, hi);
+    *reinterpret_cast<uint2*>(cache_unit(p, s, dest, r0, rank) + i0) = make_uint2(lo, hi);
   }
-  if (sub == 0) s.scale[static_cast<int64_t>(dest) * s.scale_row_stride + h] = s16;
+  if (sub == 0) *scale_unit(p, s, dest, h) = s16;
 }
 
 // The wide kernel's accesses: 16-byte loads of the latents, 8-byte stores of the codes.
-static bool side_is_wide_ok(const lsvd_append_tensor& t, int num_heads) {
-  if (!aligned(t.latent, 16) || (t.token_stride % 8) != 0 || !aligned(t.cache, 8) || (t.cache_row_stride % 8) != 0) return false;
+static bool side_is_wide_ok(const lsvd_append_tensor& t, int num_heads, bool head_major) {
+  if (!aligned(t.latent, 16) || (t.token_stride % 8) != 0 || !aligned(t.cache, 8) || (!head_major && (t.cache_row_stride % 8) != 0)) return false;
   for (int h = 0; h < num_heads; ++h) {
     const int64_t off = t.head_off ? t.head_off[h] : t.rank_off[h];
     if ((off % 8) != 0) return false;
@@ -214,7 +195,7 @@ static bool side_is_wide_ok(const lsvd_append_tensor& t, int num_heads) {
   return true;
 }
 
-static int fill_side(AppendSide& dst, const lsvd_append_tensor& src, int num_heads) {
+static int fill_side(AppendSide& dst, const lsvd_append_tensor& src, int num_heads, bool head_major) {
   if (src.rank_off == nullptr || src.cache == nullptr || src.cache_scale == nullptr) return LSVD_ERR_INVALID_ARG;
   if (src.rank_off[0] != 0) return LSVD_ERR_INVALID_ARG;
   for (int h = 0; h < num_heads; ++h) {
@@ -224,9 +205,9 @@ static int fill_side(AppendSide& dst, const lsvd_append_tensor& src, int num_hea
     dst.head_off[h] = src.head_off ? src.head_off[h] : src.rank_off[h];
   }
   dst.rank_off[num_heads] = src.rank_off[num_heads];
-  if (src.cache_row_stride < src.rank_off[num_heads] || (src.cache_row_stride % 4) != 0) return LSVD_ERR_INVALID_ARG;
-  if (!aligned(src.cache, 4) || !aligned(src.latent, 2) || !aligned(src.cache_scale, 2)) return LSVD_ERR_INVALID_ARG;
-  if (src.scale_row_stride < num_heads) return LSVD_ERR_INVALID_ARG;
+  if (!head_major && (src.cache_row_stride < src.rank_off[num_heads] || (src.cache_row_stride % 4) != 0)) return LSVD_ERR_INVALID_ARG;
+  if (!aligned(src.cache, head_major ? 16 : 4) || !aligned(src.latent, 2) || !aligned(src.cache_scale, 2)) return LSVD_ERR_INVALID_ARG;
+  if (!head_major && src.scale_row_stride < num_heads) return LSVD_ERR_INVALID_ARG;
   dst.latent = static_cast<const __half*>(src.latent);
   dst.token_stride = src.token_stride;
   dst.cache = src.cache;
@@ -254,14 +235,16 @@ extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
   p.num_heads = a->num_heads;
   p.num_slots = a->num_slots;
   p.rounding = a->rounding;
+  if (a->cache_layout != LSVD_CACHE_SLOT_MAJOR && a->cache_layout != LSVD_CACHE_HEAD_MAJOR) return LSVD_ERR_INVALID_ARG;
+  p.head_major = a->cache_layout == LSVD_CACHE_HEAD_MAJOR ? 1 : 0;
   p.side_mask = 0;
   if (a->k.latent != nullptr) {
-    int rc = fill_side(p.side[0], a->k, a->num_heads);
+    int rc = fill_side(p.side[0], a->k, a->num_heads, p.head_major != 0);
     if (rc != LSVD_OK) return rc;
     p.side_mask |= 1;
   }
   if (a->v.latent != nullptr) {
-    int rc = fill_side(p.side[1], a->v, a->num_heads);
+    int rc = fill_side(p.side[1], a->v, a->num_heads, p.head_major != 0);
     if (rc != LSVD_OK) return rc;
     p.side_mask |= 2;
   }
@@ -274,7 +257,7 @@ extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
   bool wide = units >= 32768;
   for (int sd = 0; sd < 2 && wide; ++sd) {
     if (((p.side_mask >> sd) & 1) == 0) continue;
-    wide = side_is_wide_ok(sd == 0 ? a->k : a->v, a->num_heads);
+    wide = side_is_wide_ok(sd == 0 ? a->k : a->v, a->num_heads, p.head_major != 0);
   }
   if (wide) {
     WideTable wt{};

@@ -17,6 +17,7 @@ conversion is offline host code.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -199,7 +200,10 @@ class HybridFFN(nn.Module):
                              else hadamard_pack(self.had_K))
         self._plans = {}
         self._chains = {}
-        self.overlap_branches = True      # RTN gate/up on a second stream beside the SVD branch
+        self.overlap_branches = True      # RTN gate/up on a second stream beside the SVD branch (chain of launches)
+        # at most 16 tokens: the whole block as ONE persistent kernel (lsvd_ffn_decode with `fused`).  Off by default:
+        # measured on B200 it is exact but slower than the chain (78 vs 56 us at the 7B shape)
+        self.fused = os.environ.get("LSVD_FFN_FUSED", "0") == "1"
         self.rank = self.U_q.shape[0] // 2
         self.n_svd = self.Vg_q.shape[0]
         self.n_q = self.Wg_q.shape[0]
@@ -362,6 +366,7 @@ class HybridFFN(nn.Module):
         a.residual = _ptr(residual)
         a.residual_row_stride = residual.stride(0) if residual is not None else 0
         a.overlap = 1 if self.overlap_branches else 0
+        a.fused = 1 if self.fused else 0
         _lib.check(_lib.load().lsvd_ffn_decode(C.byref(a), _stream_ptr(x)))
         return out.view(*shape[:-1], self.d_out)
 
@@ -386,9 +391,11 @@ class HybridFFN(nn.Module):
             if self.had_K_packed is None:
                 self.had_K_packed = hadamard_pack(self.had_K)
             a.had_K_packed = self.had_K_packed.data_ptr()
-        ws = torch.empty(int(lib.lsvd_ffn_decode_workspace_bytes(m, self.d_in, self.d_ffn, self.rank)), dtype=torch.uint8,
-                         device=device)
+        # zeroed once: the fused form keeps its barrier counters there from call to call
+        ws = torch.zeros(int(lib.lsvd_ffn_decode_workspace_bytes(m, self.d_in, self.d_ffn, self.rank, self.d_out)),
+                         dtype=torch.uint8, device=device)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        a.fused = 1 if self.fused else 0
         got = (a, ws)
         self._chains[key] = got
         return got

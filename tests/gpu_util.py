@@ -24,16 +24,22 @@ def build_case(batch, num_heads, head_dim, k_ranks, v_ranks, seq_lens, seed=0, s
     return c
 
 
-def run_gpu(c, want="out", status=None):
+def run_gpu(c, want="out", status=None, head_major=False):
+    """The kernels on the case's cache; ``head_major`` re-stores the cache head by head first (same values)."""
     dev = "cuda"
     st = InferState(c["batch"], c["max_len"], c["b_seq_len"], device=dev, req_to_token=c["req_to_token"],
                     b_req_idx=c["b_req_idx"])
-    args = [c["q"].to(dev), st, c["num_heads"], c["head_dim"], c["cache_k"].to(dev), c["scale_k"].to(dev),
-            c["cache_v"].to(dev), c["scale_v"].to(dev), c["up_k"].to(dev)]
+    lay = c["layout"]
+    ck, sk, cv, sv = c["cache_k"], c["scale_k"], c["cache_v"], c["scale_v"]
+    if head_major:
+        lay = lay.as_head_major()
+        ck, sk = lay.to_head_major(ck, sk, "k")
+        cv, sv = lay.to_head_major(cv, sv, "v")
+    args = [c["q"].to(dev), st, c["num_heads"], c["head_dim"], ck.to(dev), sk.to(dev), cv.to(dev), sv.to(dev), c["up_k"].to(dev)]
     if want == "out":
-        o = token_decode_attention_int8_latent_absorb(*args, c["up_v"].to(dev), layout=c["layout"], status_word=status)
+        o = token_decode_attention_int8_latent_absorb(*args, c["up_v"].to(dev), layout=lay, status_word=status)
     else:
-        o = token_decode_attention_int8_latent_absorb(*args, None, layout=c["layout"], status_word=status)
+        o = token_decode_attention_int8_latent_absorb(*args, None, layout=lay, status_word=status)
     torch.cuda.synchronize()
     return o.cpu()
 

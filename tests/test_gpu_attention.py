@@ -118,3 +118,55 @@ def test_13b_shape_heads():
     kr = synth.ragged_ranks(40, 64, seed=7)
     vr = synth.ragged_ranks(40, 64, seed=8)
     check(U.build_case(3, 40, 128, kr, vr, [513, 64, 1000], seed=9, shuffle=True))
+
+
+@pytest.mark.parametrize("shuffle", [False, True])
+def test_head_major_cache_layout_same_bits(shuffle):
+    """The cache stored head by head ([H][N_slots][r_h], scales [H][N_slots]) holds the same values: the streaming
+    kernel runs the same arithmetic on it, so the output is bit-identical to the slot-major one (and checked against
+    the oracle by `check`).  Identity and shuffled slot maps, ragged ranks, ragged batch."""
+    kr = synth.ragged_ranks(32, 64, seed=3)
+    vr = synth.ragged_ranks(32, 64, seed=4)
+    c = U.build_case(4, 32, 128, kr, vr, [700, 1, 33, 1024], seed=12, shuffle=shuffle, extra_slots=50 if shuffle else 0)
+    o = check(c)
+    assert torch.equal(U.run_gpu(c, head_major=True), o)
+    assert torch.equal(U.run_gpu(c, want="latent", head_major=True), U.run_gpu(c, want="latent"))
+
+
+def _adversarial(c, kind):
+    """Put the case into a corner of the value range; the cache is re-quantised by the oracle."""
+    from oracle import quant
+    c = dict(c)
+    if kind == "peaked":
+        # one token per head whose key latent is aligned with the absorbed query and far larger than the rest:
+        # its score exceeds the others by tens of units, so the softmax is a one-hot up to e^-30
+        lk = c["latent_k"].clone().float()
+        qt = torch.einsum("rd,bhd->bhr", c["up_k"].float()[: c["k_off"][1]], c["q"].float()[:, :1])     # head 0 direction
+        lk[5, : c["k_off"][1]] = 40.0 * qt[0, 0] / qt[0, 0].abs().max()
+        c["latent_k"] = lk.half()
+    elif kind == "dominant_q":
+        q = c["q"].clone()
+        q[:, :, 7] = q[:, :, 7] * 1000.0                     # one query entry three orders above the rest
+        c["q"] = q
+    elif kind == "scale_v_range":
+        lv = c["latent_v"].clone().float()
+        n = lv.shape[0]
+        mag = torch.logspace(-4, 4, n).unsqueeze(1)           # value latents (hence scale_v) across eight decades
+        c["latent_v"] = (lv * mag).clamp(-60000, 60000).half()
+    c["cache_k"], c["scale_k"] = quant.latent_quant_ragged(c["latent_k"], c["k_off"])
+    c["cache_v"], c["scale_v"] = quant.latent_quant_ragged(c["latent_v"], c["v_off"])
+    return c
+
+
+@pytest.mark.parametrize("kind", ["peaked", "dominant_q", "scale_v_range"])
+def test_value_range_corners(kind):
+    """Where the kernel's block-floating query grid (21 bits per head) and the 16-bit per-step weight grid lose most:
+    a softmax dominated by one token, a query with one entry 1000x the rest, value scales spanning the fp16 range.
+    Still inside the specification's 2e-3 * ||o_ref||_2."""
+    kr = synth.ragged_ranks(8, 64, seed=5)
+    vr = synth.ragged_ranks(8, 64, seed=6)
+    c = _adversarial(U.build_case(2, 8, 128, kr, vr, [300, 77], seed=13), kind)
+    o = U.run_gpu(c)
+    o_ref, _ = U.run_oracle(c)
+    assert torch.isfinite(o.float()).all()
+    assert rel_to_norm(o.float(), o_ref.float()) < TOL

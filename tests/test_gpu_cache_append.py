@@ -153,3 +153,31 @@ def test_append_many_tokens_out_of_range_slots_are_skipped_and_reported():
         q, s = quant.latent_quant_ragged(lat, list(offs))
         assert torch.equal(cache.cpu()[good], q[good]) and torch.equal(scale.cpu()[good], s[good])
         assert (cache.cpu()[~good] == 0).all() and (scale.cpu()[~good] == 0).all()
+
+
+@pytest.mark.parametrize("tokens", [37, 2100])
+def test_head_major_layout_holds_the_same_codes(tokens):
+    """LSVD_CACHE_HEAD_MAJOR ([H][N_slots][r_h] + scales [H][N_slots]): the same codes and scales as the slot-major
+    cache, in both the decode-sized and the prefill-sized kernel (2100 tokens x 5 heads x 2 sides = 21 000 units < 32 768
+    stays on the first; the second size is reached with 16 heads below)."""
+    gen = torch.Generator().manual_seed(tokens)
+    heads = 5 if tokens < 100 else 16
+    k_ranks = synth.ragged_ranks(heads, 64, seed=1) if heads == 16 else [16, 128, 48, 64, 32]
+    v_ranks = synth.ragged_ranks(heads, 64, seed=2) if heads == 16 else [64, 16, 16, 112, 128]
+    lay = LatentCacheLayout(k_ranks, v_ranks)
+    hm = lay.as_head_major()
+    N = tokens + 64
+    lk = (torch.randn(tokens, lay.sum_k, generator=gen) * 2).half().cuda()
+    lv = (torch.randn(tokens, lay.sum_v, generator=gen) * 0.5).half().cuda()
+    dest = torch.randperm(N, generator=gen)[:tokens].to(torch.int32).cuda()
+    ck, sk, cv, sv = [t.zero_() for t in lay.alloc(N)]
+    hk, hsk, hv, hsv = [t.zero_() for t in hm.alloc(N)]
+    cache_append(lay, lk, lv, dest, ck, sk, cv, sv)
+    cache_append(hm, lk, lv, dest, hk, hsk, hv, hsv)
+    torch.cuda.synchronize()
+    k2, sk2 = hm.from_head_major(hk, hsk, "k")
+    v2, sv2 = hm.from_head_major(hv, hsv, "v")
+    assert torch.equal(k2, ck) and torch.equal(sk2, sk) and torch.equal(v2, cv) and torch.equal(sv2, sv)
+    # and the conversion helpers are inverses of each other
+    fk, fsk = hm.to_head_major(ck, sk, "k")
+    assert torch.equal(fk, hk) and torch.equal(fsk, hsk)
