@@ -93,6 +93,17 @@ typedef struct lsvd_append_args {
 
 int lsvd_cache_append(const lsvd_append_args* args, void* stream);
 
+/* Advance the batch bookkeeping of a decode loop by one token, on the device (no host round trip between steps, so a
+ * step can be replayed as a CUDA graph): b_seq_len[b] += 1 and mem_index[b] = req_to_token[b_req_idx[b], b_seq_len[b] - 1],
+ * the slot the next step appends to.  The fields are those of the reference's MockInferState
+ * (kernels/layer_bench/ffn_kernel/baseline_kernel.py:38-53), which the reference rebuilds on the host for every step.
+ * A length that would pass max_len is left alone and reported as LSVD_ERR_BOUNDS in the status word.  With period > 0 a
+ * request that reaches base_len + period starts over at base_len (benchmarks that replay more steps than the context
+ * they reserved). */
+int lsvd_decode_advance(int32_t* b_seq_len, int32_t* mem_index, const int32_t* req_to_token, int64_t req_to_token_stride,
+                        const int32_t* b_req_idx, int32_t batch, int32_t base_len, int32_t period, int32_t max_len,
+                        int32_t* status_word, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * int8 latent flash-decoding attention, one query token per request ("absorb" form).
  * Replaces token_decode_attention_flash_int8_latent_per_head_decoding_rope
@@ -104,6 +115,8 @@ int lsvd_cache_append(const lsvd_append_args* args, void* stream);
  *   o    = B_v^T o_lat                             (written to out if not NULL)
  * Request b reads the cache rows req_to_token[b_req_idx[b], 0 .. b_seq_len[b]-1].  A request of
  * length 0 gets zeros (the reference leaves 0/0 there).  num_q_heads == num_kv_heads only.
+ * up_k and up_v are weights: the kernels may read them before the work queued ahead of the call on `stream` has
+ * finished (they start under programmatic stream serialisation), so they must not be produced by that work.
  * ------------------------------------------------------------------------------------------- */
 typedef struct lsvd_attn_decode_args {
   int32_t batch;
@@ -142,6 +155,9 @@ typedef struct lsvd_attn_decode_args {
   void* ev_stream_begin;         /* optional cudaEvent_t pair recorded around the streaming kernel alone (the      */
   void* ev_stream_end;           /* launch that reads the cache), for roofline measurements; NULL = not recorded   */
   int32_t cache_layout;          /* LSVD_CACHE_*                                                                   */
+  int32_t req_to_token_rows;     /* rows of req_to_token: a b_req_idx outside [0, rows) is skipped and reported as     */
+                                 /* LSVD_ERR_BOUNDS (0: not checked).  A b_seq_len above max_len_in_batch is treated   */
+                                 /* as max_len_in_batch and reported the same way.                                      */
 } lsvd_attn_decode_args;
 
 /* Bytes of workspace lsvd_attn_decode needs for this problem on the current device. */
@@ -165,7 +181,7 @@ int lsvd_attn_decode_plan(int32_t batch, int32_t num_heads, const int32_t* k_off
  *     (the need grows with batch x (heads + context / item size); batch 16 x context 4096 at the 7B shape takes ~3 MB).
  *   - The call makes no cudaMalloc / cudaFree and uses no allocating library routine.  The first call on a
  *     device looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
- *     stream capture.
+ *     stream capture.  The address is kept for the life of the process (no cudaDeviceReset while the library is loaded).
  *   - The array keeps what the last call left in it; the one word that must start at zero (the work counter)
  *     is cleared on the stream by the first kernel of each call.  Two calls that overlap on the GPU (different
  *     streams, no ordering) race on the scratch: order them, or give one of them lsvd_attn_decode with its own
@@ -340,7 +356,9 @@ int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
  *   h = [ silu(Vg z_g) * (Vu z_u) | silu(Wg x_q) * (Wu x_q) ];  out = Wd quant(hadamard(h)) [+ residual]
  * Weights are int8 [out, in] row-major with one fp32 scale per output channel; all of them contiguous.
  * With overlap != 0 the RTN pair runs on a second stream owned by the library (created on first use, one per
- * device) and rejoins `stream` before the Hadamard step, also inside a stream capture.
+ * device) and rejoins `stream` before the Hadamard step, also inside a stream capture.  That stream and its two
+ * events are shared by every call on the device: with overlap != 0 the entry point is for ONE calling thread and ONE
+ * caller stream per device at a time (concurrent callers must pass overlap = 0 or serialise their calls).
  * ------------------------------------------------------------------------------------------- */
 typedef struct lsvd_ffn_decode_args {
   int32_t m, d_in, d_ffn, d_out, rank, n_svd;   /* d_ffn = n_svd (SVD channels, first) + RTN channels            */

@@ -59,7 +59,7 @@ class AttnDecodeArgs(C.Structure):
         ("out_latent", C.c_void_p), ("out_latent_stride_b", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status_word", C.c_void_p), ("ev_stream_begin", C.c_void_p), ("ev_stream_end", C.c_void_p),
-        ("cache_layout", C.c_int32),
+        ("cache_layout", C.c_int32), ("req_to_token_rows", C.c_int32),
     ]
 
 
@@ -179,6 +179,8 @@ SIGNATURES = {
     "lsvd_status_string": (C.c_char_p, [C.c_int]),
     "lsvd_last_cuda_error": (C.c_int, []),
     "lsvd_cache_append": (C.c_int, [C.POINTER(AppendArgs), C.c_void_p]),
+    "lsvd_decode_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                      C.c_int32, C.c_void_p, C.c_void_p]),
     "lsvd_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int32] * 5),
     "lsvd_attn_decode": (C.c_int, [C.POINTER(AttnDecodeArgs), C.c_void_p]),
     "lsvd_attn_decode_static_scratch_bytes": (C.c_size_t, []),

@@ -248,6 +248,17 @@ class InferState:
         self.mem_index = self.req_manager.req_to_token_indexs[self.b_req_idx.long(), last].contiguous()
 
 
+def decode_advance(infer_state: "InferState", base_len: int = 0, period: int = 0, status_word=None) -> None:
+    """One token further, on the device: ``b_seq_len += 1`` and ``mem_index`` = the slot of the new last position (read
+    from ``req_to_token``).  ``max_len_in_batch`` of the state is the bound the lengths may reach.  With ``period`` a
+    request that reaches ``base_len + period`` starts over at ``base_len``."""
+    r2t = infer_state.req_manager.req_to_token_indexs
+    _lib.check(_lib.load().lsvd_decode_advance(
+        infer_state.b_seq_len.data_ptr(), infer_state.mem_index.data_ptr(), r2t.data_ptr(), r2t.stride(0),
+        infer_state.b_req_idx.data_ptr(), infer_state.batch_size, base_len, period, int(infer_state.max_len_in_batch),
+        status_word.data_ptr() if status_word is not None else None, torch.cuda.current_stream(r2t.device).cuda_stream))
+
+
 def attn_decode_workspace_bytes(batch: int, layout: LatentCacheLayout, max_len_in_batch: int) -> int:
     return int(_lib.load().lsvd_attn_decode_workspace_bytes(batch, layout.num_heads, layout.sum_k, layout.sum_v,
                                                             max_len_in_batch))
@@ -327,6 +338,7 @@ def token_decode_attention_int8_latent_absorb(
     if up_v is not None:
         a.up_v, a.up_v_row_stride = up_v.data_ptr(), up_v.stride(0)
     a.req_to_token, a.req_to_token_stride = r2t.data_ptr(), r2t.stride(0)
+    a.req_to_token_rows = r2t.shape[0]
     a.b_req_idx, a.b_seq_len = infer_state.b_req_idx.data_ptr(), infer_state.b_seq_len.data_ptr()
     if out is not None:
         a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)

@@ -62,6 +62,7 @@ struct StreamParams {
   int32_t batch, num_heads, num_slots, sum_rk;
   int32_t items_per_request, acc_per_request, total_items;
   int32_t head_major;        // cache layout: 0 = [slot][sum r] + scales [slot][H]; 1 = [head][slot][r_h] + scales [H][slot]
+  int32_t max_len, r2t_rows; // bound of b_seq_len the items were cut for; rows of req_to_token (0: not checked)
   HeadPlan head[LSVD_MAX_HEADS];
 };
 
@@ -228,7 +229,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
   const __half* ksc = p.head_major ? p.scale_k + static_cast<int64_t>(h) * p.num_slots : p.scale_k + h;
   const __half* vsc = p.head_major ? p.scale_v + static_cast<int64_t>(h) * p.num_slots : p.scale_v + h;
   const int64_t ks_stride = p.head_major ? 1 : p.scale_k_row_stride, vs_stride = p.head_major ? 1 : p.scale_v_row_stride;
-  const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
+  const int32_t* r2t = p.req_to_token + static_cast<int64_t>(__ldg(p.b_req_idx + b)) * p.req_to_token_stride;
   const float step = p.qstep[b * p.num_heads + h];
   // row strides fit 32 bits (checked by the host): a row address is one 32 x 32 + 64-bit multiply-add
   const uint32_t kstride = p.head_major ? static_cast<uint32_t>(nk * 16) : static_cast<uint32_t>(p.cache_k_row_stride);
@@ -451,7 +452,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const 
     const int h = __reduce_add_sync(0xffffffffu, below) - 1;
     const HeadPlan& H = p.head[h];
     const int k = rem - H.part_off;
-    const int len = p.b_seq_len[b];
+    // a length beyond the bound the items were cut for, or a request row outside the table, is reported, not followed
+    int len = p.b_seq_len[b];
+    if (len > p.max_len) {
+      if (lane == 0) report_status(p.status_word, LSVD_ERR_BOUNDS);
+      len = p.max_len;
+    }
+    const int req = p.b_req_idx[b];
+    if (p.r2t_rows > 0 && (req < 0 || req >= p.r2t_rows)) {
+      if (lane == 0) report_status(p.status_word, LSVD_ERR_BOUNDS);
+      continue;
+    }
     const int ntiles = tiles_of(len);
     const int t0 = k * H.chunk_tiles;
     const int t1 = min(ntiles, t0 + H.chunk_tiles);
@@ -757,6 +768,8 @@ int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
   sp.acc_per_request = hp.acc_per_request;
   sp.total_items = static_cast<int32_t>(hp.total_items);
   sp.head_major = a->cache_layout == LSVD_CACHE_HEAD_MAJOR ? 1 : 0;
+  sp.max_len = a->max_len_in_batch;
+  sp.r2t_rows = a->req_to_token_rows > 0 ? a->req_to_token_rows : 0;
   for (int h = 0; h < a->num_heads; ++h) sp.head[h] = hp.head[h];
   if (a->ev_stream_begin) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_begin), st));
   LSVD_CUDA_TRY(launch_chained(latent_stream_kernel, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
@@ -859,7 +872,8 @@ static void* g_static_scratch_addr[kMaxDevices] = {nullptr};     // device addre
 static std::mutex g_static_scratch_mu;
 
 // The array's name is only a host-side handle here; the device address has to be asked for, once per
-// device, with that device current.
+// device, with that device current.  The address is kept for the life of the process: a cudaDeviceReset (or any
+// other re-creation of the device's primary context) while the library is loaded is not supported.
 static int static_scratch_address(void** out) {
   int dev = 0;
   LSVD_CUDA_TRY(cudaGetDevice(&dev));

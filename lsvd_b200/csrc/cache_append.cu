@@ -217,7 +217,34 @@ static int fill_side(AppendSide& dst, const lsvd_append_tensor& src, int num_hea
   return LSVD_OK;
 }
 
+// One decode step further: every request is one token longer and its new token's slot is looked up.
+__global__ void decode_advance_kernel(int32_t* b_seq_len, int32_t* mem_index, const int32_t* req_to_token, int64_t r2t_stride,
+                                      const int32_t* b_req_idx, int32_t batch, int32_t base_len, int32_t period, int32_t max_len,
+                                      int32_t* status_word) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  int len = b_seq_len[b] + 1;
+  if (period > 0 && len >= base_len + period) len = base_len;       // start over (benchmarks that run longer than the context they reserved)
+  if (len > max_len || len < 1) {
+    report_status(status_word, LSVD_ERR_BOUNDS);
+    return;
+  }
+  b_seq_len[b] = len;
+  mem_index[b] = req_to_token[static_cast<int64_t>(b_req_idx[b]) * r2t_stride + len - 1];
+}
+
 }  // namespace lsvd
+
+extern "C" int lsvd_decode_advance(int32_t* b_seq_len, int32_t* mem_index, const int32_t* req_to_token, int64_t req_to_token_stride,
+                                   const int32_t* b_req_idx, int32_t batch, int32_t base_len, int32_t period, int32_t max_len,
+                                   int32_t* status_word, void* stream) {
+  if (b_seq_len == nullptr || mem_index == nullptr || req_to_token == nullptr || b_req_idx == nullptr || batch <= 0 || max_len < 1)
+    return LSVD_ERR_INVALID_ARG;
+  lsvd::decode_advance_kernel<<<(batch + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      b_seq_len, mem_index, req_to_token, req_to_token_stride, b_req_idx, batch, base_len, period, max_len, status_word);
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}
 
 extern "C" int lsvd_cache_append(const lsvd_append_args* a, void* stream) {
   using namespace lsvd;

@@ -152,6 +152,21 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                : "memory");
 }
 
+// Named barrier `id` of `count` threads that also ORs a flag over them: every participant gets the same answer, so a
+// decision to stop (a bounded wait that gave up somewhere) is taken by all of them or by none -- nobody is left
+// waiting alone at the next barrier.
+__device__ __forceinline__ bool named_barrier_or(int id, int count, bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+      "barrier.red.or.pred q, %2, %3, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(flag ? 1u : 0u), "r"(id), "r"(count)
+      : "memory");
+  return r != 0u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -106,13 +106,13 @@ w8a8_gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0;
 
+    bool bad = false;
     for (int ks = 0; ks < ksteps; ++ks, ++it) {
       const int s = it % stages;
-      // Only the barrier decides: a stage is filled for all consumer warps or for none, so after a timeout
-      // none of them is left waiting at the named barrier below.
       if (!mbar_wait_bounded(&full_bar[s], (it / stages) & 1)) {
         report_status(p.status_word, LSVD_ERR_TIMEOUT);
-        return;
+        bad = true;              // leave the K loop, but still attend the named barrier below
+        break;
       }
       const uint8_t* st = ring + static_cast<size_t>(s) * L::kStage;
       const uint8_t* wc = st + warp * (kTgRows * 128);                      // this warp's 128-byte chunk: [16 rows][128]
@@ -154,7 +154,8 @@ w8a8_gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
       for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) mine[((mtx * NT + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
-    consumer_sync();
+    // the barrier ORs "a wait gave up" over the consumer warps: they all stop here or none does
+    if (named_barrier_or(1, kTgConsumers * 32, bad)) return;
     const int row0 = tile * kTgRows;
     // element e of a matrix: (j, c, lane) -> row = g + 8 (c >> 1), token = 8 j + 2 t + (c & 1)
     for (int e = threadIdx.x; e < NT * 4 * 32; e += kTgConsumers * 32) {

@@ -213,14 +213,17 @@ i8gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
         cs[i] = v;
       }
-      // Only the barrier decides whether to go on: it completes for all epilogue warps or for none, so none of them
-      // is left alone at the named barrier below.
+      // Every epilogue warp attends the named barrier whatever its own wait returned; the barrier also ORs "a wait gave
+      // up or the block is aborting" over the eight warps, so they go on together or leave together (and an aborted
+      // tile's partial accumulator is never stored).
+      bool bad = false;
       if (!mbar_wait_bounded(&acc_full[buf], (li >> 1) & 1)) {
         report_status(p.status_word, LSVD_ERR_TIMEOUT);
         *abort_flag = 1;
-        break;
+        bad = true;
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");   // the staged scales are visible; tile li - 2's readers are done
+      // the staged scales are visible; tile li - 2's readers are done
+      if (named_barrier_or(1, kEpiWarps * 32, bad || *abort_flag != 0)) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < p.m;

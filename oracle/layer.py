@@ -26,10 +26,13 @@ def linear_a8w8(x16, w_q, w_s, residual=None):
 
 
 def decoder_layer(x16, w, ffn_w, k_off, v_off, num_heads, head_dim, rank_q, cache_k, scale_k, cache_v, scale_v,
-                  req_to_token, b_req_idx, b_seq_len, mem_index):
-    """Returns (out fp16, stages).  Mutates the cache like the reference block does."""
+                  req_to_token, b_req_idx, b_seq_len, mem_index, xn=None, y1=None):
+    """Returns (out fp16, stages).  Mutates the cache like the reference block does.  ``xn`` / ``y1`` replace the
+    normalised input / the attention block's output by values computed elsewhere, so that the stages behind them can be
+    compared bit for bit (an fp32 mean of 4096 squares depends on the order of the additions)."""
     Rq = num_heads * rank_q
-    xn = rms_norm(x16, w["ln1"], 1e-5)
+    xn_own = rms_norm(x16, w["ln1"], 1e-5)
+    xn = xn_own if xn is None else xn
     lat = linear_a8w8(xn, w["W_lat_q"], w["W_lat_s"])
     attention.cache_append(lat[:, Rq:Rq + k_off[-1]].contiguous(), mem_index, k_off, cache_k, scale_k)
     attention.cache_append(lat[:, Rq + k_off[-1]:].contiguous(), mem_index, v_off, cache_v, scale_v)
@@ -39,11 +42,12 @@ def decoder_layer(x16, w, ffn_w, k_off, v_off, num_heads, head_dim, rank_q, cach
                                        req_to_token, b_req_idx, b_seq_len, sm_scale=1.0 / math.sqrt(head_dim),
                                        dtype=torch.float32)
     o16 = o_lat.half()
-    y1 = linear_a8w8(o16, w["W_uvo_q"], w["W_uvo_s"], residual=xn)
+    y1_own = linear_a8w8(o16, w["W_uvo_q"], w["W_uvo_s"], residual=xn)
+    y1 = y1_own if y1 is None else y1
     x2 = rms_norm(y1, w["ln2"], 1e-6)
     st = ffn.hybrid_ffn_stages(x2, ffn_w)
     out = (st["out"].float() + y1.float()).half()
-    return out, dict(xn=xn, lat=lat, o_lat=o16, y1=y1, out=out)
+    return out, dict(xn=xn_own, lat=lat, o_lat=o16, y1=y1_own, out=out)
 
 
 def decoder_layer_tp_rank(x16, lw, fw, info, head_dim, rank_q, world, cache_k, scale_k, cache_v, scale_v,

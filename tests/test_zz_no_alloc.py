@@ -70,6 +70,8 @@ def test_static_scratch_entry_matches_the_ordinary_one_twice_in_a_row():
         assert torch.isfinite(out.float()).all()
         assert rel_to_norm(out.float(), ref.float()) < TIGHT
         assert torch.equal(out, ref)             # the two entry points run the same kernels on the same items
+        o_ref, _ = U.run_oracle(c)               # and both stand against the CPU oracle
+        assert rel_to_norm(out.float(), o_ref.float()) < TIGHT
 
 
 def test_static_scratch_entry_refuses_a_problem_that_does_not_fit():
