@@ -3,18 +3,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-A "step" is one decode step of one decoder layer's hot path over one batch of synthetic
-requests.  Default workload `c3_layer` (BASELINE config 3 shape): append this step's K/V
-latents to the int8 latent cache, int8 latent flash-decoding attention over the whole
-context (batch 16, context 4096, ragged per-head ranks, mean 64), then the hybrid SVD/RTN
-FFN (4096/11008) on the 16 tokens.  Metric: decode tokens/s of that layer step.  Other
-workloads: `c2_ffn` (--tokens 1/8/64), `c3_attention`, `c1_attention`.
+A "step" is one decode step of one decoder layer over one batch of synthetic requests.
 
-N > 1 (launched by torch.distributed.run): requests are independent, so each rank serves
-its own batch of the same size with no data-path collective (weak scaling).
+N = 1, default workload `c3_layer` (BASELINE config 3): the full LSVD W8A8 decoder layer at the LLaVA-Next-7B shape
+(RMSNorm + A8, int8 latent projection, cache append, int8 latent flash-decoding attention over the whole context --
+batch 16, context 4096 growing by one token per step for 128 steps, ragged per-head ranks mean 64 -- fused output
+projection, hybrid SVD/RTN FFN 4096/11008).  Metric: decode tokens/s of that layer step.
 
---impl reference times the CPU restatement of the reference's algorithm (the oracle, a
-port: the reference has no CPU implementation of latent attention) on the host cores.
+N > 1 (launched by torch.distributed.run), default workload `c4_layer_tp` (BASELINE config 4): one decoder layer of the
+13B shape (hidden 5120, 40 heads, intermediate 13824, batch 64, context 8192) TENSOR-PARALLEL over the N ranks -- heads
+and FFN channels sharded, one NCCL all-reduce per block plus the all-gather of the FFN hidden vector -- strong scaling:
+the same total work at every N.  `--replicas` runs N independent copies of the 1-GPU workload instead.
+
+Other workloads: `c2_ffn` (--tokens 1/8/64), `c3_attention`, `c1_attention`, `c5_prefill_ffn`, ... (see WORKLOADS).
+Every timed leg is repeated (each repeat = exactly --steps steps between a barrier + synchronize on both sides, maximum
+over ranks); `ms_per_step` is the median repeat, the spread is reported in `parts`.
+
+--impl reference times the CPU restatement of the reference's algorithm (the oracle, a port: the reference has no CPU
+implementation of latent attention) on the host cores.
 """
 from __future__ import annotations
 
@@ -65,6 +71,16 @@ WORKLOADS = {
                              "intermediate 13824 = 108 x 128) tensor-parallel over the ranks: batch 64, context 8192, "
                              "ragged K/V ranks (mean 64); heads and FFN channels sharded, NCCL all-reduce per block and "
                              "an all-gather of the FFN hidden vector; needs --gpus >= 2"),
+    "c4_stack": dict(batch=64, heads=40, head_dim=128, context=8192, aux="stack_tp", hidden=5120, d_ffn=13824, layers=40,
+                     desc="BASELINE config 4: the LLaVA-Next-13B-shape LSVD layer stack (hidden 5120, 40 heads x 128, "
+                          "intermediate 13824, 40 layers), random init with ragged K/V ranks (mean 64), batch 64, context 8192, "
+                          "int8 latent cache; heads and FFN channels tensor-parallel over the ranks with an NCCL all-reduce per "
+                          "block; one decode step of the whole stack per step; needs --gpus >= 2 (the cache alone is 107 GB)"),
+    "c5_e2e": dict(batch=8, heads=32, head_dim=128, context=4096, aux="stack_e2e", hidden=4096, d_ffn=11008, layers=32,
+                   decode_steps=256,
+                   desc="BASELINE config 5: a 32-layer LLaVA-Next-7B-shape LSVD W8A8 language-model stack, random init: prefill "
+                        "of 8 x 4096 tokens (latent-projection, gate / up / down GEMMs on tcgen05 kind::i8, latent cache written "
+                        "by the prefill), then 256 decode steps; one step = one whole prefill + decode run"),
     "fig5_mixffn": dict(batch=32, context=0, aux="mixffn", hidden=4096, d_ffn=14336,
                         desc="the reference's mixffn W8A8 FFN (its own structure and fp32 conventions) at the shape of "
                              "its layer benchmark: hidden 4096, intermediate 14336, 32 tokens, svd_ratio 0.5, "
@@ -135,6 +151,35 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def timed_repeats(loop, steps, barrier, world, dev, min_seconds=0.5, min_repeats=5, max_repeats=400):
+    """Milliseconds of repeated runs of exactly `steps` steps (`loop(steps)` enqueues them): every repeat sits between a
+    barrier + synchronize on both sides and is timed by CUDA events; with several ranks a repeat counts as its slowest
+    rank.  Repeats go on until they add up to `min_seconds` (the ranks decide on the reduced times, hence together)."""
+    times = []
+    while True:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        loop(steps)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times.append(t.item())
+        if (len(times) >= min_repeats and sum(times) >= min_seconds * 1e3) or len(times) >= max_repeats:
+            return times
+
+
+def spread(times, steps):
+    """p50 / p20 / p80 of the repeats, per step, in microseconds (the reference's harness reports the same three,
+    kernels/layer_bench/ffn_kernel/utils.py:709-712)."""
+    s = sorted(times)
+    pick = lambda q: s[min(len(s) - 1, int(q * len(s)))] / steps * 1e3
+    return {"repeats": len(s), "p50_us": pick(0.5), "p20_us": pick(0.2), "p80_us": pick(0.8)}
+
+
 def make_workload(w, device, seed):
     """Synthetic cache, weights and per-step inputs, resident on `device`; the cache is built by the library's
     own append kernel from fp16 N(0,1) latents (bit-identical to the reference's PyTorch quantiser)."""
@@ -142,9 +187,10 @@ def make_workload(w, device, seed):
     B, H, D, L = w["batch"], w["heads"], w["head_dim"], w["context"]
     kr = synth.ragged_ranks(H, 64, seed=0) if w["ragged"] else [64] * H
     vr = synth.ragged_ranks(H, 64, seed=1) if w["ragged"] else [64] * H
-    lay = LatentCacheLayout(kr, vr, head_major=w.get("cache_layout", "head") == "head")
+    lay = LatentCacheLayout(kr, vr, head_major=w.get("cache_layout", "slot") == "head")
     seq = L + 1                      # context plus the slot of the decoding token, as the reference's benchmark
-    n_slots = B * seq
+    grow = DECODE_TOKENS if w.get("full") else 0     # slots reserved for the tokens the decode loop appends
+    n_slots = B * (seq + grow)
     g = torch.Generator(device=device).manual_seed(seed)
     ck, sk, cv, sv = lay.alloc(n_slots, device)
     chunk = 8192
@@ -156,20 +202,23 @@ def make_workload(w, device, seed):
         cache_append(lay, lk, lv, dest, ck, sk, cv, sv)
     up_k = (torch.randn(lay.sum_k, D, generator=g, device=device) / 8).half()
     up_v = (torch.randn(lay.sum_v, D, generator=g, device=device) / 8).half()
-    st = InferState(B, seq, [seq] * B, device=device)
+    st = InferState(B, seq + grow, [seq] * B, device=device)
     return dict(layout=lay, ck=ck, cv=cv, sk=sk, sv=sv, up_k=up_k, up_v=up_v, state=st, B=B, H=H, D=D, L=L, seq=seq,
-                n_slots=n_slots)
+                n_slots=n_slots, grow=grow)
+
+
+DECODE_TOKENS = int(os.environ.get("LSVD_BENCH_DECODE_TOKENS", "128"))          # BASELINE config 3: "decode 128 tokens"
 
 
 def algorithmic_bytes(wl):
     """Bytes one launch of the streaming kernel must move: the int8 K and V latents of every cached token, their
-    fp16 scales, the slot indices, the absorbed query limbs and the partial results."""
+    fp16 scales and the slot indices.  With a growing context: the mean over the decode loop's lengths."""
     lay, B, H = wl["layout"], wl["B"], wl["H"]
-    tokens = B * wl["seq"]
+    tokens = B * (wl["seq"] + (wl["grow"] - 1) / 2.0) if wl.get("grow") else B * wl["seq"]
     cache = tokens * (lay.sum_k + lay.sum_v)
     scales = tokens * H * 2 * 2
     slots = tokens * 4
-    return cache + scales + slots
+    return int(cache + scales + slots)
 
 
 FFN_SHAPE = dict(d_in=4096, d_ffn=11008, rank=512, n_svd=5504, K=172)
@@ -192,7 +241,7 @@ def make_ffn(device, seed, copies, input_had=True):
 
 def run_ours(args, rank, world, local):
     from lsvd_b200 import _lib, cache_append, token_decode_attention_int8_latent_absorb
-    from lsvd_b200.attention import attn_decode_workspace_bytes
+    from lsvd_b200.attention import attn_decode_workspace_bytes, decode_advance
     _lib.load()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -219,7 +268,7 @@ def run_ours(args, rank, world, local):
         ws = torch.empty(attn_decode_workspace_bytes(B, lay, wl["seq"]), dtype=torch.uint8, device=dev)
         attn_out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
         shapes = [(B, H * D)] if full else [(B, H, D), (B, lay.sum_k), (B, lay.sum_v)]
-        launches += 8 if full else 4
+        launches += 9 if full else 4
     else:
         shapes = [(B, FFN_SHAPE["d_in"])]
     if has_ffn:
@@ -263,7 +312,10 @@ def run_ours(args, rank, world, local):
         """One decode step of the layer's hot path.  The FFN takes the attention output's heads flattened
         (hidden = heads x head_dim) as its input: the data dependency of the layer without the projections."""
         if full:
+            # the layer step, then one token further on the device: lengths + 1, the new token's slot looked up; after
+            # DECODE_TOKENS steps the requests start over at the initial context (the slots reserved for them are reused)
             layer(inputs[0], wl["ck"], wl["sk"], wl["cv"], wl["sv"], st, out=ffn_out, timing_events=ev)
+            decode_advance(st, base_len=wl["seq"], period=DECODE_TOKENS, status_word=status)
             return
         if has_attn:
             q, lk, lv = inputs
@@ -313,26 +365,21 @@ def run_ours(args, rank, world, local):
         sampler.start()
         time.sleep(0.3)
     # ---- device-resident leg (value): inputs already in HBM, graph replays ----
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        load_inputs(i, False)                       # device-to-device refresh of this step's inputs (a few hundred KB)
-        graphs[i % len(graphs)].replay()
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
+    def loop_dev(n):
+        for i in range(n):
+            load_inputs(i, False)                   # device-to-device refresh of this step's inputs (a few hundred KB)
+            graphs[i % len(graphs)].replay()
+
     # ---- end-to-end leg: this step's inputs from pinned host memory, the result read back, every step ----
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    f0.record()
-    for i in range(args.steps):
-        load_inputs(i, True)
-        graphs[i % len(graphs)].replay()
-        host_out.copy_(result, non_blocking=True)
-    f1.record()
-    barrier()
-    ms_e2e = f0.elapsed_time(f1)
+    def loop_e2e(n):
+        for i in range(n):
+            load_inputs(i, True)
+            graphs[i % len(graphs)].replay()
+            host_out.copy_(result, non_blocking=True)
+
+    t_dev = timed_repeats(loop_dev, args.steps, barrier, world, dev)
+    t_e2e = timed_repeats(loop_e2e, args.steps, barrier, world, dev)
+    ms_total, ms_e2e = statistics.median(t_dev), statistics.median(t_e2e)
     # ---- the dominant kernel on its own, timed by event pairs on the launching stream (eager steps) ----
     kernel_ms = []
     if has_attn:
@@ -368,11 +415,6 @@ def run_ours(args, rank, world, local):
     if status.item() != 0:
         raise RuntimeError(f"device status word = {status.item()}")
 
-    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        import torch.distributed as dist
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = t.tolist()
     if rank != 0:
         return None
     ms_step = ms_total / args.steps
@@ -405,10 +447,11 @@ def run_ours(args, rank, world, local):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax, fp16 out",
         "data": "synthetic",
-        "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B, "layers": 1, "step": " + ".join(what),
-                   "launch": "CUDA graph replay of the step",
-                   "l2": "inputs larger than L2: every step streams %.0f MB of cache/weights%s"
-                         % (step_bytes / 1e6, "" if has_attn else " (three weight copies cycled, 300 MB)")},
+        "config": bench_config(args, w, B, world),
+        "config_detail": {"step": " + ".join(what), "launch": "CUDA graph replay of the step",
+                          "cache_layout": args.cache_layout if has_attn else None,
+                          "l2": "inputs larger than L2: every step streams %.0f MB of cache/weights%s"
+                                % (step_bytes / 1e6, "" if has_attn else " (three weight copies cycled, 300 MB)")},
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * args.steps,
@@ -419,7 +462,8 @@ def run_ours(args, rank, world, local):
                      "traffic": 284952832 if (has_attn and w["batch"] == 16 and w["context"] == 4096 and w["ragged"]) else None,
                      "algorithmic_bytes_per_launch": abytes, "kernel_us": k_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
         "parts": {"step_us": ms_step * 1e3, "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
-                  "step_algorithmic_bytes": step_bytes, "dominant_kernel_us": k_ms * 1e3},
+                  "step_algorithmic_bytes": step_bytes, "dominant_kernel_us": k_ms * 1e3,
+                  "value_leg": spread(t_dev, args.steps), "e2e_leg": spread(t_e2e, args.steps)},
         "clocks": clocks,
     }
     return line
@@ -620,25 +664,20 @@ def run_aux(args, rank, world, local):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    e0, e1 = ev(), ev()
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        feed(i, False)
-        step()
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    f0, f1 = ev(), ev()
-    barrier()
-    f0.record()
-    for i in range(args.steps):
-        feed(i, True)
-        step()
-        host_out.copy_(out, non_blocking=True)
-    f1.record()
-    barrier()
-    ms_e2e = f0.elapsed_time(f1)
+    def loop_dev(n):
+        for i in range(n):
+            feed(i, False)
+            step()
+
+    def loop_e2e(n):
+        for i in range(n):
+            feed(i, True)
+            step()
+            host_out.copy_(out, non_blocking=True)
+
+    t_dev = timed_repeats(loop_dev, args.steps, barrier, world, dev)
+    t_e2e = timed_repeats(loop_e2e, args.steps, barrier, world, dev)
+    ms_total, ms_e2e = statistics.median(t_dev), statistics.median(t_e2e)
     # the step alone (no input refresh), for the roofline figure
     k0, k1 = ev(), ev()
     torch.cuda.synchronize()
@@ -651,11 +690,6 @@ def run_aux(args, rank, world, local):
     clocks = sampler.stop() if rank == 0 else None
     if status.item() != 0:
         raise RuntimeError(f"device status word = {status.item()}")
-    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        import torch.distributed as dist
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = t.tolist()
     if rank != 0:
         return None
     ms_step = ms_total / args.steps
@@ -664,8 +698,8 @@ def run_aux(args, rank, world, local):
         "metric": metric, "value": units * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp16 out", "data": "synthetic",
-        "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": w["batch"], "layers": 1, "step": what,
-                   "launch": "CUDA graph replay of the step" if w["aux"] in ("mixffn", "block") else "eager launches on one stream", "l2": l2},
+        "config": bench_config(args, w, w["batch"], world),
+        "config_detail": {"step": what, "launch": "CUDA graph replay of the step" if w["aux"] in ("mixffn", "block") else "eager launches on one stream", "l2": l2},
         "e2e": {"value": units * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * args.steps,
@@ -673,6 +707,7 @@ def run_aux(args, rank, world, local):
                      "unit": roof["unit"], "frac": achieved / roof["peak"], "of": "measured" if peaks else "fallback",
                      "traffic": None, "work_per_step": roof["work"], "step_us": k_ms * 1e3,
                      **({"peak_note": roof["peak_note"]} if "peak_note" in roof else {})},
+        "parts": {"value_leg": spread(t_dev, args.steps), "e2e_leg": spread(t_e2e, args.steps)},
         "clocks": clocks,
     }
     return line
@@ -686,12 +721,16 @@ def run_tp(args, rank, world, local):
     from lsvd_b200.layer import TPDecoderLayer, make_layer_weights
     from lsvd_b200.parallel import shard_layer
     _lib.load()
-    if world < 2:
-        raise SystemExit("c4_layer_tp shards one layer over the ranks: launch it with --gpus 2, 4 or 8 under torchrun")
     w = WORKLOADS[args.workload]
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    if world == 1 and "RANK" not in os.environ:
+        # the unsharded layer on one GPU (the first point of the strong-scaling curve): a process group of one
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(29500 + os.getpid() % 2000))
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    else:
+        dist.init_process_group("nccl", device_id=dev)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -704,30 +743,35 @@ def run_tp(args, rank, world, local):
     lw, fw, info = shard_layer(lw_full, fw_full, kr, vr, rq, world, rank)
     del lw_full, fw_full
     to = lambda d: {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
-    layer = TPDecoderLayer(to(lw), to(fw), info, D, rq, world)
+    head_major = args.cache_layout == "head"
+    layer = TPDecoderLayer(to(lw), to(fw), info, D, rq, world, head_major=head_major)
+    lay = layer.layout
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     n_slots = B * (L + 1)
-    rk_loc, rv_loc, h_loc = sum(info["k_ranks"]), sum(info["v_ranks"]), len(info["k_ranks"])
-    ck = torch.randint(-128, 128, (n_slots, rk_loc), dtype=torch.int8, device=dev, generator=g)
-    cv = torch.randint(-128, 128, (n_slots, rv_loc), dtype=torch.int8, device=dev, generator=g)
-    sk = (torch.rand(n_slots, h_loc, device=dev, generator=g) * 0.02 + 0.01).half()
-    sv = (torch.rand(n_slots, h_loc, device=dev, generator=g) * 0.02 + 0.01).half()
+    h_loc = lay.num_heads
+    ck, sk, cv, sv = lay.alloc(n_slots, dev)
+    for t in (ck, cv):                                  # random codes, chunked: torch's RNG makes int64 on the way
+        flat = t.view(-1)
+        for o in range(0, flat.numel(), 1 << 28):
+            n = min(1 << 28, flat.numel() - o)
+            flat[o:o + n] = torch.randint(-128, 128, (n,), dtype=torch.int8, device=dev, generator=g)
+    sk.copy_((torch.rand(sk.shape, device=dev, generator=g) * 0.02 + 0.01).half())
+    sv.copy_((torch.rand(sv.shape, device=dev, generator=g) * 0.02 + 0.01).half())
     st = InferState(B, L + 1, [L + 1] * B, device=dev)
     gx = torch.Generator().manual_seed(9)                                              # replicated hidden states
     xs_host = [torch.randn(B, hid, generator=gx).half().pin_memory() for _ in range(4)]
     xs = [t.to(dev) for t in xs_host]
     x_in = torch.empty_like(xs[0])
     host_out = torch.empty(B, hid, dtype=torch.float16).pin_memory()
-    ev = lambda: torch.cuda.Event(enable_timing=True)
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
-    def loop(n, host):
+    def loop(n, host, evs=None):
         for i in range(n):
             x_in.copy_((xs_host if host else xs)[i % 4], non_blocking=True)
-            y = layer(x_in, ck, sk, cv, sv, st)
+            y = layer(x_in, ck, sk, cv, sv, st, timing_events=None if evs is None else evs[i])
             if host:
                 host_out.copy_(y, non_blocking=True)
     loop(max(args.warmup, 3), False)
@@ -735,42 +779,231 @@ def run_tp(args, rank, world, local):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    times = []
-    for host in (False, True):
-        e0, e1 = ev(), ev()
-        barrier()
-        e0.record()
-        loop(args.steps, host)
-        e1.record()
-        barrier()
-        times.append(e0.elapsed_time(e1))
+    t_dev = timed_repeats(lambda n: loop(n, False), args.steps, barrier, world, dev)
+    t_e2e = timed_repeats(lambda n: loop(n, True), args.steps, barrier, world, dev)
+    ms_total, ms_e2e = statistics.median(t_dev), statistics.median(t_e2e)
+    # the dominant kernel of every rank (its share of the cache stream), by event pairs around that launch
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a0, a1 in kev:
+        a0.record()
+        a1.record()
+    barrier()
+    loop(args.steps, False, kev)
+    barrier()
+    k_ms = statistics.mean(a0.elapsed_time(a1) for a0, a1 in kev)
+    kt = torch.tensor([k_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(kt, op=dist.ReduceOp.MAX)
+    k_ms = kt.item()
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor(times, dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = t.tolist()
     local_bytes = ck.numel() + cv.numel() + (sk.numel() + sv.numel()) * 2 + sum(
         v.numel() for v in list(lw.values()) + list(fw.values()) if isinstance(v, torch.Tensor) and v.dtype == torch.int8)
+    stream_bytes = n_slots * (lay.sum_k + lay.sum_v + 4 * h_loc + 4)
     dist.destroy_process_group()
     if rank != 0:
         return None
     ms_step = ms_total / args.steps
     peak = float(peaks.get("hbm_gbs", 6650.0))
-    achieved = local_bytes / (ms_step * 1e-3) / 1e9
+    achieved = stream_bytes / (k_ms * 1e-3) / 1e9
     return {
         "metric": "decode_tokens_per_s", "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax, fp16 out", "data": "synthetic",
-        "config": {"workload": args.workload, "what": w["desc"], "global_batch": B, "layers": 1, "parallelism": f"tp{world}",
-                   "launch": "eager launches, NCCL collectives on the same stream",
-                   "l2": "each rank streams %.0f MB of cache and weights per step" % (local_bytes / 1e6)},
+        "config": bench_config(args, w, B, world),
+        "config_detail": {"step": "RMSNorm + A8, int8 latent projection, cache append, int8 latent decode attention on the rank's "
+                                  "heads, row-parallel output projection + all-reduce, column-parallel hybrid FFN gate/up, "
+                                  "all-gather of the hidden vector, Hadamard 128 x 108 + A8, row-parallel int32 down projection + "
+                                  "all-reduce",
+                          "launch": "eager launches (about 20 host calls per step), NCCL collectives on the same stream",
+                          "cache_layout": args.cache_layout,
+                          "l2": "each rank streams %.0f MB of cache and weights per step" % (local_bytes / 1e6)},
         "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": x_in.numel() * 2,
                 "d2h_bytes_per_step": host_out.numel() * 2},
-        "gpu_launches": 17 * args.steps,
-        "roofline": {"kernel": "whole tensor-parallel layer step, per GPU (17 library launches + 3 NCCL collectives)",
-                     "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "of": "measured" if peaks else "fallback", "traffic": None, "bytes_per_gpu_per_step": local_bytes},
+        "gpu_launches": 19 * args.steps,
+        "roofline": {"kernel": "latent_stream_kernel (slowest rank's share of the cache)", "bound": "hbm", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "of": "measured" if peaks else "fallback",
+                     "traffic": None, "algorithmic_bytes_per_launch": stream_bytes, "kernel_us": k_ms * 1e3},
+        "parts": {"step_us": ms_step * 1e3, "bytes_per_gpu_per_step": local_bytes,
+                  "step_hbm_gbs_per_gpu": local_bytes / (ms_step * 1e-3) / 1e9,
+                  "value_leg": spread(t_dev, args.steps), "e2e_leg": spread(t_e2e, args.steps)},
         "clocks": clocks,
     }
+
+
+def bench_config(args, w, batch, world):
+    """The `config` object of a line: the same object from both arms (ours / reference) of a workload at a given N."""
+    tp = w.get("aux") in ("tp", "stack_tp")
+    return {"workload": args.workload, "what": w["desc"], "layers": w.get("layers", 1),
+            ("global_batch" if tp else "batch_per_gpu"): batch,
+            "parallelism": f"tp{world}" if tp else ("single GPU" if world == 1 else f"{world} independent replicas")}
+
+
+def run_stack(args, rank, world, local):
+    """Whole layer stacks: config 4 (40 tensor-parallel layers, one decode step of the stack per step) and config 5
+    (32 layers on one GPU: prefill of 8 x 4096 tokens, then 256 decode steps; one run per step)."""
+    from lsvd_b200 import _lib, synth
+    from lsvd_b200.attention import InferState, decode_advance
+    from lsvd_b200.model import LSVDModel, TPModel, fill_random_cache
+    _lib.load()
+    w = WORKLOADS[args.workload]
+    tp = w["aux"] == "stack_tp"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 or tp:
+        import torch.distributed as dist
+        if tp and world < 2:
+            raise SystemExit("c4_stack needs --gpus 2, 4 or 8 under torchrun: its cache does not fit one GPU")
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    B, H, D, L, hid, dff, nl, rq = w["batch"], w["heads"], w["head_dim"], w["context"], w["hidden"], w["d_ffn"], w["layers"], 64
+    if args.layers > 0:
+        nl = args.layers
+    kr, vr = synth.ragged_ranks(H, 64, seed=0), synth.ragged_ranks(H, 64, seed=1)
+    head_major = args.cache_layout == "head"
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if tp:
+        K = 108
+        n_slots = B * (L + 1)
+        model = TPModel(nl, hid, H, D, dff, rq, kr, vr, 640, dff // 2, synth.sign_matrix(K, seed=0).float(), K, n_slots, world, rank,
+                        device=dev, seed=100, head_major=head_major, fill_cache=True)
+        st = InferState(B, L + 1, [L + 1] * B, device=dev)
+        gx = torch.Generator().manual_seed(9)
+        xs_host = [torch.randn(B, hid, generator=gx).half().pin_memory() for _ in range(4)]
+        xs = [t.to(dev) for t in xs_host]
+        x_in = torch.empty_like(xs[0])
+        host_out = torch.empty(B, hid, dtype=torch.float16).pin_memory()
+
+        def loop(n, host):
+            for i in range(n):
+                x_in.copy_((xs_host if host else xs)[i % 4], non_blocking=True)
+                y = model.decode_step(x_in, st)
+                if host:
+                    host_out.copy_(y, non_blocking=True)
+        loop(max(args.warmup, 3), False)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.3)
+        t_dev = timed_repeats(lambda n: loop(n, False), args.steps, barrier, world, dev, min_repeats=3)
+        t_e2e = timed_repeats(lambda n: loop(n, True), args.steps, barrier, world, dev, min_repeats=3)
+        ms_total, ms_e2e = statistics.median(t_dev), statistics.median(t_e2e)
+        lay = model.layout
+        per_layer_cache = n_slots * (lay.sum_k + lay.sum_v + 4 * lay.num_heads + 4)
+        local_bytes = nl * per_layer_cache + model.weight_bytes
+        units, metric = B, "decode_tokens_per_s"
+        h2d, d2h = x_in.numel() * 2, host_out.numel() * 2
+        what = "one decode step of %d tensor-parallel layers (each: about 20 host calls, 2 all-reduces, 1 all-gather)" % nl
+        roof = dict(kernel="whole stack step, per GPU", bound="hbm", peak=float(peaks.get("hbm_gbs", 6650.0)), unit="GB/s",
+                    work=local_bytes)
+        launches = 19 * nl
+        parts_extra = {"bytes_per_gpu_per_step": local_bytes}
+    else:
+        K = 172
+        steps_dec = w["decode_steps"]
+        n_slots = B * (L + steps_dec)
+        model = LSVDModel(nl, hid, H, D, dff, rq, kr, vr, 512, dff // 2, synth.sign_matrix(K, seed=0).float(), K, n_slots, device=dev,
+                          seed=200 + rank, head_major=head_major)
+        r2t = torch.arange(n_slots, dtype=torch.int32).view(B, L + steps_dec)
+        dest = torch.cat([r2t[b, :L] for b in range(B)]).contiguous().to(dev)
+        gx = torch.Generator().manual_seed(9 + rank)
+        x_host = torch.randn(B * L, hid, generator=gx).half().pin_memory()
+        x_pre_dev = x_host.to(dev)
+        x_pre = torch.empty_like(x_pre_dev)
+        xd_host = [torch.randn(B, hid, generator=gx).half().pin_memory() for _ in range(4)]
+        xd = [t.to(dev) for t in xd_host]
+        x_in = torch.empty_like(xd[0])
+        host_out = torch.empty(B, hid, dtype=torch.float16).pin_memory()
+        st = InferState(B, L + steps_dec, [L + 1] * B, device=dev, req_to_token=r2t)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        pre_ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        split = {"prefill_ms": [], "decode_ms": []}
+
+        def one_run(host, record=False):
+            x_pre.copy_(x_host if host else x_pre_dev, non_blocking=True)
+            if record:
+                pre_ev[0].record()
+            model.prefill(x_pre, dest)
+            if record:
+                pre_ev[1].record()
+            # the decode loop restarts at the prefilled length: period = decode_steps brings the state back for the next run
+            for t in range(steps_dec):
+                x_in.copy_((xd_host if host else xd)[t % 4], non_blocking=True)
+                dec_graph.replay()
+                if host:
+                    host_out.copy_(y_dec, non_blocking=True)
+            if record:
+                pre_ev[2].record()
+
+        def loop(n, host):
+            for _ in range(n):
+                one_run(host)
+        # a decode step of the whole stack (all layers + the device-side state advance) is one CUDA graph
+        model.prefill(x_pre_dev, dest)
+        dec_graph, y_dec = model.capture_decode(x_in, st, advance=dict(base_len=L + 1, period=steps_dec, status_word=status))
+        one_run(False)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.3)
+        t_dev = timed_repeats(lambda n: loop(n, False), args.steps, barrier, world, dev, min_repeats=2, min_seconds=0.1)
+        t_e2e = timed_repeats(lambda n: loop(n, True), args.steps, barrier, world, dev, min_repeats=2, min_seconds=0.1)
+        ms_total, ms_e2e = statistics.median(t_dev), statistics.median(t_e2e)
+        torch.cuda.synchronize()
+        one_run(False, record=True)
+        torch.cuda.synchronize()
+        pre_ms, dec_ms = pre_ev[0].elapsed_time(pre_ev[1]), pre_ev[1].elapsed_time(pre_ev[2])
+        if status.item() != 0:
+            raise RuntimeError(f"device status word = {status.item()}")
+        units, metric = (B * L + B * steps_dec) * world, "tokens_per_s"
+        h2d, d2h = x_pre.numel() * 2 + steps_dec * x_in.numel() * 2, steps_dec * host_out.numel() * 2
+        what = "%d layers: prefill of %d x %d tokens (tcgen05 GEMMs, cache written), then %d decode steps" % (nl, B, L, steps_dec)
+        # tensor-core work of the prefill: the int8 GEMMs of every layer (latent projection, fused output projection, FFN)
+        lat_rows = H * rq + sum(kr) + sum(vr)
+        ops = 2.0 * B * L * nl * (lat_rows * hid + hid * sum(vr) + FFN_BYTES)
+        int8_peak = 2.0 * float(peaks.get("bf16_tflops", 1590.0))
+        roof = dict(kernel="the prefill's int8 GEMMs (i8gemm_tcgen05_kernel), all layers, over the prefill's whole time", bound="tensor",
+                    peak=int8_peak, unit="TOP/s", work=ops, time_ms=pre_ms,
+                    peak_note="int8 dense rate taken as twice the measured bf16 GEMM figure (nominal: 4500 TOP/s)")
+        launches = nl * (9 + 15 * steps_dec)
+        parts_extra = {"prefill_ms": pre_ms, "decode_ms": dec_ms, "prefill_tokens_per_s": B * L / (pre_ms * 1e-3),
+                       "decode_tokens_per_s": B * steps_dec / (dec_ms * 1e-3), "decode_step_us": dec_ms / steps_dec * 1e3,
+                       "prefill_int8_frac_of_nominal_4500": ops / (pre_ms * 1e-3) / 1e12 / 4500.0}
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1 or tp:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    ms_step = ms_total / args.steps
+    t_roof = roof.get("time_ms", ms_step)
+    achieved = roof["work"] / (t_roof * 1e-3) / (1e9 if roof["bound"] == "hbm" else 1e12)
+    line = {
+        "metric": metric, "value": units / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3) if tp else 1, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax, fp16 out",
+        "data": "synthetic", "config": bench_config(args, w, B, world),
+        "config_detail": {"step": what, "layers": nl,
+                          "launch": "eager launches" if tp else "prefill: eager launches; decode: one CUDA graph per step of the stack",
+                          "cache_layout": args.cache_layout,
+                          "prefill_attention": None if tp else "none in the reference: every prefill token attends to itself only "
+                                                                  "(its own V latent); the GEMMs and the cache write are those of a real prefill"},
+        "e2e": {"value": units / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"kernel": roof["kernel"], "bound": roof["bound"], "achieved": achieved, "peak": roof["peak"], "unit": roof["unit"],
+                     "frac": achieved / roof["peak"], "of": "measured" if peaks else "fallback", "traffic": None,
+                     **({"peak_note": roof["peak_note"]} if "peak_note" in roof else {})},
+        "parts": {"step_us": ms_step * 1e3, **parts_extra, "value_leg": spread(t_dev, args.steps), "e2e_leg": spread(t_e2e, args.steps)},
+        "clocks": clocks,
+    }
+    return line
 
 
 def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
@@ -831,7 +1064,9 @@ def cpu_baseline(workload, tokens, seconds_hint=15.0, threads=None):
             break
     return {"value": bs * n / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
             "sample": f"{bs} of {B} requests/tokens of the same workload, {n} steps, torch on {threads} threads "
-                      f"(int8 products evaluated in float64 for exactness, attention in fp32; the cache is pre-quantised)"}
+                      f"(int8 products evaluated in float64 for exactness, attention in fp32; the cache is pre-quantised; "
+                      f"left out of the sample: the cache append of the step's token, the RMSNorm in front of the FFN, the "
+                      f"bookkeeping between steps; the context stays at its initial length)"}
 
 
 def cpu_baseline_aux(w, seconds_hint, threads):
@@ -866,7 +1101,7 @@ def cpu_baseline_aux(w, seconds_hint, threads):
             oattn.cache_append(zv, dest, vo, cv, sv)
         per_call = T
         sample = f"{T} of {w['batch'] * w['context']} tokens"
-    elif w["aux"] == "tp":
+    elif w["aux"] in ("tp", "stack_tp", "stack_e2e"):
         # the attention of the layer (its dominant part) for one request and a few heads; the projections and the FFN,
         # a few per cent of the CPU time at this context length, are left out
         H, D, L, R, hs = w["heads"], w["head_dim"], w["context"] + 1, 64, 4
@@ -879,8 +1114,9 @@ def cpu_baseline_aux(w, seconds_hint, threads):
         one = torch.tensor([0], dtype=torch.int32)
         fn = lambda: oattn.decode_absorb(q, ck.view(L, -1), sk, cv.view(L, -1), sv, upk, upk, offs, offs, r2t, one,
                                          torch.tensor([L], dtype=torch.int32), dtype=torch.float32)
-        per_call = hs / H
-        sample = f"attention only: 1 of {w['batch']} requests, {hs} of {H} heads, context {L}"
+        per_call = hs / H / w.get("layers", 1)
+        sample = (f"attention only: 1 of {w['batch']} requests, {hs} of {H} heads, context {L}, one layer"
+                  + (f" (scaled by the {w['layers']} layers of the stack; decode steps only)" if w.get("layers") else ""))
     elif w["aux"] == "mixffn":
         from oracle import mixffn as omix
         hid, dff, M = w["hidden"], w["d_ffn"], w["batch"]
@@ -916,11 +1152,13 @@ def run_reference(args, rank, world):
     B = args.tokens if w.get("ffn_only") else w["batch"]
     if w.get("aux") in ("prefill_ffn", "append"):
         B = w["batch"] * w["context"]
+    B_cfg = args.tokens if w.get("ffn_only") else w["batch"]            # what the other arm prints as its batch
     cb = cpu_baseline(args.workload, args.tokens, seconds_hint=max(5.0, 3.0 * args.steps))
     return {"impl": "reference", "metric": "prefill_tokens_per_s" if w.get("aux") in ("prefill_ffn", "append") else "decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * B / cb["value"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32/fp64 (CPU)", "data": "synthetic",
-            "config": {"workload": args.workload, "what": w["desc"], "batch_per_gpu": B}, "cpu_baseline": cb,
+            "higher_is_better": True, "scaling": "strong" if w.get("aux") == "tp" else "weak", "vs_baseline": None,
+            "dtype": "fp32/fp64 (CPU)", "data": "synthetic",
+            "config": bench_config(args, w, B_cfg, world), "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
@@ -930,14 +1168,20 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_layer", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="default: c3_layer on one GPU, c4_layer_tp (the tensor-parallel layer) on several")
+    ap.add_argument("--layers", type=int, default=0, help="stack workloads: run this many layers instead of the configuration's")
+    ap.add_argument("--replicas", action="store_true",
+                    help="with several GPUs: N independent copies of the 1-GPU workload instead of the tensor-parallel layer")
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step of the c2_ffn workload (1..64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cache-layout", default="head", choices=["head", "slot"],
+    ap.add_argument("--cache-layout", default="slot", choices=["head", "slot"],
                     help="latent cache stored head by head ([H][slots][r_h], the layout the streaming kernel prefers) or "
                          "slot by slot ([slots][sum r], the reference's)")
     args = ap.parse_args()
     rank, world, local = dist_env()
+    if args.workload is None:
+        args.workload = "c3_layer" if (world == 1 or args.replicas) else "c4_layer_tp"
     if args.impl == "reference":
         line = run_reference(args, rank, world)
         if line is not None:
@@ -947,6 +1191,13 @@ def main():
     if aux == "tp":
         line = run_tp(args, rank, world, local)
         if line is not None:
+            print(json.dumps(line))
+        return
+    if aux in ("stack_tp", "stack_e2e"):
+        line = run_stack(args, rank, world, local)
+        if line is not None:
+            if world == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline(args.workload, args.tokens)
             print(json.dumps(line))
         return
     line = run_aux(args, rank, world, local) if aux else run_ours(args, rank, world, local)

@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define LSVD_ABI_VERSION 2
+#define LSVD_ABI_VERSION 3
 #define LSVD_MAX_HEADS 128      /* heads per call (per GPU shard)                     */
 #define LSVD_MAX_RANK 128       /* latent entries per head; ranks are multiples of 16 */
 
@@ -248,7 +248,10 @@ int lsvd_attn_decode_rope(const lsvd_attn_rope_args* args, void* stream);
  *   sign != NULL : x <- FWHT(x * sign) / sqrt(cols)   (x @ random_hadamard_matrix, fake_quant/utils/hadamard_utils.py:99-104)
  *   fwht  != 0   : x <- FWHT(x) / sqrt(cols)          (matmul_hadU_cuda with K == 1, hadamard_utils.py:106-109)
  * then scale = absmax / 127 (1 for a zero row), q = clamp(rne(x / scale), -128, 127).  cols <= 16384; a
- * rotation needs cols to be a power of two.  Replaces ActQuantizer.find_params + quantize. */
+ * rotation needs cols to be a power of two.  Replaces ActQuantizer.find_params + quantize.
+ * There is no separate entry for the rotation alone (matmul_hadU_cuda, fake_quant/utils/hadamard_utils.py:106-113): the
+ * rotated fp16 row is the optional `x_rot` output here (K == 1), `y` of lsvd_hadamard_quant (K > 1) and `y` of
+ * lsvd_heads_hadamard_quant (across heads); the codes and scales are written as well and may be ignored. */
 typedef struct lsvd_act_quant_args {
   int32_t rows, cols;
   const void* x;                 /* device fp16 [rows, cols]                                        */
@@ -263,6 +266,13 @@ typedef struct lsvd_act_quant_args {
   const void* norm_weight;       /* device fp16 [cols] or NULL: RMSNorm(x) * weight first, fp32 statistics and fp16
                                     products as kernels/layer_bench/ffn_kernel/utils.py:560-565 (not with `sign`) */
   float norm_eps;
+  const float* x_f32;            /* optional device fp32 [rows, cols] (contiguous): the row is fp16(x_f32 + add) instead of
+                                    x -- a partial sum that came back from an all-reduce plus its residual (tensor-parallel
+                                    output projection); not with a rotation                                              */
+  const void* add;               /* optional device fp16 [rows, cols] (contiguous), with x_f32                            */
+  void* sum_out;                 /* optional device fp16 [rows, cols] (contiguous): receives fp16(x_f32 + add)            */
+  void* fake;                    /* optional device fp16 [rows, cols] (contiguous): the fake-quantised row fp16(scale * code),
+                                    what ActQuantizer.forward returns (fake_quant/utils/quant_utils.py:141-148)           */
 } lsvd_act_quant_args;
 int lsvd_act_quant(const lsvd_act_quant_args* args, void* stream);
 
@@ -345,8 +355,25 @@ typedef struct lsvd_gemv_args {
   int32_t prefetch_weights;      /* register-fed form: every block asks for its weight rows (L2 prefetch) before */
                                  /* it waits for the kernel launched before it on the stream; pays when the       */
                                  /* call follows a short kernel (measured: 126 -> 120 us for the mixffn step)      */
+  float* out_f32;                /* optional device fp32 [m, n] (single product, forms 0 and 3): (acc * a_scale) * w_scale  */
+                                 /* with no fp16 rounding -- the partial sum a row-parallel rank sends to the all-reduce  */
 } lsvd_gemv_args;
 int lsvd_w8a8_gemv(const lsvd_gemv_args* args, void* stream);
+
+/* out[m, n] = fp16(fp16((acc[m, n] * a_scale[m]) * w_scale[n]) + residual[m, n]): the epilogue of lsvd_w8a8_gemv applied to
+ * accumulators that were summed over tensor-parallel ranks first (int32, exact).  acc contiguous; residual may be NULL. */
+int lsvd_dequant_residual(const int32_t* acc, const float* a_scale, const float* w_scale, const void* residual,
+                          int64_t residual_row_stride, void* out, int64_t out_row_stride, int32_t m, int32_t n, void* stream);
+
+/* Ragged per-head up-projection of a latent, the arithmetic of SVDLinear.forward for per-head factors
+ * (fake_quant/utils/svd_utils.py:1978-2027):
+ *   y[t, h * cout + c] = fp16(sum_r A_h[c, r] * z[t, rank_off[h] + r]) (+ bias[h * cout + c], added in fp16)
+ * z fp16 [tokens, >= rank_off[num_heads]]; factors fp16: A_0, A_1, ... one after the other, A_h [cout, r_h] row-major with
+ * r_h = rank_off[h + 1] - rank_off[h] (rank_off: HOST array of num_heads + 1 ints, rank_off[0] = 0); y fp16
+ * [tokens, >= num_heads * cout]; strides in elements.  Each head reads its own r_h columns: nothing is padded to the
+ * largest rank.  fp32 accumulation. */
+int lsvd_per_head_up(const void* z, int64_t z_row_stride, const void* factors, const int32_t* rank_off, const void* bias,
+                     void* y, int64_t y_row_stride, int32_t tokens, int32_t num_heads, int32_t cout, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * The whole hybrid SVD/RTN FFN for a decode batch (1..64 tokens) in one call: the chain of lsvd_act_quant,

@@ -14,7 +14,12 @@ from .mixffn import MixedFFNGateUpDenseLatentFused, b200_mixffn
 from .ffn import (HybridFFN, quantize_weight_rtn, act_quant, hadamard_pack, hadamard_quant, heads_hadamard_quant, w8a8_gemv,
                   i8gemm)
 
-__all__ = ["LsvdError", "LatentCacheLayout", "destindex_copy_quantize_latent", "cache_append",
+from .modules import ActQuantizer, ActQuantWrapper, SVDLinear, add_actquant, find_qlayers
+from .formats import load_channel_groups, resolve_channel_group, load_qmodel, hybrid_ffn_weights, load_hybrid_ffn, int8_from_fake_quant
+
+__all__ = ["ActQuantizer", "ActQuantWrapper", "SVDLinear", "add_actquant", "find_qlayers", "load_channel_groups",
+           "resolve_channel_group", "load_qmodel", "hybrid_ffn_weights", "load_hybrid_ffn", "int8_from_fake_quant",
+           "LsvdError", "LatentCacheLayout", "destindex_copy_quantize_latent", "cache_append",
            "token_decode_attention_int8_latent_absorb", "token_decode_attention_flash_int8_latent_per_head_decoding_rope",
            "LatentDecodeAttention", "InferState", "Int8AttentionBlock", "MixedFFNGateUpDenseLatentFused", "b200_mixffn", "HybridFFN", "quantize_weight_rtn", "act_quant", "hadamard_pack",
            "hadamard_quant", "heads_hadamard_quant", "w8a8_gemv", "i8gemm"]

@@ -87,6 +87,7 @@ class ActQuantArgs(C.Structure):
         ("rows", C.c_int32), ("cols", C.c_int32), ("x", C.c_void_p), ("x_row_stride", C.c_int64),
         ("sign", C.c_void_p), ("fwht", C.c_int32), ("q", C.c_void_p), ("q_row_stride", C.c_int64),
         ("scale", C.c_void_p), ("x_rot", C.c_void_p), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float),
+        ("x_f32", C.c_void_p), ("add", C.c_void_p), ("sum_out", C.c_void_p), ("fake", C.c_void_p),
     ]
 
 
@@ -116,7 +117,7 @@ class GemvArgs(C.Structure):
         ("acc_out", C.c_void_p), ("acc2_out", C.c_void_p), ("residual", C.c_void_p), ("residual_row_stride", C.c_int64),
         ("status_word", C.c_void_p), ("form", C.c_int32),
         ("row_absmax", C.c_void_p), ("row_absmax_stride", C.c_int64), ("absmax_split", C.c_int32),
-        ("prefetch_weights", C.c_int32),
+        ("prefetch_weights", C.c_int32), ("out_f32", C.c_void_p),
     ]
 
 
@@ -197,6 +198,10 @@ SIGNATURES = {
     "lsvd_hadamard_packed_bytes": (C.c_size_t, [C.c_int32]),
     "lsvd_hadamard_pack": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),
+    "lsvd_dequant_residual": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32,
+                                        C.c_int32, C.c_void_p]),
+    "lsvd_per_head_up": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_int64,
+                                   C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "lsvd_i8gemm_prefill": (C.c_int, [C.POINTER(I8GemmArgs), C.c_void_p]),
     "lsvd_mix_rmsnorm_quant": (C.c_int, [C.POINTER(MixRmsnormQuantArgs), C.c_void_p]),
     "lsvd_mix_group_quant": (C.c_int, [C.POINTER(MixGroupQuantArgs), C.c_void_p]),

@@ -25,7 +25,7 @@ struct HostPlan {
 };
 
 struct WorkspaceLayout {
-  size_t qlimb, qstep, queue, part_ml, part_acc, total;
+  size_t qlimb, qstep, queue, san, part_ml, part_acc, total;
 };
 
 struct AttnLaunch {

@@ -62,7 +62,6 @@ struct StreamParams {
   int32_t batch, num_heads, num_slots, sum_rk;
   int32_t items_per_request, acc_per_request, total_items;
   int32_t head_major;        // cache layout: 0 = [slot][sum r] + scales [slot][H]; 1 = [head][slot][r_h] + scales [H][slot]
-  int32_t max_len, r2t_rows; // bound of b_seq_len the items were cut for; rows of req_to_token (0: not checked)
   HeadPlan head[LSVD_MAX_HEADS];
 };
 
@@ -80,6 +79,11 @@ struct AbsorbParams {
   float score_scale;       // sm_scale * log2(e)
   int32_t num_heads, head_dim, sum_rk;
   int32_t up_k_vec16;      // rows of up_k are 16-byte aligned
+  // checked copies of the batch bookkeeping for the kernels that follow: a request row outside the table becomes an empty
+  // request, a length beyond the bound the work items were cut for becomes that bound; both are reported
+  const int32_t* b_req_idx; const int32_t* b_seq_len;
+  int32_t* san_req; int32_t* san_len; int32_t* status_word;
+  int32_t max_len, r2t_rows;
   int32_t k_off[LSVD_MAX_HEADS + 1];
 };
 
@@ -103,6 +107,20 @@ __global__ void __launch_bounds__(128) absorb_query_kernel(const __grid_constant
   }
   grid_dependency_wait();
   if (h == 0 && b == 0 && threadIdx.x == 0) *p.queue = 0;
+  if (h == 0 && threadIdx.x == 0) {
+    int req = p.b_req_idx[b], len = p.b_seq_len[b];
+    if (p.r2t_rows > 0 && static_cast<uint32_t>(req) >= static_cast<uint32_t>(p.r2t_rows)) {
+      report_status(p.status_word, LSVD_ERR_BOUNDS);
+      req = 0;
+      len = 0;
+    }
+    if (len > p.max_len) {
+      report_status(p.status_word, LSVD_ERR_BOUNDS);
+      len = p.max_len;
+    }
+    p.san_req[b] = req;
+    p.san_len[b] = len < 0 ? 0 : len;
+  }
   const __half* qp = p.q + b * p.q_stride_b + h * p.q_stride_h;
   for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) qs[d] = __half2float(qp[d]);
   __syncthreads();
@@ -216,6 +234,7 @@ __device__ __forceinline__ void transpose4x4_bytes(uint32_t x0, uint32_t x1, uin
 //            feeds four MMAs (row g <-> rank 8g+r, row g+8 <-> rank 8g+4+r); B = the softmax weights
 //            p * scale_v of the 32 tokens, quantised per step to two unsigned base-256 limbs against the step's
 //            largest weight (16 bits), columns 0..1.  The int32 results are scaled back into fp32 accumulators.
+template <bool kHeadMajor>
 __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPlan& H, int b, int h, int rem, int k,
                                             int len, int t0, int t1, uint4* scratch, uint8_t* wlimb, int lane) {
   const int nk = H.nk, nv = H.nv;
@@ -223,17 +242,16 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
   const int nvg = (nv + 3) >> 2;                 // 64-rank groups of V
   const int g = lane >> 2, t4 = lane & 3;
   // head-major layout: a head's rows of consecutive slots are contiguous (r_h bytes apart), and so are its scales
-  const int8_t* kbase = p.cache_k + (p.head_major ? static_cast<int64_t>(H.k_col) * p.num_slots : H.k_col) + t4 * 8;
-  const int8_t* vbase = p.cache_v + (p.head_major ? static_cast<int64_t>(H.v_col) * p.num_slots : H.v_col) + g * 8;
+  const int8_t* kbase = p.cache_k + (kHeadMajor ? static_cast<int64_t>(H.k_col) * p.num_slots : H.k_col) + t4 * 8;
+  const int8_t* vbase = p.cache_v + (kHeadMajor ? static_cast<int64_t>(H.v_col) * p.num_slots : H.v_col) + g * 8;
   const bool v_ok0 = g * 8 < nv * 16, v_ok1 = 64 + g * 8 < nv * 16;
-  const __half* ksc = p.head_major ? p.scale_k + static_cast<int64_t>(h) * p.num_slots : p.scale_k + h;
-  const __half* vsc = p.head_major ? p.scale_v + static_cast<int64_t>(h) * p.num_slots : p.scale_v + h;
-  const int64_t ks_stride = p.head_major ? 1 : p.scale_k_row_stride, vs_stride = p.head_major ? 1 : p.scale_v_row_stride;
-  const int32_t* r2t = p.req_to_token + static_cast<int64_t>(__ldg(p.b_req_idx + b)) * p.req_to_token_stride;
+  const __half* ksc = kHeadMajor ? p.scale_k + static_cast<int64_t>(h) * p.num_slots : p.scale_k + h;
+  const __half* vsc = kHeadMajor ? p.scale_v + static_cast<int64_t>(h) * p.num_slots : p.scale_v + h;
+  const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
   const float step = p.qstep[b * p.num_heads + h];
   // row strides fit 32 bits (checked by the host): a row address is one 32 x 32 + 64-bit multiply-add
-  const uint32_t kstride = p.head_major ? static_cast<uint32_t>(nk * 16) : static_cast<uint32_t>(p.cache_k_row_stride);
-  const uint32_t vstride = p.head_major ? static_cast<uint32_t>(nv * 16) : static_cast<uint32_t>(p.cache_v_row_stride);
+  const uint32_t kstride = kHeadMajor ? static_cast<uint32_t>(nk * 16) : static_cast<uint32_t>(p.cache_k_row_stride);
+  const uint32_t vstride = kHeadMajor ? static_cast<uint32_t>(nv * 16) : static_cast<uint32_t>(p.cache_v_row_stride);
 
   __syncwarp();
   {
@@ -299,7 +317,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     resolve(s0, valid, rslot);
   }
   load_k(rslot);
-  float ks = __half2float(ksc[rslot * ks_stride]);
+  float ks = __half2float(ksc[kHeadMajor ? static_cast<int64_t>(rslot) : rslot * p.scale_k_row_stride]);
   int slot_n1 = -1;                  // slot of "my" token of the next step (lane = token role)
   if (tok_begin + kTileTokens + lane < tok_end) slot_n1 = r2t[tok_begin + kTileTokens + lane];
 
@@ -316,7 +334,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
       if (v_ok0) va[i] = ldg64(row);
       if (v_ok1) vb[i] = ldg64(row + 64);
     }
-    const float vs = __half2float(vsc[rslot * vs_stride]);
+    const float vs = __half2float(vsc[kHeadMajor ? static_cast<int64_t>(rslot) : rslot * p.scale_v_row_stride]);
 
     // ---- scores ----
     float sc[4];                     // score of token g + 8j, in lanes t = 0, 1 of the quad
@@ -353,7 +371,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     if (tb + kTileTokens < tok_end) {
       resolve(slot_n1, valid, rslot);
       load_k(rslot);
-      ks = __half2float(ksc[rslot * ks_stride]);
+      ks = __half2float(ksc[kHeadMajor ? static_cast<int64_t>(rslot) : rslot * p.scale_k_row_stride]);
     }
     // ---- online softmax; the running maximum is shared by the warp ----
     const float mx = fmaxf(m, warp_max_redux(s));
@@ -433,6 +451,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
   }
 }
 
+template <bool kHeadMajor>
 __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const __grid_constant__ StreamParams p) {
   __shared__ uint4 limb_scratch[kStreamWarps][8 * 3];
   __shared__ __align__(16) uint8_t weight_limbs[kStreamWarps][96];
@@ -452,22 +471,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const 
     const int h = __reduce_add_sync(0xffffffffu, below) - 1;
     const HeadPlan& H = p.head[h];
     const int k = rem - H.part_off;
-    // a length beyond the bound the items were cut for, or a request row outside the table, is reported, not followed
-    int len = p.b_seq_len[b];
-    if (len > p.max_len) {
-      if (lane == 0) report_status(p.status_word, LSVD_ERR_BOUNDS);
-      len = p.max_len;
-    }
-    const int req = p.b_req_idx[b];
-    if (p.r2t_rows > 0 && (req < 0 || req >= p.r2t_rows)) {
-      if (lane == 0) report_status(p.status_word, LSVD_ERR_BOUNDS);
-      continue;
-    }
+    const int len = p.b_seq_len[b];               // the checked copies written by the absorb kernel
     const int ntiles = tiles_of(len);
     const int t0 = k * H.chunk_tiles;
     const int t1 = min(ntiles, t0 + H.chunk_tiles);
     if (t0 >= t1) continue;                       // this request is shorter than the bound the items were cut for
-    stream_item(p, H, b, h, rem, k, len, t0, t1, limb_scratch[warp], weight_limbs[warp], lane);
+    stream_item<kHeadMajor>(p, H, b, h, rem, k, len, t0, t1, limb_scratch[warp], weight_limbs[warp], lane);
   }
 }
 
@@ -645,6 +654,7 @@ static WorkspaceLayout workspace_layout(int batch, int num_heads, int sum_rk, in
   w.qlimb = off; off = align_up(off + static_cast<size_t>(batch) * (sum_rk / 16) * 48, 256);
   w.qstep = off; off = align_up(off + static_cast<size_t>(batch) * num_heads * 4, 256);
   w.queue = off; off += 256;
+  w.san = off; off = align_up(off + static_cast<size_t>(batch) * 8, 256);
   w.part_ml = off; off = align_up(off + static_cast<size_t>(batch) * items_per_request * 8, 256);
   w.part_acc = off; off = align_up(off + static_cast<size_t>(batch) * acc_per_request * 4, 256);
   w.total = off;
@@ -732,6 +742,13 @@ int attn_launch_absorb(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
   ap.head_dim = a->head_dim;
   ap.sum_rk = a->k_off[a->num_heads];
   ap.up_k_vec16 = (aligned(a->up_k, 16) && (a->up_k_row_stride % 8) == 0) ? 1 : 0;
+  ap.b_req_idx = a->b_req_idx;
+  ap.b_seq_len = a->b_seq_len;
+  ap.san_req = reinterpret_cast<int32_t*>(ws + L.wl.san);
+  ap.san_len = ap.san_req + a->batch;
+  ap.status_word = a->status_word;
+  ap.max_len = a->max_len_in_batch;
+  ap.r2t_rows = a->req_to_token_rows > 0 ? a->req_to_token_rows : 0;
   std::memcpy(ap.k_off, a->k_off, sizeof(int32_t) * (a->num_heads + 1));
   LSVD_CUDA_TRY(launch_chained(absorb_query_kernel, dim3(a->num_heads, a->batch), dim3(128), 0, st, 1, true, ap));
   return LSVD_OK;
@@ -752,8 +769,8 @@ int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
   sp.scale_v_row_stride = a->scale_v_row_stride;
   sp.req_to_token = a->req_to_token;
   sp.req_to_token_stride = a->req_to_token_stride;
-  sp.b_req_idx = a->b_req_idx;
-  sp.b_seq_len = a->b_seq_len;
+  sp.b_req_idx = reinterpret_cast<const int32_t*>(ws + L.wl.san);      // the absorb kernel's checked copies
+  sp.b_seq_len = sp.b_req_idx + a->batch;
   sp.qlimb = reinterpret_cast<uint4*>(ws + L.wl.qlimb);
   sp.qstep = reinterpret_cast<float*>(ws + L.wl.qstep);
   sp.part_ml = reinterpret_cast<float*>(ws + L.wl.part_ml);
@@ -768,11 +785,10 @@ int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
   sp.acc_per_request = hp.acc_per_request;
   sp.total_items = static_cast<int32_t>(hp.total_items);
   sp.head_major = a->cache_layout == LSVD_CACHE_HEAD_MAJOR ? 1 : 0;
-  sp.max_len = a->max_len_in_batch;
-  sp.r2t_rows = a->req_to_token_rows > 0 ? a->req_to_token_rows : 0;
   for (int h = 0; h < a->num_heads; ++h) sp.head[h] = hp.head[h];
   if (a->ev_stream_begin) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_begin), st));
-  LSVD_CUDA_TRY(launch_chained(latent_stream_kernel, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
+  if (sp.head_major) LSVD_CUDA_TRY(launch_chained(latent_stream_kernel<true>, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
+  else LSVD_CUDA_TRY(launch_chained(latent_stream_kernel<false>, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
   if (a->ev_stream_end) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_end), st));
   return LSVD_OK;
 }
@@ -810,7 +826,7 @@ int attn_launch_merge(const lsvd_attn_decode_args* a, const AttnLaunch& L, cudaS
   MergeParams mp{};
   mp.part_ml = reinterpret_cast<const float*>(ws + L.wl.part_ml);
   mp.part_acc = reinterpret_cast<const float*>(ws + L.wl.part_acc);
-  mp.b_seq_len = a->b_seq_len;
+  mp.b_seq_len = reinterpret_cast<const int32_t*>(ws + L.wl.san) + a->batch;
   mp.up_v = static_cast<const __half*>(a->up_v);
   mp.up_v_row_stride = a->up_v_row_stride;
   mp.out = static_cast<__half*>(a->out);

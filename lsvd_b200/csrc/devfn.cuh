@@ -28,6 +28,12 @@ struct ActQuantParams {
   int32_t rows, cols, rotate;
   int32_t vec8;              // rows of x, sign and q allow 16 / 8-byte accesses
   float rot_scale;           // 1 / sqrt(cols)
+  // optional: the row is fp16(x32[r, i] + add16[r, i]) instead of x (a reduced fp32 partial sum plus its fp16
+  // residual); sum_out receives that fp16 row
+  const float* x32;
+  const __half* add16;
+  __half* sum_out;
+  __half* fake;              // optional [rows, cols] (contiguous): the fake-quantised row fp16(scale * code)
 };
 
 __device__ __forceinline__ float block_max(float v, float* red) {
@@ -53,7 +59,16 @@ __device__ __forceinline__ int8_t act_code(float x, float s) {
 // must call it (block barriers inside); any block size that is a multiple of 32 up to 256.
 __device__ __forceinline__ void act_quant_row(const ActQuantParams& p, int r, float* row, float* red) {
   const __half* x = p.x + r * p.x_row_stride;
-  if (p.vec8) {
+  if (p.x32 != nullptr) {
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+      const int64_t o = static_cast<int64_t>(r) * p.cols + i;
+      float v = __ldcg(p.x32 + o);
+      if (p.add16 != nullptr) v += __half2float(p.add16[o]);
+      const __half hv = __float2half_rn(v);
+      if (p.sum_out != nullptr) p.sum_out[o] = hv;
+      row[i] = __half2float(hv);
+    }
+  } else if (p.vec8) {
     // 16-byte loads, all of a thread's chunks in flight before the first use
     const int chunks = p.cols >> 3;
     for (int c0 = threadIdx.x; c0 < chunks; c0 += 4 * blockDim.x) {
@@ -153,6 +168,12 @@ __device__ __forceinline__ void act_quant_row(const ActQuantParams& p, int r, fl
   } else {
     for (int i = threadIdx.x; i < p.cols; i += blockDim.x) q[i] = act_code(row[i], s);
   }
+  if (p.fake != nullptr) {
+    // what the reference's quantiser returns from forward(): scale * code in fp32, rounded to fp16
+    // (fake_quant/utils/quant_utils.py:41-46)
+    __half* f = p.fake + static_cast<int64_t>(r) * p.cols;
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) f[i] = __float2half_rn(s * static_cast<float>(act_code(row[i], s)));
+  }
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -244,7 +265,7 @@ __device__ __forceinline__ void act_quant_rot4096_row(const ActQuantParams& p, i
 
 // True when act_quant_rot4096_row can take the row (the host-side test of lsvd_act_quant).
 __host__ __device__ inline bool act_quant_rot4096_ok(const ActQuantParams& p) {
-  return p.rotate && p.cols == 4096 && p.vec8 && p.norm_weight == nullptr &&
+  return p.rotate && p.cols == 4096 && p.vec8 && p.norm_weight == nullptr && p.fake == nullptr &&
          (reinterpret_cast<uintptr_t>(p.q) & 15) == 0 && (p.q_row_stride % 16) == 0 &&
          (p.x_rot == nullptr || (reinterpret_cast<uintptr_t>(p.x_rot) & 15) == 0);
 }

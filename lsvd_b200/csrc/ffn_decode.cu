@@ -665,11 +665,38 @@ static int launch_gemv_nt(const GemvParams& p, bool dual, bool split, cudaStream
 
 }  // namespace lsvd
 
+namespace lsvd {
+__global__ void dequant_residual_kernel(const int32_t* acc, const float* a_scale, const float* w_scale, const __half* residual,
+                                        int64_t res_stride, __half* out, int64_t out_stride, int m, int n) {
+  grid_dependency_sync();
+  const int64_t total = static_cast<int64_t>(m) * n;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int tok = static_cast<int>(i / n), ch = static_cast<int>(i - static_cast<int64_t>(tok) * n);
+    __half v = __float2half_rn((static_cast<float>(acc[i]) * a_scale[tok]) * w_scale[ch]);
+    if (residual != nullptr) v = __float2half_rn(__half2float(v) + __half2float(residual[tok * res_stride + ch]));
+    out[tok * out_stride + ch] = v;
+  }
+}
+}  // namespace lsvd
+
+extern "C" int lsvd_dequant_residual(const int32_t* acc, const float* a_scale, const float* w_scale, const void* residual,
+                                     int64_t residual_row_stride, void* out, int64_t out_row_stride, int32_t m, int32_t n, void* stream) {
+  using namespace lsvd;
+  if (!acc || !a_scale || !w_scale || !out || m <= 0 || n <= 0) return LSVD_ERR_INVALID_ARG;
+  const int64_t total = static_cast<int64_t>(m) * n;
+  const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 4 * std::max(1, device_sm_count())));
+  LSVD_CUDA_TRY(launch_chained(dequant_residual_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), 1, false, acc,
+                               a_scale, w_scale, static_cast<const __half*>(residual), residual_row_stride, static_cast<__half*>(out),
+                               out_row_stride, static_cast<int>(m), static_cast<int>(n)));
+  return LSVD_OK;
+}
+
 extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   using namespace lsvd;
   if (a == nullptr || a->rows < 0 || a->cols <= 0 || a->cols > 16384) return LSVD_ERR_INVALID_ARG;
   if (a->rows == 0) return LSVD_OK;
-  if (!a->x || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
+  if ((!a->x && !a->x_f32) || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
+  if (a->x_f32 != nullptr && (a->sign != nullptr || a->fwht != 0)) return LSVD_ERR_UNSUPPORTED;
   const bool rotate = a->sign != nullptr || a->fwht != 0;
   if (rotate && !is_pow2(a->cols)) return LSVD_ERR_INVALID_ARG;
   ActQuantParams p{};
@@ -687,9 +714,13 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   p.cols = a->cols;
   p.rotate = rotate ? 1 : 0;
   p.rot_scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(a->cols)));
+  p.x32 = a->x_f32;
+  p.add16 = static_cast<const __half*>(a->add);
+  p.sum_out = static_cast<__half*>(a->sum_out);
+  p.fake = static_cast<__half*>(a->fake);
   p.vec8 = ((a->cols % 8) == 0 && aligned(a->x, 16) && (a->x_row_stride % 8) == 0 && aligned(a->q, 8) &&
             (a->q_row_stride % 8) == 0 && (a->sign == nullptr || aligned(a->sign, 16))) ? 1 : 0;
-  if (rotate && a->cols == 4096 && p.vec8 && p.norm_weight == nullptr && aligned(a->q, 16) && (a->q_row_stride % 16) == 0 &&
+  if (rotate && a->cols == 4096 && p.vec8 && p.norm_weight == nullptr && p.fake == nullptr && aligned(a->q, 16) && (a->q_row_stride % 16) == 0 &&
       (p.x_rot == nullptr || aligned(p.x_rot, 16))) {
     LSVD_CUDA_TRY(launch_chained(act_quant_rot4096_kernel, dim3(a->rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 1,
                                  false, p));
@@ -812,7 +843,7 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   if (a == nullptr || a->m <= 0 || a->m > 64 || a->n <= 0 || (a->n % 16) || a->k <= 0 || (a->k % 16))
     return LSVD_ERR_INVALID_ARG;
   if (!a->w || !a->a) return LSVD_ERR_INVALID_ARG;
-  if (a->out != nullptr && (!a->w_scale || !a->a_scale)) return LSVD_ERR_INVALID_ARG;
+  if ((a->out != nullptr || a->out_f32 != nullptr) && (!a->w_scale || !a->a_scale)) return LSVD_ERR_INVALID_ARG;
   const bool dual = a->w2 != nullptr;
   if (dual != (a->epilogue == 1 || a->epilogue == 2) || a->epilogue < 0 || a->epilogue > 2) return LSVD_ERR_INVALID_ARG;
   const bool fp32_form = a->epilogue == 2 || a->row_absmax != nullptr;     // built into the register-fed kernel only
@@ -837,6 +868,8 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   p.row_absmax = a->row_absmax; p.row_absmax_stride = a->row_absmax_stride;
   p.absmax_split = a->absmax_split > 0 ? a->absmax_split : a->n;
   p.prefetch = (a->prefetch_weights != 0 && ffn_chain_enabled()) ? 1 : 0;
+  p.out_f32 = a->out_f32;
+  if (a->out_f32 != nullptr && (dual || a->form == 1 || a->form == 2)) return LSVD_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->form == 1) return a->m <= 16 ? launch_gemv_streamed(p, dual, split, st) : LSVD_ERR_UNSUPPORTED;
   if (a->form == 2) return launch_gemv_wide(p, dual, split, st);
@@ -844,7 +877,7 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   // more than 32 tokens and a large matrix: the form that shares the token rows between a block's warps
   // (measured: 35.6 vs 48.9 us for the 45 MB gate/up pair at 64 tokens; no gain at 32 tokens or below 16 MB)
   const int64_t weight_bytes = static_cast<int64_t>(a->n) * a->k * (dual ? 2 : 1);
-  if (a->form == 0 && !fp32_form && a->m > 32 && weight_bytes >= (16ll << 20)) return launch_gemv_wide(p, dual, split, st);
+  if (a->form == 0 && !fp32_form && a->out_f32 == nullptr && a->m > 32 && weight_bytes >= (16ll << 20)) return launch_gemv_wide(p, dual, split, st);
   if (a->m <= 8) return launch_gemv_nt<1>(p, dual, split, st);
   if (a->m <= 16) return launch_gemv_nt<2>(p, dual, split, st);
   if (a->m <= 32) return launch_gemv_nt<4>(p, dual, split, st);

@@ -19,6 +19,7 @@ struct GemvParams {
   // float (ordered like an unsigned integer): slot 0 for channels below absmax_split, slot 1 from there on
   uint32_t* row_absmax; int64_t row_absmax_stride; int32_t absmax_split;
   int32_t prefetch;          // pull the block's weight rows toward L2 before waiting for the previous kernel
+  float* out_f32;            // optional [m, n]: (acc * a_scale) * w_scale before any fp16 rounding (single products)
 };
 
 // The TMA-fed persistent form (gemv_tma.cu), for at most 16 tokens.
@@ -45,6 +46,8 @@ template <bool DUAL, bool SPLIT_B, bool MIX = false>
 __device__ __forceinline__ float gemv_store(const GemvParams& p, int tok, int row, int sum0, int sum1) {
   if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = sum0;
   if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = sum1;
+  if (!DUAL && p.out_f32 != nullptr)
+    p.out_f32[static_cast<int64_t>(tok) * p.n + row] = (static_cast<float>(sum0) * p.a_scale[tok * p.a_scale_stride]) * p.w_scale[row];
   if (p.out == nullptr) return 0.f;
   const float sa = p.a_scale[tok * p.a_scale_stride];
   const float f0 = (static_cast<float>(sum0) * sa) * p.w_scale[row];

@@ -55,28 +55,61 @@ def _ptr(t):
     return t.data_ptr() if t is not None else None
 
 
-def act_quant(x: torch.Tensor, sign: Optional[torch.Tensor] = None, fwht: bool = False, want_rotated: bool = False,
-              norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5):
-    """Per-token int8 quantisation of fp16 rows ``[rows, cols]`` (optionally after a Hadamard rotation).
+def act_quant(x: Optional[torch.Tensor], sign: Optional[torch.Tensor] = None, fwht: bool = False, want_rotated: bool = False,
+              norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-5, x_f32: Optional[torch.Tensor] = None,
+              add: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None, q: Optional[torch.Tensor] = None,
+              scale: Optional[torch.Tensor] = None, rot: Optional[torch.Tensor] = None, fake: Optional[torch.Tensor] = None):
+    """Per-token int8 quantisation of fp16 rows ``[rows, cols]`` (optionally after a Hadamard rotation or an RMSNorm).
+    With ``x_f32`` (fp32, contiguous) the row is ``fp16(x_f32 + add)`` instead of ``x`` and ``sum_out`` receives it: the
+    tensor-parallel output projection's reduced partial sums plus the residual.  ``q`` / ``scale`` / ``rot`` may be passed
+    in (preallocated); ``fake`` (fp16 ``[rows, cols]``, contiguous) receives the fake-quantised rows ``fp16(scale * code)``.
     Returns (codes int8, scale fp32 [rows], rotated fp16 or None)."""
-    _require_cuda(x)
-    if x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1:
+    src = x if x is not None else x_f32
+    _require_cuda(src)
+    if x is not None and (x.dtype != torch.float16 or x.dim() != 2 or x.stride(1) != 1):
         raise ValueError("x must be a 2-D fp16 tensor with unit inner stride")
-    rows, cols = x.shape
-    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
-    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
-    rot = torch.empty(rows, cols, dtype=torch.float16, device=x.device) if want_rotated else None
+    if x_f32 is not None and (x_f32.dtype != torch.float32 or not x_f32.is_contiguous() or
+                              (add is not None and not add.is_contiguous()) or (sum_out is not None and not sum_out.is_contiguous())):
+        raise ValueError("x_f32 must be contiguous fp32, add / sum_out contiguous fp16")
+    rows, cols = src.shape
+    if q is None:
+        q = torch.empty(rows, cols, dtype=torch.int8, device=src.device)
+    if scale is None:
+        scale = torch.empty(rows, dtype=torch.float32, device=src.device)
+    if rot is None and want_rotated:
+        rot = torch.empty(rows, cols, dtype=torch.float16, device=src.device)
     a = _lib.ActQuantArgs()
     a.rows, a.cols = rows, cols
-    a.x, a.x_row_stride = x.data_ptr(), x.stride(0)
+    if x is not None:
+        a.x, a.x_row_stride = x.data_ptr(), x.stride(0)
     a.sign = _ptr(sign)
     a.fwht = 1 if fwht else 0
     a.q, a.q_row_stride = q.data_ptr(), q.stride(0)
     a.scale = scale.data_ptr()
     a.x_rot = _ptr(rot)
     a.norm_weight, a.norm_eps = _ptr(norm_weight), norm_eps
-    _lib.check(_lib.load().lsvd_act_quant(C.byref(a), _stream_ptr(x)))
+    a.x_f32, a.add, a.sum_out = _ptr(x_f32), _ptr(add), _ptr(sum_out)
+    if fake is not None and (fake.dtype != torch.float16 or not fake.is_contiguous() or fake.shape != src.shape):
+        raise ValueError("fake must be a contiguous fp16 tensor of the input's shape")
+    a.fake = _ptr(fake)
+    _lib.check(_lib.load().lsvd_act_quant(C.byref(a), _stream_ptr(src)))
     return q, scale, rot
+
+
+def dequant_residual(acc: torch.Tensor, a_scale: torch.Tensor, w_scale: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``fp16(fp16((acc * a_scale[m]) * w_scale[n]) + residual)`` for int32 accumulators ``[m, n]`` (contiguous) that were
+    summed over tensor-parallel ranks: the epilogue of ``w8a8_gemv`` applied after the all-reduce."""
+    _require_cuda(acc)
+    m, n = acc.shape
+    if acc.dtype != torch.int32 or not acc.is_contiguous():
+        raise ValueError("acc must be a contiguous int32 tensor")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float16, device=acc.device)
+    _lib.check(_lib.load().lsvd_dequant_residual(acc.data_ptr(), a_scale.data_ptr(), w_scale.data_ptr(), _ptr(residual),
+                                                residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0),
+                                                m, n, _stream_ptr(acc)))
+    return out
 
 
 def hadamard_pack(had_K: torch.Tensor) -> torch.Tensor:
@@ -90,15 +123,17 @@ def hadamard_pack(had_K: torch.Tensor) -> torch.Tensor:
     return packed
 
 
-def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rotated: bool = False):
+def hadamard_quant(x: torch.Tensor, had_K_packed: torch.Tensor, K: int, want_rotated: bool = False, q=None, scale=None):
     """(H_K kron H_{cols/K}) rotation of fp16 rows followed by per-token int8 quantisation.
     ``had_K_packed`` comes from ``hadamard_pack(had_K)``."""
     _require_cuda(x, had_K_packed)
     if x.dtype != torch.float16 or had_K_packed.dtype != torch.uint8:
         raise ValueError("x must be fp16 and had_K_packed the buffer made by hadamard_pack")
     rows, cols = x.shape
-    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
-    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    if q is None:
+        q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
+    if scale is None:
+        scale = torch.empty(rows, dtype=torch.float32, device=x.device)
     y = torch.empty(rows, cols, dtype=torch.float16, device=x.device) if want_rotated else None
     a = _lib.HadamardQuantArgs()
     a.rows, a.cols, a.K = rows, cols, K
@@ -134,7 +169,7 @@ def heads_hadamard_quant(x: torch.Tensor, heads: int, want_rotated: bool = False
 
 def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a2_scale=None, out=None, out_col=0,
               want_acc=False, want_out=True, residual=None, form=0, status_word=None, fp32_swiglu=False,
-              row_absmax=None, absmax_split=0, prefetch_weights=False):
+              row_absmax=None, absmax_split=0, prefetch_weights=False, out_f32=None, acc=None):
     """acc = a_q @ w_q^T (int32, exact) for 1..64 tokens, dequantised to fp16; with (w2, a2) a gate/up pair whose
     result is silu(gate) * up.  Returns (out fp16 [m, n] or the passed tensor, acc int32 or None, acc2 or None).
     ``form`` 0 is the register-fed kernel, 1 the persistent TMA-fed one (at most 16 tokens); ``status_word`` (int32
@@ -148,9 +183,11 @@ def w8a8_gemv(a_q, a_scale, w_q, w_scale, w2_q=None, w2_scale=None, a2_q=None, a
     dual = w2_q is not None
     if out is None and want_out:
         out = torch.empty(m, n, dtype=torch.float16, device=dev)
-    acc = torch.empty(m, n, dtype=torch.int32, device=dev) if want_acc else None
+    if acc is None and want_acc:
+        acc = torch.empty(m, n, dtype=torch.int32, device=dev)
     acc2 = torch.empty(m, n, dtype=torch.int32, device=dev) if (want_acc and dual) else None
     g = _lib.GemvArgs()
+    g.out_f32 = _ptr(out_f32)          # fp32 [m, n], contiguous: the dequantised value before any fp16 rounding
     g.m, g.n, g.k = m, n, k
     g.w, g.w_row_stride, g.w_scale = w_q.data_ptr(), w_q.stride(0), _ptr(w_scale)
     if dual:

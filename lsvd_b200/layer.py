@@ -23,7 +23,7 @@ import torch
 from torch import nn
 
 from .attention import LatentCacheLayout, cache_append, token_decode_attention_int8_latent_absorb, attn_decode_workspace_bytes
-from .ffn import HybridFFN, act_quant, w8a8_gemv, quantize_weight_rtn
+from .ffn import HybridFFN, act_quant, w8a8_gemv, quantize_weight_rtn, i8gemm
 
 
 class LSVDDecoderLayer(nn.Module):
@@ -66,19 +66,47 @@ class LSVDDecoderLayer(nn.Module):
         return out
 
 
-def make_layer_weights(hidden: int, num_heads: int, head_dim: int, rank_q: int, k_ranks, v_ranks, seed: int = 0):
-    """Seeded random layer weights on the CPU (xavier-like scales as the reference's block,
-    kernels/layer_bench/ffn_kernel/baseline_kernel.py:86-91); returns the dict ``LSVDDecoderLayer`` takes."""
-    g = torch.Generator().manual_seed(seed)
+def _layer_prefill(self, x, cache_k, scale_k, cache_v, scale_v, dest_slots, stages=None, out=None):
+    """The layer for a prefill-sized batch of tokens ``x [T, hidden]`` whose cache slots are ``dest_slots [T]``: the same
+    stages as a decode step with every product on the tcgen05 GEMM (lsvd_i8gemm_prefill) and the cache written by the
+    prefill-sized form of the append kernel.  The reference has no prefill attention (its kernels are decode-only,
+    kernels/layer_bench/fd_kernel/): between the cache write and the output projection this step lets every token attend
+    to ITSELF only, i.e. the attention output is the token's own (fp16) V latent.  Everything BASELINE config 5 names for
+    the prefill -- the latent-projection, gate / up / down GEMMs and the cache write -- runs as in a real prefill; the
+    values that reach the decode steps differ from a causal-attention prefill, which this library does not have."""
+    lay = self.layout
+    xq, xs, xn = act_quant(x, want_rotated=True, norm_weight=self.ln1, norm_eps=1e-5)
+    lat, _ = i8gemm(xq, xs, self.W_lat_q, self.W_lat_s)
+    lk = lat[:, self.Rq:self.Rq + lay.sum_k]
+    lv = lat[:, self.Rq + lay.sum_k:]
+    cache_append(lay, lk, lv, dest_slots, cache_k, scale_k, cache_v, scale_v)
+    o_lat = lv.contiguous()
+    oq, os_, _ = act_quant(o_lat)
+    y1, _ = i8gemm(oq, os_, self.W_uvo_q, self.W_uvo_s, residual=xn)
+    out = self.ffn(y1, out=out, norm_weight=self.ln2, norm_eps=1e-6, residual=y1)
+    if stages is not None:
+        stages.update(xn=xn, lat=lat, o_lat=o_lat, y1=y1, out=out)
+    return out
+
+
+LSVDDecoderLayer.forward_prefill = torch.no_grad()(_layer_prefill)
+
+
+def make_layer_weights(hidden: int, num_heads: int, head_dim: int, rank_q: int, k_ranks, v_ranks, seed: int = 0, device=None):
+    """Seeded random layer weights (xavier-like scales as the reference's block,
+    kernels/layer_bench/ffn_kernel/baseline_kernel.py:86-91); returns the dict ``LSVDDecoderLayer`` takes.  Drawn on the
+    CPU unless ``device`` is given (whole stacks in benchmarks)."""
+    g = (torch.Generator() if device is None else torch.Generator(device=device)).manual_seed(seed)
+    dv = dict(device=device) if device is not None else {}
     Rq, Rk, Rv = num_heads * rank_q, sum(k_ranks), sum(v_ranks)
 
     def rnd(*shape, std):
-        return torch.randn(*shape, generator=g) * std
+        return torch.randn(*shape, generator=g, **dv) * std
 
     W_lat = rnd(Rq + Rk + Rv, hidden, std=1.0 / math.sqrt(hidden))
     A_q = rnd(num_heads, head_dim, rank_q, std=1.0 / math.sqrt(rank_q))          # query up-factor per head
     B_k = rnd(Rk, head_dim, std=1.0 / 8)                                           # K up-factor rows per head
-    C = torch.empty(Rk, rank_q)
+    C = torch.empty(Rk, rank_q, **dv)
     off = 0
     for h, r in enumerate(k_ranks):
         C[off:off + r] = B_k[off:off + r] @ A_q[h]
@@ -95,71 +123,94 @@ class TPDecoderLayer(nn.Module):
 
     Built from that rank's local weights; ``forward`` takes the replicated hidden state and the rank's own cache
     columns, and issues one all-reduce in the attention block, one all-gather and one all-reduce in the FFN block.
+    Everything between the collectives runs in the library's kernels (the dequantising steps around a collective are
+    epilogues: an fp32 partial-sum output of the product before the first all-reduce, the residual + RMSNorm + A8
+    quantiser after it, a dequantise + residual kernel after the second); buffers are kept per batch size, so a step is
+    about twenty host calls and allocates nothing.
     """
 
-    def __init__(self, lw: dict, fw: dict, info: dict, head_dim: int, rank_q: int, world: int, group=None):
+    def __init__(self, lw: dict, fw: dict, info: dict, head_dim: int, rank_q: int, world: int, group=None, head_major: bool = False):
         super().__init__()
         self.info, self.head_dim, self.rank_q, self.world, self.group = info, head_dim, rank_q, world, group
-        self.layout = LatentCacheLayout(info["k_ranks"], info["v_ranks"])
+        self.layout = LatentCacheLayout(info["k_ranks"], info["v_ranks"], head_major=head_major)
         for name in ("ln1", "ln2", "W_lat_q", "W_lat_s", "C", "W_uvo_q", "W_uvo_s"):
             self.register_buffer(name, lw[name].contiguous())
-        for name in ("U_q", "U_s", "Vg_q", "Vg_s", "Vu_q", "Vu_s", "Wg_q", "Wg_s", "Wu_q", "Wu_s", "Wd_svd_q", "Wd_rtn_q", "Wd_s"):
+        for name in ("U_q", "U_s", "Vg_q", "Vg_s", "Vu_q", "Vu_s", "Wg_q", "Wg_s", "Wu_q", "Wu_s", "Wd_loc_q", "Wd_s"):
             self.register_buffer("f_" + name, fw[name].contiguous())
         self.K = int(fw.get("K", 1))
         hk = fw.get("had_K")
         self.register_buffer("had_K", None if hk is None else hk.to(torch.float16).contiguous())
         self.had_K_packed = None
         self.Rq = self.layout.num_heads * rank_q
-        self._ws = None
+        self._bufs = {}
+
+    def _step_buffers(self, B: int, max_len: int, dev):
+        key = (B, max_len, str(dev))
+        b = self._bufs.get(key)
+        if b is not None:
+            return b
+        from .parallel import gather_plan
+        lay, hidden = self.layout, self.ln1.shape[0]
+        r = self.f_U_q.shape[0] // 2
+        ns, nq = self.f_Vg_q.shape[0], self.f_Wg_q.shape[0]
+        d_ffn = self.info["n_svd"] + self.info["n_q"]
+        widest, idx = gather_plan(self.info, self.world, dev)
+        e = lambda *shape, dt=torch.float16: torch.empty(*shape, dtype=dt, device=dev)
+        b = dict(
+            ws=torch.empty(attn_decode_workspace_bytes(B, lay, max_len), dtype=torch.uint8, device=dev),
+            xq=e(B, hidden, dt=torch.int8), xs=e(B, dt=torch.float32), xn=e(B, hidden),
+            lat=e(B, self.W_lat_q.shape[0]), o_lat=e(B, lay.sum_v), oq=e(B, lay.sum_v, dt=torch.int8), os=e(B, dt=torch.float32),
+            part=e(B, hidden, dt=torch.float32), y1=e(B, hidden), x2q=e(B, hidden, dt=torch.int8), x2s=e(B, dt=torch.float32),
+            lat2=e(B, 2 * r), zq=e(2 * B, r, dt=torch.int8), zs=e(2 * B, dt=torch.float32),
+            send=torch.zeros(B, widest, dtype=torch.float16, device=dev), recv=e(self.world * B, widest),
+            hq=e(B, d_ffn, dt=torch.int8), hs=e(B, dt=torch.float32), hloc=e(B, ns + nq, dt=torch.int8),
+            acc=e(B, hidden, dt=torch.int32), out=e(B, hidden), plan=(widest, idx))
+        self._bufs[key] = b
+        return b
 
     @torch.no_grad()
-    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages=None):
+    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages=None, timing_events=None):
         import torch.distributed as dist
-        from .ffn import hadamard_pack, hadamard_quant
+        from .ffn import hadamard_pack, hadamard_quant, dequant_residual
         from .parallel import gather_hidden
         lay, Hl, B, dev = self.layout, self.layout.num_heads, x.shape[0], x.device
-        xq, xs, xn = act_quant(x, want_rotated=True, norm_weight=self.ln1, norm_eps=1e-5)
-        lat, _, _ = w8a8_gemv(xq, xs, self.W_lat_q, self.W_lat_s)
+        b = self._step_buffers(B, int(infer_state.max_len_in_batch), dev)
+        # ---- attention block: RMSNorm + A8, latent projection, append, attention, row-parallel output projection ----
+        act_quant(x, norm_weight=self.ln1, norm_eps=1e-5, q=b["xq"], scale=b["xs"], rot=b["xn"])
+        w8a8_gemv(b["xq"], b["xs"], self.W_lat_q, self.W_lat_s, out=b["lat"])
+        lat = b["lat"]
         cache_append(lay, lat[:, self.Rq:self.Rq + lay.sum_k], lat[:, self.Rq + lay.sum_k:], infer_state.mem_index,
                      cache_k, scale_k, cache_v, scale_v)
-        need = attn_decode_workspace_bytes(B, lay, infer_state.max_len_in_batch)
-        if self._ws is None or self._ws.numel() < need:
-            self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
-        o_lat = torch.empty(B, lay.sum_v, dtype=torch.float16, device=dev)
         token_decode_attention_int8_latent_absorb(lat[:, :self.Rq].unflatten(1, (Hl, self.rank_q)), infer_state, Hl,
                                                   self.rank_q, cache_k, scale_k, cache_v, scale_v, self.C, None,
-                                                  layout=lay, out_latent=o_lat, workspace=self._ws,
-                                                  sm_scale=1.0 / math.sqrt(self.head_dim))
-        # row-parallel output projection: dequantised partial sums in fp32, ONE all-reduce, then the residual
-        oq, os_, _ = act_quant(o_lat)
-        _, acc, _ = w8a8_gemv(oq, os_, self.W_uvo_q, None, want_acc=True, want_out=False)
-        part = (acc.float() * os_[:, None]) * self.W_uvo_s[None, :]
-        dist.all_reduce(part, group=self.group)
-        y1 = (part + xn.float()).half()
-        # FFN: replicated latents, column-parallel gate/up, gathered hidden vector, row-parallel int32 down projection
+                                                  layout=lay, out_latent=b["o_lat"], workspace=b["ws"],
+                                                  sm_scale=1.0 / math.sqrt(self.head_dim), timing_events=timing_events)
+        act_quant(b["o_lat"], q=b["oq"], scale=b["os"])
+        w8a8_gemv(b["oq"], b["os"], self.W_uvo_q, self.W_uvo_s, want_out=False, out_f32=b["part"])       # fp32 partial sums
+        dist.all_reduce(b["part"], group=self.group)
+        # y1 = fp16(sum + xn); x2 = A8(RMSNorm(y1)): one launch
+        act_quant(None, x_f32=b["part"], add=b["xn"], sum_out=b["y1"], norm_weight=self.ln2, norm_eps=1e-6, q=b["x2q"], scale=b["x2s"])
+        # ---- FFN: replicated latents, column-parallel gate/up, gathered hidden vector, row-parallel int32 down projection ----
         r = self.f_U_q.shape[0] // 2
-        x2q, x2s, _ = act_quant(y1, norm_weight=self.ln2, norm_eps=1e-6)
-        lat2, _, _ = w8a8_gemv(x2q, x2s, self.f_U_q, self.f_U_s)
-        zq, zs, _ = act_quant(lat2.view(-1, r))
-        zq, zs = zq.view(-1, 2 * r), zs.view(-1, 2)
-        ns, nq = self.f_Vg_q.shape[0], self.f_Wg_q.shape[0]
-        h_local = torch.empty(B, ns + nq, dtype=torch.float16, device=dev)
+        ns = self.f_Vg_q.shape[0]
+        w8a8_gemv(b["x2q"], b["x2s"], self.f_U_q, self.f_U_s, out=b["lat2"])
+        act_quant(b["lat2"].view(-1, r), q=b["zq"], scale=b["zs"])
+        zq, zs = b["zq"].view(B, 2 * r), b["zs"].view(B, 2)
+        h_local = b["send"]                       # the rank's [SVD slice | RTN slice]; the padding columns stay zero
         w8a8_gemv(zq[:, :r], zs[:, 0], self.f_Vg_q, self.f_Vg_s, self.f_Vu_q, self.f_Vu_s, a2_q=zq[:, r:], a2_scale=zs[:, 1],
                   out=h_local, out_col=0)
-        w8a8_gemv(x2q, x2s, self.f_Wg_q, self.f_Wg_s, self.f_Wu_q, self.f_Wu_s, out=h_local, out_col=ns)
-        h = gather_hidden(h_local, self.info, self.world, self.group)
+        w8a8_gemv(b["x2q"], b["x2s"], self.f_Wg_q, self.f_Wg_s, self.f_Wu_q, self.f_Wu_s, out=h_local, out_col=ns)
+        h = gather_hidden(h_local, self.info, self.world, self.group, plan=b["plan"], send=b["send"], recv=b["recv"])
         if self.had_K_packed is None:
             self.had_K_packed = hadamard_pack(self.had_K)
-        hq, hs, _ = hadamard_quant(h, self.had_K_packed, self.K)
+        hq, hs, _ = hadamard_quant(h, self.had_K_packed, self.K, q=b["hq"], scale=b["hs"])
         s0, s1 = self.info["svd"]
         q0, q1 = self.info["rtn"]
         n_svd = self.info["n_svd"]
-        _, a1, _ = w8a8_gemv(hq[:, s0:s1], hs, self.f_Wd_svd_q, None, want_acc=True, want_out=False)
-        _, a2, _ = w8a8_gemv(hq[:, n_svd + q0:n_svd + q1], hs, self.f_Wd_rtn_q, None, want_acc=True, want_out=False)
-        acc = a1 + a2
-        dist.all_reduce(acc, group=self.group)
-        down = ((acc.float() * hs[:, None]) * self.f_Wd_s[None, :]).half()
-        out = (down.float() + y1.float()).half()
+        torch.cat((hq[:, s0:s1], hq[:, n_svd + q0:n_svd + q1]), dim=1, out=b["hloc"])
+        w8a8_gemv(b["hloc"], hs, self.f_Wd_loc_q, None, want_out=False, acc=b["acc"])
+        dist.all_reduce(b["acc"], group=self.group)
+        out = dequant_residual(b["acc"], hs, self.f_Wd_s, residual=b["y1"], out=b["out"])
         if stages is not None:
-            stages.update(xn=xn, o_lat=o_lat, y1=y1, h_q=hq, down_acc=acc, out=out)
+            stages.update(xn=b["xn"], o_lat=b["o_lat"], y1=b["y1"], h_q=hq, down_acc=b["acc"], out=out)
         return out

@@ -2,8 +2,8 @@
 
 The reference has no tensor parallelism.  The layer shards by independent units with one sum per block:
 
-  attention block   heads are split over the ranks (contiguous runs balanced by latent bytes); a rank owns its
-                    heads' rows of the latent projection, their K/V cache columns, their query/K factors and
+  attention block   heads are dealt to the ranks by latent bytes (largest first, each to the lightest rank); a rank
+                    owns its heads' rows of the latent projection, their K/V cache columns, their query/K factors and
                     the matching input columns of the fused output projection, which makes that projection
                     row-parallel: ONE all-reduce (sum, fp32 [B, hidden]) per block.
   FFN block         the intermediate channels of both branches are split over the ranks (column-parallel
@@ -24,24 +24,20 @@ from typing import List, Sequence, Tuple
 import torch
 
 
-def partition_heads(k_ranks: Sequence[int], v_ranks: Sequence[int], world: int) -> List[Tuple[int, int]]:
-    """Contiguous head ranges [h0, h1) per rank, balanced by latent bytes (r_k + r_v), every rank non-empty."""
+def partition_heads(k_ranks: Sequence[int], v_ranks: Sequence[int], world: int) -> List[List[int]]:
+    """Heads of every rank (ascending), balanced by latent bytes r_k + r_v: the heaviest head first, each to the rank
+    that is lightest so far (ties: fewer heads, then the lower rank).  Every rank gets at least one head."""
     H = len(k_ranks)
     if world < 1 or world > H:
         raise ValueError("need 1 <= world <= number of heads")
     cost = [a + b for a, b in zip(k_ranks, v_ranks)]
-    total = sum(cost)
-    bounds, acc, h = [0], 0, 0
-    for r in range(1, world):
-        target = total * r / world
-        while h < H - (world - r) and acc + cost[h] / 2 < target:
-            acc += cost[h]
-            h += 1
-        h = max(h, bounds[-1] + 1)
-        bounds.append(h)
-        acc = sum(cost[:h])
-    bounds.append(H)
-    return [(bounds[i], bounds[i + 1]) for i in range(world)]
+    order = sorted(range(H), key=lambda h: (-cost[h], h))
+    load, heads = [0] * world, [[] for _ in range(world)]
+    for h in order:
+        r = min(range(world), key=lambda i: (load[i], len(heads[i]), i))
+        heads[r].append(h)
+        load[r] += cost[h]
+    return [sorted(hs) for hs in heads]
 
 
 def channel_slices(n: int, world: int) -> List[Tuple[int, int]]:
@@ -64,17 +60,23 @@ def _off(ranks):
     return o
 
 
+def _cols(off, heads):
+    return torch.cat([torch.arange(off[h], off[h + 1]) for h in heads])
+
+
 def shard_layer(w: dict, ffn_w: dict, k_ranks, v_ranks, rank_q: int, world: int, rank: int):
-    """Local weights of `rank`.  Returns (layer dict, ffn dict, info) with info = head range, local rank lists,
-    cache column ranges and the rank's channel slices."""
+    """Local weights of `rank`.  Returns (layer dict, ffn dict, info) with info = the rank's heads, their local rank
+    lists, the columns of the unsharded K / V cache rows they occupy (index tensors) and the rank's channel slices.
+    The down projection's local input columns are one matrix ``Wd_loc_q [d_out, svd slice | rtn slice]``."""
     H = len(k_ranks)
-    h0, h1 = partition_heads(k_ranks, v_ranks, world)[rank]
+    heads = partition_heads(k_ranks, v_ranks, world)[rank]
     ko, vo = _off(k_ranks), _off(v_ranks)
     Rq, Rk = H * rank_q, ko[-1]
-    rows = torch.cat([torch.arange(h0 * rank_q, h1 * rank_q), Rq + torch.arange(ko[h0], ko[h1]),
-                      Rq + Rk + torch.arange(vo[h0], vo[h1])])
+    k_cols, v_cols = _cols(ko, heads), _cols(vo, heads)
+    q_rows = torch.cat([torch.arange(h * rank_q, (h + 1) * rank_q) for h in heads])
+    rows = torch.cat([q_rows, Rq + k_cols, Rq + Rk + v_cols])
     lw = {"ln1": w["ln1"], "ln2": w["ln2"], "W_lat_q": w["W_lat_q"][rows].contiguous(), "W_lat_s": w["W_lat_s"][rows].contiguous(),
-          "C": w["C"][ko[h0]:ko[h1]].contiguous(), "W_uvo_q": w["W_uvo_q"][:, vo[h0]:vo[h1]].contiguous(), "W_uvo_s": w["W_uvo_s"]}
+          "C": w["C"][k_cols].contiguous(), "W_uvo_q": w["W_uvo_q"][:, v_cols].contiguous(), "W_uvo_s": w["W_uvo_s"]}
     n_svd, n_q = ffn_w["Vg_q"].shape[0], ffn_w["Wg_q"].shape[0]
     s0, s1 = channel_slices(n_svd, world)[rank]
     q0, q1 = channel_slices(n_q, world)[rank]
@@ -83,28 +85,40 @@ def shard_layer(w: dict, ffn_w: dict, k_ranks, v_ranks, rank_q: int, world: int,
         fw[name + "_q"], fw[name + "_s"] = ffn_w[name + "_q"][s0:s1].contiguous(), ffn_w[name + "_s"][s0:s1].contiguous()
     for name in ("Wg", "Wu"):
         fw[name + "_q"], fw[name + "_s"] = ffn_w[name + "_q"][q0:q1].contiguous(), ffn_w[name + "_s"][q0:q1].contiguous()
-    fw["Wd_svd_q"] = ffn_w["Wd_q"][:, s0:s1].contiguous()
-    fw["Wd_rtn_q"] = ffn_w["Wd_q"][:, n_svd + q0:n_svd + q1].contiguous()
-    info = dict(heads=(h0, h1), k_ranks=list(k_ranks[h0:h1]), v_ranks=list(v_ranks[h0:h1]), k_cols=(ko[h0], ko[h1]),
-                v_cols=(vo[h0], vo[h1]), svd=(s0, s1), rtn=(q0, q1), n_svd=n_svd, n_q=n_q)
+    fw["Wd_loc_q"] = torch.cat([ffn_w["Wd_q"][:, s0:s1], ffn_w["Wd_q"][:, n_svd + q0:n_svd + q1]], dim=1).contiguous()
+    fw.pop("Wd_q", None)
+    info = dict(heads=heads, k_ranks=[k_ranks[h] for h in heads], v_ranks=[v_ranks[h] for h in heads], k_cols=k_cols,
+                v_cols=v_cols, svd=(s0, s1), rtn=(q0, q1), n_svd=n_svd, n_q=n_q)
     return lw, fw, info
 
 
-def gather_hidden(h_local: torch.Tensor, info: dict, world: int, group=None) -> torch.Tensor:
-    """All-gather the ranks' [B, svd slice | rtn slice] pieces and lay them out in the global [SVD | RTN] order."""
-    import torch.distributed as dist
-    B = h_local.shape[0]
+def gather_plan(info: dict, world: int, device=None):
+    """(widest, index): every rank sends ``[B, widest]`` (its SVD slice, then its RTN slice, zero padded); the gathered
+    ``[world, B, widest]`` buffer seen as ``[B, world * widest]`` gives the hidden vector in the global [SVD | RTN] order
+    through ``index`` (one index_select)."""
     n_svd, n_q = info["n_svd"], info["n_q"]
     svd_sl, rtn_sl = channel_slices(n_svd, world), channel_slices(n_q, world)
     widest = max((a[1] - a[0]) + (b[1] - b[0]) for a, b in zip(svd_sl, rtn_sl))
-    send = h_local.new_zeros(B, widest)
-    send[:, :h_local.shape[1]] = h_local
-    parts = [torch.empty_like(send) for _ in range(world)]
-    dist.all_gather(parts, send, group=group)
-    full = h_local.new_empty(B, n_svd + n_q)
+    idx = torch.empty(n_svd + n_q, dtype=torch.int64)
     for r in range(world):
         ns = svd_sl[r][1] - svd_sl[r][0]
         nr = rtn_sl[r][1] - rtn_sl[r][0]
-        full[:, svd_sl[r][0]:svd_sl[r][1]] = parts[r][:, :ns]
-        full[:, n_svd + rtn_sl[r][0]:n_svd + rtn_sl[r][1]] = parts[r][:, ns:ns + nr]
-    return full
+        idx[svd_sl[r][0]:svd_sl[r][1]] = r * widest + torch.arange(ns)
+        idx[n_svd + rtn_sl[r][0]:n_svd + rtn_sl[r][1]] = r * widest + ns + torch.arange(nr)
+    return widest, (idx if device is None else idx.to(device))
+
+
+def gather_hidden(h_local: torch.Tensor, info: dict, world: int, group=None, plan=None, send=None, recv=None) -> torch.Tensor:
+    """All-gather the ranks' [B, svd slice | rtn slice] pieces and lay them out in the global [SVD | RTN] order:
+    one collective into a preallocated buffer, one index_select.  ``send [B, widest]`` must have its padding columns zero."""
+    import torch.distributed as dist
+    B = h_local.shape[0]
+    widest, idx = plan if plan is not None else gather_plan(info, world, h_local.device)
+    if send is None:
+        send = h_local.new_zeros(B, widest)
+    if send.data_ptr() != h_local.data_ptr():
+        send[:, :h_local.shape[1]].copy_(h_local)
+    if recv is None:
+        recv = h_local.new_empty(world * B, widest)            # rank r's rows at r * B ..
+    dist.all_gather_into_tensor(recv, send, group=group)
+    return recv.view(world, B, widest).permute(1, 0, 2).reshape(B, world * widest).index_select(1, idx)

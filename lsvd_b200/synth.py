@@ -63,7 +63,7 @@ def sign_matrix(K: int, seed: int = 0):
 
 
 def ffn_weights(d_in: int, d_ffn: int, rank: int, n_svd: int, seed: int = 0, std: float = 0.02, had_K=None,
-                K: int = 1, input_had: bool = True, mse: bool = False) -> dict:
+                K: int = 1, input_had: bool = True, mse: bool = False, device=None) -> dict:
     """Seeded hybrid-FFN weights on the CPU: N(0, std) draws, int8 RTN per output channel.
 
     A seeded ``randperm(d_ffn)[:n_svd]`` picks the SVD channel group; the weights being random, the permutation
@@ -71,12 +71,15 @@ def ffn_weights(d_in: int, d_ffn: int, rank: int, n_svd: int, seed: int = 0, std
     Returns the dict ``HybridFFN`` and the CPU checker both take.
     """
     from .ffn import quantize_weight_rtn
-    g = torch.Generator().manual_seed(seed)
+    # `device`: draw on that device (benchmarks of whole stacks, where a CPU draw of every layer would take minutes);
+    # the default CPU generator is what the parity tests and the CPU checker share
+    g = (torch.Generator() if device is None else torch.Generator(device=device)).manual_seed(seed)
+    dv = dict(device=device) if device is not None else {}
     n_q = d_ffn - n_svd
     w = {"K": K, "had_K": had_K, "online_had": True}
     for name, shape in (("U", (2 * rank, d_in)), ("Vg", (n_svd, rank)), ("Vu", (n_svd, rank)),
                         ("Wg", (n_q, d_in)), ("Wu", (n_q, d_in)), ("Wd", (d_in, d_ffn))):
-        w[name + "_q"], w[name + "_s"] = quantize_weight_rtn(torch.randn(*shape, generator=g) * std, mse)
-    w["perm"] = torch.randperm(d_ffn, generator=g)
-    w["had_sign"] = (torch.randint(0, 2, (d_in,), generator=g).float() * 2 - 1).to(torch.float16) if input_had else None
+        w[name + "_q"], w[name + "_s"] = quantize_weight_rtn(torch.randn(*shape, generator=g, **dv) * std, mse)
+    w["perm"] = torch.randperm(d_ffn, generator=g, **dv)
+    w["had_sign"] = (torch.randint(0, 2, (d_in,), generator=g, **dv).float() * 2 - 1).to(torch.float16) if input_had else None
     return w

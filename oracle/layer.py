@@ -50,6 +50,22 @@ def decoder_layer(x16, w, ffn_w, k_off, v_off, num_heads, head_dim, rank_q, cach
     return out, dict(xn=xn_own, lat=lat, o_lat=o16, y1=y1_own, out=out)
 
 
+def prefill_layer(x16, w, ffn_w, k_off, v_off, num_heads, rank_q, cache_k, scale_k, cache_v, scale_v, dest_slots):
+    """The prefill form of the layer (lsvd_b200/layer.py, forward_prefill): the same stages as a decode step with the
+    attention output replaced by the token's own V latent (the reference has no prefill attention; see that docstring)."""
+    Rq = num_heads * rank_q
+    xn = rms_norm(x16, w["ln1"], 1e-5)
+    lat = linear_a8w8(xn, w["W_lat_q"], w["W_lat_s"])
+    attention.cache_append(lat[:, Rq:Rq + k_off[-1]].contiguous(), dest_slots, k_off, cache_k, scale_k)
+    attention.cache_append(lat[:, Rq + k_off[-1]:].contiguous(), dest_slots, v_off, cache_v, scale_v)
+    o16 = lat[:, Rq + k_off[-1]:].contiguous()
+    y1 = linear_a8w8(o16, w["W_uvo_q"], w["W_uvo_s"], residual=xn)
+    x2 = rms_norm(y1, w["ln2"], 1e-6)
+    st = ffn.hybrid_ffn_stages(x2, ffn_w)
+    out = (st["out"].float() + y1.float()).half()
+    return out, dict(xn=xn, lat=lat, y1=y1, out=out)
+
+
 def decoder_layer_tp_rank(x16, lw, fw, info, head_dim, rank_q, world, cache_k, scale_k, cache_v, scale_v,
                           req_to_token, b_req_idx, b_seq_len, mem_index, group=None):
     """One tensor-parallel rank of the layer on the CPU (gloo collectives): the same algebra as
@@ -92,7 +108,7 @@ def decoder_layer_tp_rank(x16, lw, fw, info, head_dim, rank_q, world, cache_k, s
     s0, s1 = info["svd"]
     q0, q1 = info["rtn"]
     n_svd = info["n_svd"]
-    acc = ffn._i32_matmul(hq[:, s0:s1], fw["Wd_svd_q"]) + ffn._i32_matmul(hq[:, n_svd + q0:n_svd + q1], fw["Wd_rtn_q"])
+    acc = ffn._i32_matmul(torch.cat((hq[:, s0:s1], hq[:, n_svd + q0:n_svd + q1]), dim=1), fw["Wd_loc_q"])
     dist.all_reduce(acc, group=group)
     down = ((acc.float() * hs[:, None]) * fw["Wd_s"][None, :]).half()
     out = (down.float() + y1.float()).half()

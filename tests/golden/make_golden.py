@@ -448,9 +448,204 @@ def gen_partial_hadamard():
          x28=x2, had28=hk.to(torch.int8), rotated28=seen2["x"])
 
 
+def gen_modules():
+    """SVDLinear (ragged and uniform per-head forms), ActQuantWrapper in its rotation / quantiser settings, and the two
+    on-disk formats of the hybrid FFN: a channel-group JSON and a --save_qmodel_path style checkpoint."""
+    for m in [k for k in sys.modules if k == "utils" or k.startswith("utils.")]:
+        del sys.modules[m]
+    sys.path.insert(0, os.path.join(REF, "fake_quant"))
+    import json
+    import torch.nn as nn
+    from utils import quant_utils, hadamard_utils, svd_utils
+    from utils.svd_utils import SVDLinear
+    from utils import hybrid_ffn_utils as hf
+    g = torch.Generator().manual_seed(11)
+
+    # ---- SVDLinear, per head with a rank split (svd_utils.py:185-233, 1978-2015) and uniform (:234-268, 2017-2027)
+    H, cout, cin = 4, 16, 64
+    ranks = [16, 32, 16, 48]
+    U = [torch.randn(cout, r, generator=g).half() for r in ranks]
+    S = [torch.rand(r, generator=g).half() + 0.5 for r in ranks]
+    V = [(torch.randn(cin, r, generator=g) * 0.2).half() for r in ranks]
+    bias = (torch.randn(H * cout, generator=g) * 0.1).half()
+    res = {}
+    for fuse in ("UV", "U", "V"):
+        m = SVDLinear(U, S, V, bias=bias if fuse == "UV" else None, sigma_fuse=fuse, is_per_head_svd=True, rank_split=ranks)
+        x = torch.randn(2, 3, cin, generator=g).half()
+        res[f"ragged_{fuse}_x"], res[f"ragged_{fuse}_y"] = x, m(x)
+        res[f"ragged_{fuse}_B"] = m.BLinear.weight.data
+        res[f"ragged_{fuse}_A"] = torch.cat([a.data.reshape(-1) for a in m.ALinear])
+    r = 32
+    Uu = torch.randn(H, cout, r, generator=g).half()
+    Su = torch.rand(H, r, generator=g).half() + 0.5
+    Vu = (torch.randn(H, cin, r, generator=g) * 0.2).half()
+    m = SVDLinear(Uu, Su, Vu, sigma_fuse="UV", is_per_head_svd=True)
+    xu = torch.randn(1, 5, cin, generator=g).half()
+    res.update(uni_U=Uu, uni_S=Su, uni_V=Vu, uni_x=xu, uni_y=m(xu), uni_B=m.BLinear.weight.data, uni_A=m.ALinear.data)
+    save("svd_linear", ranks=np.array(ranks), bias=bias, U=torch.cat([u.reshape(-1) for u in U]), S=torch.cat(S),
+         V=torch.cat([v.reshape(-1) for v in V]), cout=np.int64(cout), cin=np.int64(cin), **res)
+
+    # ---- ActQuantWrapper (quant_utils.py:225-340): Linear weights int8 fake-quantised by the reference's own RTN
+    def rtn_(lin, mse=False):
+        wq = quant_utils.WeightQuantizer()
+        wq.configure(8, perchannel=True, sym=True, mse=mse)
+        wq.find_params(lin.weight.data)
+        lin.weight.data = wq.quantize(lin.weight.data).to(lin.weight.dtype)
+        return wq
+
+    res = {}
+
+    def case(tag, n_in, n_out, tokens, with_bias=False, out_bits=16, setup=None, w16=False):
+        lin = nn.Linear(n_in, n_out, bias=with_bias).half()
+        lin.weight.data = (torch.randn(n_out, n_in, generator=g) * 0.05).half()
+        if with_bias:
+            lin.bias.data = (torch.randn(n_out, generator=g) * 0.1).half()
+        if not w16:
+            rtn_(lin)
+        w = quant_utils.ActQuantWrapper(lin)
+        if setup is not None:
+            setup(w)
+        w.quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+        if out_bits < 16:
+            w.out_quantizer.configure(bits=out_bits, groupsize=-1, sym=True, clip_ratio=1.0)
+        x = torch.randn(2, tokens, n_in, generator=g).half()
+        x[0, 0] = 0
+        res[tag + "_x"], res[tag + "_W"], res[tag + "_y"] = x, lin.weight.data, w(x)
+        if with_bias:
+            res[tag + "_b"] = lin.bias.data
+        return w
+
+    case("plain", 96, 48, 3, with_bias=True, out_bits=8)
+    case("w16", 96, 48, 3, w16=True)
+
+    def full(w):
+        w.online_full_had = True
+        w.had_K, w.K = hadamard_utils.get_hadK(w.in_features)
+        if w.K > 1:
+            res["had%d" % w.K] = w.had_K.to(torch.int8)
+
+    case("full64", 64, 32, 4, setup=full)
+    case("full768", 768, 32, 4, setup=full)
+
+    def full32(w):
+        full(w)
+        w.fp32_had = True
+
+    case("full64_fp32", 64, 32, 4, setup=full32)
+
+    def partial(w):
+        w.online_partial_had, w.had_dim, w.K = True, 16, 1
+
+    case("partial", 8 * 16, 32, 4, setup=partial)
+
+    def rnd(w):
+        torch.manual_seed(3)
+        w.online_random_had = True
+        w.had_K = hadamard_utils.random_hadamard_matrix(w.in_features, "cpu").half()
+        res["random_Q"] = w.had_K
+
+    case("random", 128, 32, 4, setup=rnd)
+    wr = case("many", 96, 48, 80, with_bias=True)          # more than 64 tokens: the prefill-sized product
+    save("act_quant_wrapper", **res)
+
+    # ---- channel groups: the selector's result in the layout the analysis pass writes (hybrid_ffn_utils.py:2774-2801)
+    d_in, d_ffn, rank = 64, 192, 32
+    n_svd = d_ffn // 2
+    Wg = torch.randn(d_ffn, d_in, generator=g) * 0.1
+    Wu = torch.randn(d_ffn, d_in, generator=g) * 0.1
+    # the selector compares closed-form error proxies (hybrid_ffn_utils.py:156-176): rows with one large entry have a
+    # coarse quantisation step and go to the SVD group; with the 2-bit error model more than n_svd rows qualify and the
+    # cap keeps the n_svd with the largest margin
+    spike = torch.randint(0, d_in, (d_ffn,), generator=g)
+    rows = torch.arange(0, d_ffn, 2)
+    Wg[rows, spike[rows]] *= 6
+    Wu[rows, spike[rows]] *= 6
+    Wd = torch.randn(d_in, d_ffn, generator=g) * 0.1
+    calib = torch.randn(32, d_in, generator=g)
+    svd_idx, quant_idx, perm = hf.select_svd_channels(Wg, Wu, Wd, n_svd, calib_inps=calib, svd_rank=rank, w_bits=2, w_sym=True)
+    assert 0 < len(svd_idx) < d_ffn and len(svd_idx) % 16 == 0, len(svd_idx)
+    order = [int(v) for v in torch.randperm(d_ffn, generator=g)[:150]]
+    groups = {"layers": {}}
+    for idx in (0, 1):
+        entry = {"svd_idx": svd_idx, "quant_idx": quant_idx, "perm": perm.tolist(), "n_svd": len(svd_idx), "svd_rank": rank,
+                 "d_ffn": d_ffn, "d_in": d_in}
+        if idx == 1:
+            entry["greedy_accept_order"] = order
+        groups["layers"][str(idx)] = entry
+    path = os.path.join(HERE, "channel_groups.json")
+    with open(path, "w") as f:
+        json.dump(groups, f, indent=2)
+    back = hf.load_channel_groups(path)                      # the reference reads its own layout back
+    assert back["layers"]["0"]["perm"] == perm.tolist()
+    print("wrote channel_groups.json", len(svd_idx), len(quant_idx))
+
+    # ---- checkpoint: a layer whose mlp is the reference's HybridSVDQuantFFN, quantised by the loop of rtn_fwrd
+    # (gptq_utils.py:1168-1200) with the MSE clip search on, saved the way --save_qmodel_path does
+    # (main_llava_next_hybrid_ffn.py:365-375)
+    n_q = d_ffn - len(svd_idx)
+
+    def svd_lin(n_out):
+        m = SVDLinear.__new__(SVDLinear)
+        nn.Module.__init__(m)
+        m.BLinear = nn.Linear(d_in, rank, bias=False)
+        m.ALinear = nn.Linear(rank, n_out, bias=False)
+        m.is_ma_hack, m.original_linear, m.is_per_head_svd = False, None, False
+        m.BLinear.weight.data = torch.randn(rank, d_in, generator=g) * 0.1
+        m.ALinear.weight.data = torch.randn(n_out, rank, generator=g) * 0.1
+        m = m.half()
+        m.BLinear = quant_utils.ActQuantWrapper(m.BLinear)
+        return m
+
+    ref_lin = nn.Linear(d_in, d_ffn, bias=False).half()
+    g_svd, u_svd = svd_lin(len(svd_idx)), svd_lin(len(svd_idx))
+    g_q = hf._make_quant_linear(torch.randn(n_q, d_in, generator=g) * 0.1, d_in, ref_lin)
+    u_q = hf._make_quant_linear(torch.randn(n_q, d_in, generator=g) * 0.1, d_in, ref_lin)
+    down = quant_utils.ActQuantWrapper(nn.Linear(d_ffn, d_in, bias=False).half())
+    down.module.weight.data = (torch.randn(d_in, d_ffn, generator=g) * 0.05).half()
+    had_K, K = hadamard_utils.get_hadK(d_ffn)
+    mlp = hf.HybridSVDQuantFFN(g_svd, u_svd, g_q, u_q, down, perm, len(svd_idx), had_K=had_K, K=K)
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp = mlp
+
+    class Inner(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Layer()])
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = Inner()
+
+    model = Model()
+    quantizers = {}
+    for i, layer in enumerate(model.model.layers):
+        for name in hf.hybrid_ffn_rtn_targets():
+            module = svd_utils.rgetattr(layer, name)
+            qz = quant_utils.WeightQuantizer()
+            qz.configure(8, perchannel=True, sym=True, mse=True)
+            W = module.weight.data
+            qz.find_params(W)
+            module.weight.data = qz.quantize(W).to(device=W.device, dtype=W.dtype)
+            quantizers[f"model.layers.{i}.{name}"] = qz.cpu()
+    torch.save({"w_quantizers": quantizers, "model": model.state_dict()}, os.path.join(HERE, "qmodel_ffn.pt"))
+    for wmod in (g_svd.BLinear, u_svd.BLinear, g_q, u_q, down):
+        wmod.quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+    for wmod in (g_svd.BLinear, u_svd.BLinear):
+        wmod.out_quantizer.configure(bits=8, groupsize=-1, sym=True, clip_ratio=1.0)
+    x = torch.randn(5, d_in, generator=g).half()
+    scales = {k: v.scale.flatten().float() for k, v in quantizers.items()}
+    save("qmodel_ffn_io", x=x, y=mlp(x), **{k.replace(".", "__"): v for k, v in scales.items()})
+    print("wrote qmodel_ffn.pt", os.path.getsize(os.path.join(HERE, "qmodel_ffn.pt")), "bytes")
+
+
 if __name__ == "__main__":
     with torch.no_grad():
-        only = {"partial_hadamard": gen_partial_hadamard, "attention_block": gen_attention_block, "mixffn": gen_mixffn}
+        only = {"partial_hadamard": gen_partial_hadamard, "attention_block": gen_attention_block, "mixffn": gen_mixffn,
+                "modules": gen_modules}
         if len(sys.argv) > 2 and sys.argv[2] in only:
             only[sys.argv[2]]()
             sys.exit(0)

@@ -27,7 +27,7 @@ def test_header_symbols_are_exported_and_bound(lib):
     assert declared == set(_lib.SIGNATURES), (declared ^ set(_lib.SIGNATURES))
     for name in declared:
         assert hasattr(lib, name)
-    assert lib.lsvd_abi_version() == 2
+    assert lib.lsvd_abi_version() == 3
     assert lib.lsvd_status_string(_lib.ERR_TIMEOUT) == b"a bounded device-side wait gave up"
 
 

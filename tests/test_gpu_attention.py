@@ -170,3 +170,28 @@ def test_value_range_corners(kind):
     o_ref, _ = U.run_oracle(c)
     assert torch.isfinite(o.float()).all()
     assert rel_to_norm(o.float(), o_ref.float()) < TOL
+
+
+def test_bad_request_row_and_overlong_length_are_reported():
+    """A b_req_idx outside the request table gives an empty request (zeros) and LSVD_ERR_BOUNDS; a b_seq_len above
+    max_len_in_batch is read as max_len_in_batch and reported too.  Nothing is read out of range.  (The bad values are
+    written into the state's device tensors after it was built from valid ones: host-side indexing never sees them.)"""
+    from lsvd_b200.attention import InferState, token_decode_attention_int8_latent_absorb as attend
+    c = U.build_case(2, 4, 128, [64] * 4, [64] * 4, [64, 40], seed=14)
+    good = U.run_gpu(c)
+    dev = "cuda"
+    tens = [c[k].to(dev) for k in ("cache_k", "scale_k", "cache_v", "scale_v", "up_k", "up_v")]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def run(mutate):
+        st = InferState(2, c["max_len"], c["b_seq_len"], device=dev, req_to_token=c["req_to_token"], b_req_idx=c["b_req_idx"])
+        mutate(st)
+        status.zero_()
+        o = attend(c["q"].to(dev), st, 4, 128, *tens[:4], tens[4], tens[5], layout=c["layout"], status_word=status)
+        torch.cuda.synchronize()
+        return o.cpu()
+
+    o = run(lambda st: st.b_req_idx.copy_(torch.tensor([0, 7], dtype=torch.int32)))         # the table has two rows
+    assert status.item() == 6 and torch.equal(o[0], good[0]) and (o[1] == 0).all()
+    o = run(lambda st: st.b_seq_len.copy_(torch.tensor([64, 1000], dtype=torch.int32)))      # max_len_in_batch stays 64
+    assert status.item() == 6 and torch.isfinite(o.float()).all() and torch.equal(o[0], good[0])

@@ -18,7 +18,7 @@ def _rank_main(rank, world, port, out):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        from test_tp_cpu import _case
+        from test_tp_cpu import _case, local_cache
         from lsvd_b200.attention import InferState
         from lsvd_b200.layer import TPDecoderLayer
         from lsvd_b200.parallel import shard_layer
@@ -27,12 +27,10 @@ def _rank_main(rank, world, port, out):
         lw, fw, info = shard_layer(t["w"], t["fw"], t["kr"], t["vr"], t["rq"], world, rank)
         dev = lambda d: {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
         layer = TPDecoderLayer(dev(lw), dev(fw), info, t["D"], t["rq"], world)
-        h0, h1 = info["heads"]
-        kc, vc = info["k_cols"], info["v_cols"]
+        ck, sk, cv, sv = (x.cuda() for x in local_cache(c, info))
         st = InferState(2, c["max_len"], c["b_seq_len"], device="cuda")
         stages = {}
-        res = layer(t["x"].cuda(), c["cache_k"][:, kc[0]:kc[1]].contiguous().cuda(), c["scale_k"][:, h0:h1].contiguous().cuda(),
-                    c["cache_v"][:, vc[0]:vc[1]].contiguous().cuda(), c["scale_v"][:, h0:h1].contiguous().cuda(), st, stages=stages)
+        res = layer(t["x"].cuda(), ck, sk, cv, sv, st, stages=stages)
         torch.cuda.synchronize()
         out[rank] = (res.cpu(), stages["down_acc"].cpu(), stages["h_q"].cpu())
     finally:
