@@ -187,7 +187,10 @@ def make_workload(w, device, seed):
     B, H, D, L = w["batch"], w["heads"], w["head_dim"], w["context"]
     kr = synth.ragged_ranks(H, 64, seed=0) if w["ragged"] else [64] * H
     vr = synth.ragged_ranks(H, 64, seed=1) if w["ragged"] else [64] * H
-    lay = LatentCacheLayout(kr, vr, head_major=w.get("cache_layout", "slot") == "head")
+    shared = bool(w.get("shared_kv"))          # one cached latent per head serves as K and as V latent
+    if shared:
+        vr = kr
+    lay = LatentCacheLayout(kr, vr, head_major=w.get("cache_layout", "slot") == "head", shared_kv=shared)
     seq = L + 1                      # context plus the slot of the decoding token, as the reference's benchmark
     grow = DECODE_TOKENS if w.get("full") else 0     # slots reserved for the tokens the decode loop appends
     n_slots = B * (seq + grow)
@@ -197,7 +200,7 @@ def make_workload(w, device, seed):
     for s0 in range(0, n_slots, chunk):
         n = min(chunk, n_slots - s0)
         lk = torch.randn(n, lay.sum_k, generator=g, device=device, dtype=torch.float32).half()
-        lv = torch.randn(n, lay.sum_v, generator=g, device=device, dtype=torch.float32).half()
+        lv = None if shared else torch.randn(n, lay.sum_v, generator=g, device=device, dtype=torch.float32).half()
         dest = torch.arange(s0, s0 + n, dtype=torch.int32, device=device)
         cache_append(lay, lk, lv, dest, ck, sk, cv, sv)
     up_k = (torch.randn(lay.sum_k, D, generator=g, device=device) / 8).half()
@@ -215,8 +218,9 @@ def algorithmic_bytes(wl):
     fp16 scales and the slot indices.  With a growing context: the mean over the decode loop's lengths."""
     lay, B, H = wl["layout"], wl["B"], wl["H"]
     tokens = B * (wl["seq"] + (wl["grow"] - 1) / 2.0) if wl.get("grow") else B * wl["seq"]
-    cache = tokens * (lay.sum_k + lay.sum_v)
-    scales = tokens * H * 2 * 2
+    sides = 1 if lay.shared_kv else 2          # a shared latent and its scale are stored, and must be read, once
+    cache = tokens * (lay.sum_k + (0 if lay.shared_kv else lay.sum_v))
+    scales = tokens * H * 2 * sides
     slots = tokens * 4
     return int(cache + scales + slots)
 
@@ -250,6 +254,7 @@ def run_ours(args, rank, world, local):
         dist.init_process_group("nccl", device_id=dev)
     w = dict(WORKLOADS[args.workload])
     w["cache_layout"] = args.cache_layout
+    w["shared_kv"] = args.shared_kv
     has_attn = not w.get("ffn_only", False)
     has_ffn = w.get("ffn", False)
     if w.get("ffn_only"):
@@ -282,7 +287,7 @@ def run_ours(args, rank, world, local):
         # residual, hybrid FFN with its RMSNorm prologue + residual
         from lsvd_b200.layer import LSVDDecoderLayer, make_layer_weights
         RANK_Q = 64
-        lw = make_layer_weights(H * D, H, D, RANK_Q, lay.k_ranks, lay.v_ranks, seed=70 + rank)
+        lw = make_layer_weights(H * D, H, D, RANK_Q, lay.k_ranks, lay.v_ranks, seed=70 + rank, shared_kv=lay.shared_kv)
         layer = LSVDDecoderLayer(lay, D, RANK_Q, {k: v.to(dev) for k, v in lw.items()}, ffns[0])
         proj_bytes = lw["W_lat_q"].numel() + lw["W_uvo_q"].numel()
     # per-step inputs; host copies live in pinned memory for the end-to-end leg
@@ -319,7 +324,7 @@ def run_ours(args, rank, world, local):
             return
         if has_attn:
             q, lk, lv = inputs
-            cache_append(lay, lk, lv, st.mem_index, wl["ck"], wl["sk"], wl["cv"], wl["sv"])
+            cache_append(lay, lk, None if lay.shared_kv else lv, st.mem_index, wl["ck"], wl["sk"], wl["cv"], wl["sv"])
             token_decode_attention_int8_latent_absorb(q, st, H, D, wl["ck"], wl["sk"], wl["cv"], wl["sv"], wl["up_k"],
                                                       wl["up_v"], layout=lay, out=attn_out, workspace=ws,
                                                       status_word=status, timing_events=ev)
@@ -449,7 +454,7 @@ def run_ours(args, rank, world, local):
         "data": "synthetic",
         "config": bench_config(args, w, B, world),
         "config_detail": {"step": " + ".join(what), "launch": "CUDA graph replay of the step",
-                          "cache_layout": args.cache_layout if has_attn else None,
+                          "cache_layout": args.cache_layout if has_attn else None, "shared_kv_latent": bool(args.shared_kv) if has_attn else None,
                           "l2": "inputs larger than L2: every step streams %.0f MB of cache/weights%s"
                                 % (step_bytes / 1e6, "" if has_attn else " (three weight copies cycled, 300 MB)")},
         "e2e": {"value": tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -794,6 +799,18 @@ def run_tp(args, rank, world, local):
     kt = torch.tensor([k_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(kt, op=dist.ReduceOp.MAX)
     k_ms = kt.item()
+    # where the step's time goes on rank 0: events around the runs of launches and the collectives
+    seg_names = ("attention_block", "all_reduce_attn", "gate_up", "all_gather_h", "hadamard_down", "all_reduce_ffn", "finish")
+    seg_sum = [0.0] * len(seg_names)
+    barrier()
+    for i in range(args.steps):
+        evs = []
+        x_in.copy_(xs[i % 4], non_blocking=True)
+        layer(x_in, ck, sk, cv, sv, st, segment_events=evs)
+        torch.cuda.synchronize()
+        for j in range(len(seg_names)):
+            seg_sum[j] += evs[j].elapsed_time(evs[j + 1]) * 1e3 / args.steps
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
     local_bytes = ck.numel() + cv.numel() + (sk.numel() + sv.numel()) * 2 + sum(
         v.numel() for v in list(lw.values()) + list(fw.values()) if isinstance(v, torch.Tensor) and v.dtype == torch.int8)
@@ -813,7 +830,8 @@ def run_tp(args, rank, world, local):
                                   "heads, row-parallel output projection + all-reduce, column-parallel hybrid FFN gate/up, "
                                   "all-gather of the hidden vector, Hadamard 128 x 108 + A8, row-parallel int32 down projection + "
                                   "all-reduce",
-                          "launch": "eager launches (about 20 host calls per step), NCCL collectives on the same stream",
+                          "launch": ("four CUDA-graph replays per step (the launches between the collectives) + three NCCL collectives, one stream"
+                                     if layer.use_graphs else "eager launches (about 20 host calls per step), NCCL collectives on the same stream"),
                           "cache_layout": args.cache_layout,
                           "l2": "each rank streams %.0f MB of cache and weights per step" % (local_bytes / 1e6)},
         "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": x_in.numel() * 2,
@@ -824,6 +842,7 @@ def run_tp(args, rank, world, local):
                      "traffic": None, "algorithmic_bytes_per_launch": stream_bytes, "kernel_us": k_ms * 1e3},
         "parts": {"step_us": ms_step * 1e3, "bytes_per_gpu_per_step": local_bytes,
                   "step_hbm_gbs_per_gpu": local_bytes / (ms_step * 1e-3) / 1e9,
+                  "segments_us_rank0": dict(zip(seg_names, seg_sum)),
                   "value_leg": spread(t_dev, args.steps), "e2e_leg": spread(t_e2e, args.steps)},
         "clocks": clocks,
     }
@@ -1178,6 +1197,8 @@ def main():
     ap.add_argument("--cache-layout", default="slot", choices=["head", "slot"],
                     help="latent cache stored head by head ([H][slots][r_h], the layout the streaming kernel prefers) or "
                          "slot by slot ([slots][sum r], the reference's)")
+    ap.add_argument("--shared-kv", action="store_true",
+                    help="attention / layer workloads: one cached latent per head serving as K and V latent (half the cache)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.workload is None:

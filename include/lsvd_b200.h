@@ -315,6 +315,15 @@ typedef struct lsvd_heads_hadamard_quant_args {
 } lsvd_heads_hadamard_quant_args;
 int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* args, void* stream);
 
+/* The same rotation when the heads are sharded over tensor-parallel ranks.  x fp16 [rows, n_local * head_dim] holds the
+ * heads head_ids[0 .. n_local) (HOST array of global head indices); out fp32 [rows, heads * head_dim] (contiguous) receives
+ * this rank's terms of every output head, already scaled by 1 / sqrt(heads): out[h', d] = s * sum_j S[h', head_ids[j]] x[j, d]
+ * with S the Sylvester signs (heads a power of two) or had_K (device fp16 [heads, heads] of +-1).  The sum of the ranks'
+ * rows (one all-reduce) is the rotated row; lsvd_act_quant with x_f32 rounds it to fp16 and quantises it.  No
+ * counterpart in the reference (it has no tensor parallelism); the single-GPU form is lsvd_heads_hadamard_quant. */
+int lsvd_heads_hadamard_partial(const void* x, int64_t x_row_stride, const int32_t* head_ids, int32_t n_local,
+                                int32_t heads, int32_t head_dim, const void* had_K, float* out, int32_t rows, void* stream);
+
 /* Weight-streaming W8A8 product for 1..64 tokens: acc[m, n] = sum_k a[m, k] * w[n, k] (int32, exact),
  * optionally for a second weight matrix w2 (with its own activations a2, or the same ones) in the same pass.
  *   epilogue 0: out[m, out_col + n] = fp16((acc * a_scale[m]) * w_scale[n])              (a quantised Linear)

@@ -200,6 +200,8 @@ SIGNATURES = {
     "lsvd_w8a8_gemv": (C.c_int, [C.POINTER(GemvArgs), C.c_void_p]),
     "lsvd_dequant_residual": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32,
                                         C.c_int32, C.c_void_p]),
+    "lsvd_heads_hadamard_partial": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                              C.c_void_p, C.c_int32, C.c_void_p]),
     "lsvd_per_head_up": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_int64,
                                    C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "lsvd_i8gemm_prefill": (C.c_int, [C.POINTER(I8GemmArgs), C.c_void_p]),

@@ -44,14 +44,22 @@ class LatentCacheLayout:
     R gives exactly the reference's ``[N_slots, H, R]`` tensor.
     """
 
-    def __init__(self, k_ranks: Sequence[int], v_ranks: Optional[Sequence[int]] = None, head_major: bool = False):
-        """``head_major``: the cache is stored head by head -- ``cache [H][N_slots][r_h]`` as one flat int8 buffer of
+    def __init__(self, k_ranks: Sequence[int], v_ranks: Optional[Sequence[int]] = None, head_major: bool = False,
+                 shared_kv: bool = False):
+        """``shared_kv``: K and V of a head are up-projections of ONE cached latent, as when the reference builds the
+        Q, K and V factors over a shared ``BLinear`` (fake_quant/utils/svd_utils.py:1505-1507): the cache holds that latent
+        once (half the bytes); ``alloc`` returns the same tensors for the K and the V side, ``cache_append`` writes them
+        once, and the attention reads its score and value operands from the same rows.
+        ``head_major``: the cache is stored head by head -- ``cache [H][N_slots][r_h]`` as one flat int8 buffer of
         ``N_slots * sum(r)`` bytes and scales ``[H, N_slots]`` -- instead of one row per slot (``[N_slots, sum r]``,
         scales ``[N_slots, H]``, the reference's layout).  Same values; the rows a head reads for consecutive slots are
         then contiguous in memory, which the streaming kernel's loads prefer."""
         self.head_major = bool(head_major)
+        self.shared_kv = bool(shared_kv)
         v_ranks = list(k_ranks if v_ranks is None else v_ranks)
         k_ranks = list(k_ranks)
+        if self.shared_kv and k_ranks != v_ranks:
+            raise ValueError("a shared K/V latent has one rank per head")
         if len(k_ranks) != len(v_ranks) or not k_ranks:
             raise ValueError("k_ranks and v_ranks must list the same, non-zero number of heads")
         if len(k_ranks) > _lib.LSVD_MAX_HEADS:
@@ -75,10 +83,24 @@ class LatentCacheLayout:
         return cls([rank_k] * num_heads, [rank_v if rank_v is not None else rank_k] * num_heads)
 
     def as_head_major(self):
-        return LatentCacheLayout(self.k_ranks, self.v_ranks, head_major=True)
+        return LatentCacheLayout(self.k_ranks, self.v_ranks, head_major=True, shared_kv=self.shared_kv)
 
     def alloc(self, num_slots: int, device="cuda"):
         """Empty (cache_k, scale_k, cache_v, scale_v) for ``num_slots`` slots in this layout."""
+        if self.shared_kv:
+            one = LatentCacheLayout(self.k_ranks, None, head_major=self.head_major)
+            ck, sk, _, _ = one._alloc_sides(num_slots, device, ("k",))
+            return ck, sk, ck, sk
+        return self._alloc_sides(num_slots, device, ("k", "v"))
+
+    def _alloc_sides(self, num_slots: int, device, sides):
+        if sides == ("k",):
+            total = self.sum_k
+            if self.head_major:
+                return (torch.empty(num_slots * total, dtype=torch.int8, device=device),
+                        torch.empty(self.num_heads, num_slots, dtype=torch.float16, device=device), None, None)
+            return (torch.empty(num_slots, total, dtype=torch.int8, device=device),
+                    torch.empty(num_slots, self.num_heads, dtype=torch.float16, device=device), None, None)
         if self.head_major:
             return (torch.empty(num_slots * self.sum_k, dtype=torch.int8, device=device),
                     torch.empty(self.num_heads, num_slots, dtype=torch.float16, device=device),
@@ -146,8 +168,13 @@ def cache_append(layout: LatentCacheLayout, latent_k, latent_v, dest_loc, cache_
     """Quantise this step's K and V latents and write them to cache rows ``dest_loc`` in one launch.
 
     ``latent_* [T, sum(r)]`` fp16 (head h in columns off[h]:off[h+1]); ``cache_* [N_slots, sum(r)]`` int8;
-    ``scale_* [N_slots, H]`` fp16; ``dest_loc [T]`` int32.  Either side may be None.
+    ``scale_* [N_slots, H]`` fp16; ``dest_loc [T]`` int32.  Either side may be None.  With a shared K/V latent
+    (``layout.shared_kv``) the one latent is ``latent_k`` and ``latent_v`` must be None or the same tensor.
     """
+    if layout.shared_kv:
+        if latent_v is not None and latent_v.data_ptr() != latent_k.data_ptr():
+            raise ValueError("shared K/V latent: pass the latent once (latent_v None)")
+        latent_v = None
     _require_cuda(latent_k, latent_v, dest_loc, cache_k, cache_v)
     lib = _lib.load()
     if dest_loc.dtype != torch.int32 or not dest_loc.is_contiguous():

@@ -5,7 +5,7 @@
 Needs a checkout of SAI-Lab-NYU/LSVD (it is not part of this repository).  The reference's Triton layer -- its
 ``Int8AttentionBlock`` (kernels/layer_bench/ffn_kernel/baseline_kernel.py:56-145) and the ``mixffn`` provider
 (kernels/layer_bench/ffn_kernel/mix_ffn_kernel.py:2223-2246) -- and this library's drop-ins for the same two modules
-(``lsvd_b200.Int8AttentionBlock.from_module``, ``b200_mixffn``) are built from the SAME parameters, fed the SAME synthetic
+(``lsvd_b200.Int8AttentionBlock.from_module``, ``MixedFFNGateUpDenseLatentFused.from_module``) are built from the SAME parameters, fed the SAME synthetic
 cache and hidden states (the reference's generators, kernels/layer_bench/benchmark_triton_int8_layer.py:103-149), compared
 value by value, and timed by the reference's own harness function ``bench_ms`` (CUDA-graph replay + ``triton.testing.do_bench``,
 kernels/layer_bench/ffn_kernel/utils.py:687-712) in one process.  One JSON line is printed (and written to ``--out``).
@@ -65,7 +65,7 @@ def main() -> None:
     mix = importlib.import_module("ffn_kernel.mix_ffn_kernel")
     base = importlib.import_module("ffn_kernel.baseline_kernel")
     import lsvd_b200
-    from lsvd_b200.mixffn import b200_mixffn
+    from lsvd_b200.mixffn import MixedFFNGateUpDenseLatentFused
 
     dev = "cuda"
     gen = torch.Generator(device=dev).manual_seed(0)
@@ -103,8 +103,28 @@ def main() -> None:
         f_ref = ref_ffn(a_ref, ffn_module)
         torch.cuda.synchronize()
         res["reference_ffn_first_call_s"] = time.time() - t0
+        # this library's module takes over the int8 weights the reference derived from the fp16 module (its own SVD and
+        # quantisation), so both sides multiply the same integers
+        ref_mixed = mix.get_mixed_gateup_v8_ffn(ffn_module)
+        our_mixed = MixedFFNGateUpDenseLatentFused.from_module(ref_mixed)
+        b200_mixffn = lambda t, _module=None: our_mixed(t)
         f_our = b200_mixffn(a_ref, ffn_module)
         res["ffn_rel_err"] = rel(f_our, f_ref)
+        # stage by stage, each side on its own intermediates (integers: fraction of entries that differ and the largest
+        # difference; floating point: max difference over the reference's norm)
+        st_ref, st_our = ref_mixed.forward_stages(a_ref), our_mixed.forward_stages(a_ref)
+        stages = {}
+        for name, tr in st_ref.items():
+            to = st_our.get(name)
+            if not isinstance(tr, torch.Tensor) or not isinstance(to, torch.Tensor) or tr.numel() != to.numel():
+                continue
+            to = to.reshape(tr.shape)
+            if tr.dtype in (torch.int8, torch.int32, torch.int16, torch.int64):
+                d = (tr.long() - to.long()).abs()
+                stages[name] = {"differ": float((d > 0).float().mean()), "max": int(d.max())}
+            else:
+                stages[name] = {"rel": rel(to, tr)}
+        res["ffn_stages"] = stages
         res["tolerance"] = "max|ours - reference| / ||reference||_2 (2e-3 is the fp16 output bound)"
         # ---- time: the same callables the reference's harness times ----
         def timed(fn):

@@ -12,7 +12,12 @@
 // latents are the A operand straight from the cache rows, the head's slice of W_uk is staged transposed in
 // shared memory once per block as the B operand, and a lane ends up with both members of every rotary pair of
 // its columns, so rotation and the dot product with the query need no exchange beyond a reduction over the four
-// lanes of a quad.
+// lanes of a quad.  Rotation, dequantisation and the query are folded per rotary pair (columns i and i + D/2, integer
+// sums a0, a1, column scales w0, w1, rotated query q0, q1, angle of the key's position (c, s)):
+//   (k0 c - k1 s) q0 + (k1 c + k0 s) q1  with  k = a * s_k * w   =   s_k * [ c (a0 w0 q0 + a1 w1 q1) + s (a0 w0 q1 - a1 w1 q0) ]
+// so a key costs four constants per pair (staged once per block) and six multiply-adds instead of a dequantised, rounded
+// and rotated fp16 key; the fp16 roundings of the rebuilt key that the reference makes on the way are not reproduced
+// (they move a score by about 1e-5 of its value).
 #include <algorithm>
 #include <cmath>
 
@@ -60,7 +65,7 @@ __global__ void rope_table_kernel(__half2* table, int max_len, int D, float thet
 }
 
 template <int D>
-__global__ void __launch_bounds__(kRopeWarps * 32) rope_recon_kernel(const __grid_constant__ RopeParams p) {
+__global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __grid_constant__ RopeParams p) {
   extern __shared__ __align__(16) uint8_t rope_smem[];
   constexpr int D2 = D >> 1;
   const int rk = p.rk, rv = p.rv;
@@ -68,7 +73,8 @@ __global__ void __launch_bounds__(kRopeWarps * 32) rope_recon_kernel(const __gri
   int8_t* wT = reinterpret_cast<int8_t*>(rope_smem);           // [D][pitch]: column c of the head, ranks contiguous
   float* sw = reinterpret_cast<float*>(rope_smem + ((D * pitch + 15) & ~15));     // [D] column scales
   float* qrot = sw + D;                                        // [D] rotated query (fp16 values)
-  float* wpart = qrot + D;                                     // [kRopeWarps][2 + 128]
+  float4* cst = reinterpret_cast<float4*>(qrot + D);           // [D/2] (w0 q0, w1 q1, w0 q1, w1 q0) of every rotary pair
+  float* wpart = reinterpret_cast<float*>(cst + D2);           // [kRopeWarps][2 + 128]
   grid_dependency_sync();
 
   const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -101,18 +107,27 @@ __global__ void __launch_bounds__(kRopeWarps * 32) rope_recon_kernel(const __gri
     }
   }
   __syncthreads();
+  for (int i = threadIdx.x; i < D2; i += blockDim.x)
+    cst[i] = make_float4(sw[i] * qrot[i], sw[i + D2] * qrot[i + D2], sw[i] * qrot[i + D2], sw[i + D2] * qrot[i]);
+  __syncthreads();
 
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
   constexpr int ntile = D >> 3;        // 8-column MMA tiles of the head
   constexpr int npair = ntile >> 1;    // tile j pairs with tile j + npair (columns c and c + D/2)
   float m = -INFINITY, l = 0.f;
-  float accv[4] = {0.f, 0.f, 0.f, 0.f};          // ranks lane, lane + 32, lane + 64, lane + 96 of the value latent
+  // value latents: lane (tg = lane / 8, ch = lane % 8) adds tokens 4 i + tg of a tile into ranks 8 ch .. 8 ch + 7 and
+  // 64 + 8 ch .. 64 + 8 ch + 7; the four token groups are summed once, after the loop
+  float accv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) accv[i] = 0.f;
+  const int tg = lane >> 3, ch = lane & 7;
+  int next_slot = r2t[min(start + warp * 16 + (lane & 15), end - 1)];
 
   for (int t0 = start + warp * 16; t0 < end; t0 += kRopeWarps * 16) {
     // slot of token t0 + (lane & 15), kept by every lane for the shuffles below; lanes past the end reuse the
     // tile's first token (a real row) and their scores are masked
-    const int my_tok = t0 + (lane & 15);
-    int my_slot = r2t[min(my_tok, end - 1)];
+    int my_slot = next_slot;
+    next_slot = r2t[min(t0 + kRopeWarps * 16 + (lane & 15), end - 1)];      // the next tile's rows can then be requested at once
     if (my_slot < 0 || my_slot >= p.num_slots) {
       report_status(p.status_word, LSVD_ERR_BOUNDS);
       my_slot = 0;
@@ -142,7 +157,7 @@ __global__ void __launch_bounds__(kRopeWarps * 32) rope_recon_kernel(const __gri
       }
     }
 
-    // ---- dequantise to fp16, rotate at the logical position, dot with the rotated query ----
+    // ---- rotation at the logical position and the dot product with the rotated query, folded (see the top) ----
     const float sk_lo = __half2float(p.scale_k[slot_lo * p.sk_slot_stride + hk]);
     const float sk_hi = __half2float(p.scale_k[slot_hi * p.sk_slot_stride + hk]);
     const __half2* tab_lo = p.table + static_cast<int64_t>(min(t0 + g, end - 1)) * D2;
@@ -150,31 +165,31 @@ __global__ void __launch_bounds__(kRopeWarps * 32) rope_recon_kernel(const __gri
     float dot_lo = 0.f, dot_hi = 0.f;
 #pragma unroll
     for (int j = 0; j < npair; ++j) {
-      {
-        const int c = 8 * j + 2 * t;                 // columns c, c + 1 pair with c + D/2, c + 1 + D/2
-        const float2 cs0_lo = __half22float2(tab_lo[c]), cs1_lo = __half22float2(tab_lo[c + 1]);
-        const float2 cs0_hi = __half22float2(tab_hi[c]), cs1_hi = __half22float2(tab_hi[c + 1]);
+      const int c = 8 * j + 2 * t;                   // pairs c and c + 1: (cos, sin) of both in one 8-byte load
+      const uint2 raw_lo = __ldg(reinterpret_cast<const uint2*>(tab_lo + c));
+      const uint2 raw_hi = __ldg(reinterpret_cast<const uint2*>(tab_hi + c));
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float w0 = sw[c + e], w1 = sw[c + e + D2];
-          const float q0 = qrot[c + e], q1 = qrot[c + e + D2];
-          {
-            const float k0 = __half2float(__float2half_rn((static_cast<float>(acc[j][e]) * sk_lo) * w0));
-            const float k1 = __half2float(__float2half_rn((static_cast<float>(acc[j + npair][e]) * sk_lo) * w1));
-            const float2 cs = e ? cs1_lo : cs0_lo;
-            dot_lo = fmaf(k0 * cs.x - k1 * cs.y, q0, dot_lo);
-            dot_lo = fmaf(k1 * cs.x + k0 * cs.y, q1, dot_lo);
-          }
-          {
-            const float k0 = __half2float(__float2half_rn((static_cast<float>(acc[j][2 + e]) * sk_hi) * w0));
-            const float k1 = __half2float(__float2half_rn((static_cast<float>(acc[j + npair][2 + e]) * sk_hi) * w1));
-            const float2 cs = e ? cs1_hi : cs0_hi;
-            dot_hi = fmaf(k0 * cs.x - k1 * cs.y, q0, dot_hi);
-            dot_hi = fmaf(k1 * cs.x + k0 * cs.y, q1, dot_hi);
-          }
+      for (int e = 0; e < 2; ++e) {
+        const float4 k4 = cst[c + e];
+        const uint32_t wl = e ? raw_lo.y : raw_lo.x, wh = e ? raw_hi.y : raw_hi.x;
+        const float2 cs_lo = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wl & 0xffffu))),
+                                         __half2float(__ushort_as_half(static_cast<unsigned short>(wl >> 16))));
+        const float2 cs_hi = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wh & 0xffffu))),
+                                         __half2float(__ushort_as_half(static_cast<unsigned short>(wh >> 16))));
+        {
+          const float a0 = static_cast<float>(acc[j][e]), a1 = static_cast<float>(acc[j + npair][e]);
+          dot_lo = fmaf(cs_lo.x, fmaf(a1, k4.y, a0 * k4.x), dot_lo);
+          dot_lo = fmaf(cs_lo.y, fmaf(-a1, k4.w, a0 * k4.z), dot_lo);
+        }
+        {
+          const float a0 = static_cast<float>(acc[j][2 + e]), a1 = static_cast<float>(acc[j + npair][2 + e]);
+          dot_hi = fmaf(cs_hi.x, fmaf(a1, k4.y, a0 * k4.x), dot_hi);
+          dot_hi = fmaf(cs_hi.y, fmaf(-a1, k4.w, a0 * k4.z), dot_hi);
         }
       }
     }
+    dot_lo *= sk_lo;
+    dot_hi *= sk_hi;
     dot_lo += __shfl_xor_sync(0xffffffffu, dot_lo, 1);
     dot_lo += __shfl_xor_sync(0xffffffffu, dot_lo, 2);
     dot_hi += __shfl_xor_sync(0xffffffffu, dot_hi, 1);
@@ -199,29 +214,52 @@ __global__ void __launch_bounds__(kRopeWarps * 32) rope_recon_kernel(const __gri
     const float w_lo = ok_lo ? p_lo * __half2float(p.scale_v[slot_lo * p.sv_slot_stride + hk]) : 0.f;
     const float w_hi = ok_hi ? p_hi * __half2float(p.scale_v[slot_hi * p.sv_slot_stride + hk]) : 0.f;
 
-    // ---- values: lane owns ranks lane + 32 i; token weights and slots come by shuffle ----
+    // ---- values: 8-byte loads, four tokens of the tile at a time; token weights and slots come by shuffle ----
 #pragma unroll
-    for (int i = 0; i < 4; ++i) accv[i] *= corr;
-#pragma unroll 4
-    for (int r = 0; r < 16; ++r) {
-      const float w = __shfl_sync(0xffffffffu, (r < 8) ? w_lo : w_hi, (r & 7) << 2);
+    for (int i = 0; i < 16; ++i) accv[i] *= corr;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = 4 * it + tg;                       // this lane's token of the tile
+      const float wa = __shfl_sync(0xffffffffu, w_lo, (r & 7) << 2), wb = __shfl_sync(0xffffffffu, w_hi, (r & 7) << 2);
+      const float w = r < 8 ? wa : wb;
       const int slot = __shfl_sync(0xffffffffu, my_slot, r);
-      const int8_t* vrow = p.cache_v + slot * p.v_slot_stride + hk * p.v_head_stride;
+      const int8_t* vrow = p.cache_v + slot * p.v_slot_stride + hk * p.v_head_stride + 8 * ch;
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (lane + 32 * i < rv) accv[i] = fmaf(w, static_cast<float>(vrow[lane + 32 * i]), accv[i]);
+      for (int half = 0; half < 2; ++half) {
+        if (64 * half + 8 * ch < rv) {
+          const uint2 v = __ldg(reinterpret_cast<const uint2*>(vrow + 64 * half));
+          float* a = accv + 8 * half;
+          a[0] = fmaf(w, s8_to_f32<0>(v.x), a[0]);
+          a[1] = fmaf(w, s8_to_f32<1>(v.x), a[1]);
+          a[2] = fmaf(w, s8_to_f32<2>(v.x), a[2]);
+          a[3] = fmaf(w, s8_to_f32<3>(v.x), a[3]);
+          a[4] = fmaf(w, s8_to_f32<0>(v.y), a[4]);
+          a[5] = fmaf(w, s8_to_f32<1>(v.y), a[5]);
+          a[6] = fmaf(w, s8_to_f32<2>(v.y), a[6]);
+          a[7] = fmaf(w, s8_to_f32<3>(v.y), a[7]);
+        }
+      }
     }
   }
 
-  // ---- merge the block's warps (log-sum-exp), write the run's partial result ----
+  // ---- the four token groups of a warp, then the block's warps (log-sum-exp); write the run's partial result ----
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    accv[i] += __shfl_xor_sync(0xffffffffu, accv[i], 8);
+    accv[i] += __shfl_xor_sync(0xffffffffu, accv[i], 16);
+  }
   float* mine = wpart + warp * (2 + 128);
   if (lane == 0) {
     mine[0] = m;
     mine[1] = l;
   }
+  if (tg == 0) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    if (lane + 32 * i < rv) mine[2 + lane + 32 * i] = accv[i];
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (64 * half + 8 * ch + e < rv) mine[2 + 64 * half + 8 * ch + e] = accv[8 * half + e];
+  }
   __syncthreads();
   float M = -INFINITY;
 #pragma unroll
@@ -287,6 +325,7 @@ extern "C" int lsvd_attn_decode_rope(const lsvd_attn_rope_args* a, void* stream)
     return LSVD_ERR_INVALID_ARG;
   if (a->num_slots <= 0 || a->max_len_in_batch < 0 || a->block_seq < 16 || (a->block_seq % 16)) return LSVD_ERR_INVALID_ARG;
   if (!aligned(a->cache_k, 8) || (a->cache_k_slot_stride % 8) || (a->cache_k_head_stride % 8)) return LSVD_ERR_INVALID_ARG;
+  if (!aligned(a->cache_v, 8) || (a->cache_v_slot_stride % 8) || (a->cache_v_head_stride % 8)) return LSVD_ERR_INVALID_ARG;
   if (!aligned(a->wk, 16) || (a->wk_row_stride % 16)) return LSVD_ERR_INVALID_ARG;
   const size_t need = lsvd_attn_decode_rope_workspace_bytes(a->batch, a->num_q_heads, a->head_dim, a->rank_v,
                                                             a->max_len_in_batch, a->block_seq);
@@ -309,8 +348,14 @@ extern "C" int lsvd_attn_decode_rope(const lsvd_attn_rope_args* a, void* stream)
   p.status_word = a->status_word;
   p.batch = a->batch; p.heads = a->num_q_heads; p.kv_heads = a->num_kv_heads; p.group = a->num_q_heads / a->num_kv_heads;
   p.head_dim = a->head_dim; p.rk = a->rank_k; p.rv = a->rank_v; p.num_slots = a->num_slots;
-  p.max_len = a->max_len_in_batch; p.block_seq = a->block_seq;
-  p.nsplit = rope_splits(a->max_len_in_batch, a->block_seq);
+  // Tokens per block: the caller's block_seq, doubled (up to 1024) while the grid still holds eight blocks per SM: every
+  // block stages its head's slice of W_uk and the query constants first, which longer runs amortise.  The workspace was
+  // sized for block_seq, so fewer, longer runs fit.
+  int run = a->block_seq;
+  while (run < 1024 && static_cast<int64_t>(rope_splits(a->max_len_in_batch, run * 2)) * a->num_q_heads * a->batch >= 148 * 8)
+    run *= 2;
+  p.max_len = a->max_len_in_batch; p.block_seq = run;
+  p.nsplit = rope_splits(a->max_len_in_batch, run);
   const float sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / std::sqrt(static_cast<float>(a->head_dim));
   p.score_scale = sm_scale * 1.4426950408889634f;
   p.theta = a->rope_theta > 0.f ? a->rope_theta : 10000.0f;
@@ -319,7 +364,7 @@ extern "C" int lsvd_attn_decode_rope(const lsvd_attn_rope_args* a, void* stream)
     LSVD_CUDA_TRY(launch_chained(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, st, 1, true, p.table,
                                  a->max_len_in_batch, a->head_dim, p.theta));
     const int pitch = a->rank_k + 16;
-    const int smem = ((a->head_dim * pitch + 15) & ~15) + (2 * a->head_dim + kRopeWarps * (2 + 128)) * 4;
+    const int smem = ((a->head_dim * pitch + 15) & ~15) + (2 * a->head_dim + 2 * a->head_dim + kRopeWarps * (2 + 128)) * 4;
     void (*kern)(RopeParams) = a->head_dim == 128 ? rope_recon_kernel<128>
                                : (a->head_dim == 64 ? rope_recon_kernel<64> : rope_recon_kernel<32>);
     if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));

@@ -768,6 +768,62 @@ extern "C" int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* a
   return LSVD_OK;
 }
 
+// ----------------------------------------------------------------------------------------------
+// Hadamard across heads when the heads are sharded over tensor-parallel ranks
+// ----------------------------------------------------------------------------------------------
+// The transform is linear in its input heads: y[h', d] = s * sum_h S[h', h] x[h, d].  A rank that holds the heads
+// head_ids[0..n_local) adds their terms for EVERY output head h' into an fp32 row; the sum of the ranks' rows (one
+// all-reduce) is the rotated row, which lsvd_act_quant (x_f32) rounds to fp16 once and quantises.
+struct HeadsHadPartialParams {
+  const __half* x; int64_t x_row_stride;
+  const __half* had_K;             // [heads, heads] +-1, or NULL: Sylvester signs (-1)^popcount(h' & h)
+  float* out;                      // [rows, heads * head_dim]
+  int32_t rows, heads, head_dim, n_local;
+  float scale;
+  int32_t head_ids[LSVD_MAX_HEADS];
+};
+
+__global__ void __launch_bounds__(256) heads_hadamard_partial_kernel(const __grid_constant__ HeadsHadPartialParams p) {
+  const int r = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;            // output column h' * head_dim + d
+  if (i >= p.heads * p.head_dim) return;
+  const int ho = i / p.head_dim, d = i - ho * p.head_dim;
+  const __half* x = p.x + r * p.x_row_stride + d;
+  float acc = 0.f;
+  for (int j = 0; j < p.n_local; ++j) {
+    const int h = p.head_ids[j];
+    const float v = __half2float(x[j * p.head_dim]);
+    const bool neg = p.had_K != nullptr ? (__half2float(p.had_K[ho * p.heads + h]) < 0.f) : ((__popc(ho & h) & 1) != 0);
+    acc += neg ? -v : v;
+  }
+  p.out[static_cast<int64_t>(r) * p.heads * p.head_dim + i] = acc * p.scale;
+}
+
+extern "C" int lsvd_heads_hadamard_partial(const void* x, int64_t x_row_stride, const int32_t* head_ids, int32_t n_local,
+                                           int32_t heads, int32_t head_dim, const void* had_K, float* out, int32_t rows,
+                                           void* stream) {
+  using namespace lsvd;
+  if (rows < 0 || heads <= 1 || heads > LSVD_MAX_HEADS || head_dim <= 0 || n_local < 0 || n_local > heads || head_ids == nullptr)
+    return LSVD_ERR_INVALID_ARG;
+  if (rows == 0) return LSVD_OK;
+  if (x == nullptr || out == nullptr || rows > 65535) return LSVD_ERR_INVALID_ARG;
+  if (had_K == nullptr && !is_pow2(heads)) return LSVD_ERR_UNSUPPORTED;
+  HeadsHadPartialParams p{};
+  p.x = static_cast<const __half*>(x); p.x_row_stride = x_row_stride;
+  p.had_K = static_cast<const __half*>(had_K);
+  p.out = out;
+  p.rows = rows; p.heads = heads; p.head_dim = head_dim; p.n_local = n_local;
+  p.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(heads)));
+  for (int j = 0; j < n_local; ++j) {
+    if (head_ids[j] < 0 || head_ids[j] >= heads) return LSVD_ERR_INVALID_ARG;
+    p.head_ids[j] = head_ids[j];
+  }
+  const int cols = heads * head_dim;
+  heads_hadamard_partial_kernel<<<dim3((cols + 255) / 256, rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  LSVD_CUDA_TRY(cudaGetLastError());
+  return LSVD_OK;
+}
+
 extern "C" size_t lsvd_hadamard_packed_bytes(int32_t K) {
   if (K <= 1 || K > 256) return 0;
   const size_t tiles = (static_cast<size_t>(K) + 15) / 16;

@@ -17,6 +17,7 @@ The per-head query up-projection A_q and the K up-factor B_k are composed offlin
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -48,7 +49,7 @@ class LSVDDecoderLayer(nn.Module):
         xq, xs, xn = act_quant(x, want_rotated=True, norm_weight=self.ln1, norm_eps=1e-5)
         lat, _, _ = w8a8_gemv(xq, xs, self.W_lat_q, self.W_lat_s)
         lk = lat[:, self.Rq:self.Rq + lay.sum_k]
-        lv = lat[:, self.Rq + lay.sum_k:]
+        lv = None if lay.shared_kv else lat[:, self.Rq + lay.sum_k:]       # shared: one latent per head serves K and V
         cache_append(lay, lk, lv, infer_state.mem_index, cache_k, scale_k, cache_v, scale_v)
         need = attn_decode_workspace_bytes(B, lay, infer_state.max_len_in_batch)
         if self._ws is None or self._ws.numel() < need:
@@ -92,18 +93,20 @@ def _layer_prefill(self, x, cache_k, scale_k, cache_v, scale_v, dest_slots, stag
 LSVDDecoderLayer.forward_prefill = torch.no_grad()(_layer_prefill)
 
 
-def make_layer_weights(hidden: int, num_heads: int, head_dim: int, rank_q: int, k_ranks, v_ranks, seed: int = 0, device=None):
+def make_layer_weights(hidden: int, num_heads: int, head_dim: int, rank_q: int, k_ranks, v_ranks, seed: int = 0, device=None,
+                       shared_kv: bool = False):
     """Seeded random layer weights (xavier-like scales as the reference's block,
     kernels/layer_bench/ffn_kernel/baseline_kernel.py:86-91); returns the dict ``LSVDDecoderLayer`` takes.  Drawn on the
     CPU unless ``device`` is given (whole stacks in benchmarks)."""
     g = (torch.Generator() if device is None else torch.Generator(device=device)).manual_seed(seed)
     dv = dict(device=device) if device is not None else {}
     Rq, Rk, Rv = num_heads * rank_q, sum(k_ranks), sum(v_ranks)
+    lat_rows = Rq + Rk + (0 if shared_kv else Rv)      # shared: the V latent IS the K latent, no rows of its own
 
     def rnd(*shape, std):
         return torch.randn(*shape, generator=g, **dv) * std
 
-    W_lat = rnd(Rq + Rk + Rv, hidden, std=1.0 / math.sqrt(hidden))
+    W_lat = rnd(lat_rows, hidden, std=1.0 / math.sqrt(hidden))
     A_q = rnd(num_heads, head_dim, rank_q, std=1.0 / math.sqrt(rank_q))          # query up-factor per head
     B_k = rnd(Rk, head_dim, std=1.0 / 8)                                           # K up-factor rows per head
     C = torch.empty(Rk, rank_q, **dv)
@@ -118,6 +121,12 @@ def make_layer_weights(hidden: int, num_heads: int, head_dim: int, rank_q: int, 
     return w
 
 
+def _recorded_event():
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    return ev
+
+
 class TPDecoderLayer(nn.Module):
     """The decoder layer of one tensor-parallel rank (see lsvd_b200/parallel.py for the sharding).
 
@@ -125,8 +134,9 @@ class TPDecoderLayer(nn.Module):
     columns, and issues one all-reduce in the attention block, one all-gather and one all-reduce in the FFN block.
     Everything between the collectives runs in the library's kernels (the dequantising steps around a collective are
     epilogues: an fp32 partial-sum output of the product before the first all-reduce, the residual + RMSNorm + A8
-    quantiser after it, a dequantise + residual kernel after the second); buffers are kept per batch size, so a step is
-    about twenty host calls and allocates nothing.
+    quantiser after it, a dequantise + residual kernel after the second); buffers are kept per batch size, so a step
+    allocates nothing: about twenty host calls when launched eagerly, seven once the runs between the collectives are
+    replayed as CUDA graphs (``use_graphs``, on unless ``LSVD_TP_GRAPHS=0``).
     """
 
     def __init__(self, lw: dict, fw: dict, info: dict, head_dim: int, rank_q: int, world: int, group=None, head_major: bool = False):
@@ -143,6 +153,8 @@ class TPDecoderLayer(nn.Module):
         self.had_K_packed = None
         self.Rq = self.layout.num_heads * rank_q
         self._bufs = {}
+        self.use_graphs = os.environ.get("LSVD_TP_GRAPHS", "1") == "1"
+        self._graphs, self._seen = {}, {}
 
     def _step_buffers(self, B: int, max_len: int, dev):
         key = (B, max_len, str(dev))
@@ -163,54 +175,111 @@ class TPDecoderLayer(nn.Module):
             part=e(B, hidden, dt=torch.float32), y1=e(B, hidden), x2q=e(B, hidden, dt=torch.int8), x2s=e(B, dt=torch.float32),
             lat2=e(B, 2 * r), zq=e(2 * B, r, dt=torch.int8), zs=e(2 * B, dt=torch.float32),
             send=torch.zeros(B, widest, dtype=torch.float16, device=dev), recv=e(self.world * B, widest),
-            hq=e(B, d_ffn, dt=torch.int8), hs=e(B, dt=torch.float32), hloc=e(B, ns + nq, dt=torch.int8),
+            h=e(B, d_ffn), hq=e(B, d_ffn, dt=torch.int8), hs=e(B, dt=torch.float32), hloc=e(B, ns + nq, dt=torch.int8),
             acc=e(B, hidden, dt=torch.int32), out=e(B, hidden), plan=(widest, idx))
         self._bufs[key] = b
         return b
 
-    @torch.no_grad()
-    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages=None, timing_events=None):
-        import torch.distributed as dist
+    def _segments(self, b, x, cache_k, scale_k, cache_v, scale_v, infer_state, timing_events=None):
+        """The four runs of kernel launches between the step's collectives, as callables over the step buffers ``b``."""
         from .ffn import hadamard_pack, hadamard_quant, dequant_residual
-        from .parallel import gather_hidden
-        lay, Hl, B, dev = self.layout, self.layout.num_heads, x.shape[0], x.device
-        b = self._step_buffers(B, int(infer_state.max_len_in_batch), dev)
-        # ---- attention block: RMSNorm + A8, latent projection, append, attention, row-parallel output projection ----
-        act_quant(x, norm_weight=self.ln1, norm_eps=1e-5, q=b["xq"], scale=b["xs"], rot=b["xn"])
-        w8a8_gemv(b["xq"], b["xs"], self.W_lat_q, self.W_lat_s, out=b["lat"])
-        lat = b["lat"]
-        cache_append(lay, lat[:, self.Rq:self.Rq + lay.sum_k], lat[:, self.Rq + lay.sum_k:], infer_state.mem_index,
-                     cache_k, scale_k, cache_v, scale_v)
-        token_decode_attention_int8_latent_absorb(lat[:, :self.Rq].unflatten(1, (Hl, self.rank_q)), infer_state, Hl,
-                                                  self.rank_q, cache_k, scale_k, cache_v, scale_v, self.C, None,
-                                                  layout=lay, out_latent=b["o_lat"], workspace=b["ws"],
-                                                  sm_scale=1.0 / math.sqrt(self.head_dim), timing_events=timing_events)
-        act_quant(b["o_lat"], q=b["oq"], scale=b["os"])
-        w8a8_gemv(b["oq"], b["os"], self.W_uvo_q, self.W_uvo_s, want_out=False, out_f32=b["part"])       # fp32 partial sums
-        dist.all_reduce(b["part"], group=self.group)
-        # y1 = fp16(sum + xn); x2 = A8(RMSNorm(y1)): one launch
-        act_quant(None, x_f32=b["part"], add=b["xn"], sum_out=b["y1"], norm_weight=self.ln2, norm_eps=1e-6, q=b["x2q"], scale=b["x2s"])
-        # ---- FFN: replicated latents, column-parallel gate/up, gathered hidden vector, row-parallel int32 down projection ----
+        lay, Hl, B = self.layout, self.layout.num_heads, x.shape[0]
         r = self.f_U_q.shape[0] // 2
         ns = self.f_Vg_q.shape[0]
-        w8a8_gemv(b["x2q"], b["x2s"], self.f_U_q, self.f_U_s, out=b["lat2"])
-        act_quant(b["lat2"].view(-1, r), q=b["zq"], scale=b["zs"])
-        zq, zs = b["zq"].view(B, 2 * r), b["zs"].view(B, 2)
-        h_local = b["send"]                       # the rank's [SVD slice | RTN slice]; the padding columns stay zero
-        w8a8_gemv(zq[:, :r], zs[:, 0], self.f_Vg_q, self.f_Vg_s, self.f_Vu_q, self.f_Vu_s, a2_q=zq[:, r:], a2_scale=zs[:, 1],
-                  out=h_local, out_col=0)
-        w8a8_gemv(b["x2q"], b["x2s"], self.f_Wg_q, self.f_Wg_s, self.f_Wu_q, self.f_Wu_s, out=h_local, out_col=ns)
-        h = gather_hidden(h_local, self.info, self.world, self.group, plan=b["plan"], send=b["send"], recv=b["recv"])
+        widest, idx = b["plan"]
         if self.had_K_packed is None:
             self.had_K_packed = hadamard_pack(self.had_K)
-        hq, hs, _ = hadamard_quant(h, self.had_K_packed, self.K, q=b["hq"], scale=b["hs"])
-        s0, s1 = self.info["svd"]
-        q0, q1 = self.info["rtn"]
-        n_svd = self.info["n_svd"]
-        torch.cat((hq[:, s0:s1], hq[:, n_svd + q0:n_svd + q1]), dim=1, out=b["hloc"])
-        w8a8_gemv(b["hloc"], hs, self.f_Wd_loc_q, None, want_out=False, acc=b["acc"])
+
+        def attention_block():
+            # RMSNorm + A8, latent projection, append, attention, row-parallel output projection (fp32 partial sums)
+            act_quant(x, norm_weight=self.ln1, norm_eps=1e-5, q=b["xq"], scale=b["xs"], rot=b["xn"])
+            w8a8_gemv(b["xq"], b["xs"], self.W_lat_q, self.W_lat_s, out=b["lat"])
+            lat = b["lat"]
+            cache_append(lay, lat[:, self.Rq:self.Rq + lay.sum_k], lat[:, self.Rq + lay.sum_k:], infer_state.mem_index,
+                         cache_k, scale_k, cache_v, scale_v)
+            token_decode_attention_int8_latent_absorb(lat[:, :self.Rq].unflatten(1, (Hl, self.rank_q)), infer_state, Hl,
+                                                      self.rank_q, cache_k, scale_k, cache_v, scale_v, self.C, None,
+                                                      layout=lay, out_latent=b["o_lat"], workspace=b["ws"],
+                                                      sm_scale=1.0 / math.sqrt(self.head_dim), timing_events=timing_events)
+            act_quant(b["o_lat"], q=b["oq"], scale=b["os"])
+            w8a8_gemv(b["oq"], b["os"], self.W_uvo_q, self.W_uvo_s, want_out=False, out_f32=b["part"])
+
+        def gate_up():
+            # y1 = fp16(sum + xn); x2 = A8(RMSNorm(y1)): one launch; replicated latents; column-parallel gate / up
+            act_quant(None, x_f32=b["part"], add=b["xn"], sum_out=b["y1"], norm_weight=self.ln2, norm_eps=1e-6, q=b["x2q"],
+                      scale=b["x2s"])
+            w8a8_gemv(b["x2q"], b["x2s"], self.f_U_q, self.f_U_s, out=b["lat2"])
+            act_quant(b["lat2"].view(-1, r), q=b["zq"], scale=b["zs"])
+            zq, zs = b["zq"].view(B, 2 * r), b["zs"].view(B, 2)
+            # the rank's [SVD slice | RTN slice] straight into the send buffer; its padding columns stay zero
+            w8a8_gemv(zq[:, :r], zs[:, 0], self.f_Vg_q, self.f_Vg_s, self.f_Vu_q, self.f_Vu_s, a2_q=zq[:, r:], a2_scale=zs[:, 1],
+                      out=b["send"], out_col=0)
+            w8a8_gemv(b["x2q"], b["x2s"], self.f_Wg_q, self.f_Wg_s, self.f_Wu_q, self.f_Wu_s, out=b["send"], out_col=ns)
+
+        def down():
+            # gathered pieces -> global [SVD | RTN] order, Hadamard + A8, the rank's columns, row-parallel int32 product
+            torch.index_select(b["recv"].view(self.world, B, widest).permute(1, 0, 2).reshape(B, self.world * widest), 1, idx,
+                               out=b["h"])
+            hadamard_quant(b["h"], self.had_K_packed, self.K, q=b["hq"], scale=b["hs"])
+            s0, s1 = self.info["svd"]
+            q0, q1 = self.info["rtn"]
+            n_svd = self.info["n_svd"]
+            torch.cat((b["hq"][:, s0:s1], b["hq"][:, n_svd + q0:n_svd + q1]), dim=1, out=b["hloc"])
+            w8a8_gemv(b["hloc"], b["hs"], self.f_Wd_loc_q, None, want_out=False, acc=b["acc"])
+
+        def finish():
+            dequant_residual(b["acc"], b["hs"], self.f_Wd_s, residual=b["y1"], out=b["out"])
+
+        return attention_block, gate_up, down, finish
+
+    @torch.no_grad()
+    def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages=None, timing_events=None, segment_events=None):
+        """One step.  ``segment_events`` (a list) receives eight CUDA events recorded around the four runs of launches and
+        the three collectives: attention block | all-reduce | gate/up | all-gather | down | all-reduce | finish.
+        With ``use_graphs`` the four runs of launches between the collectives are captured as CUDA graphs
+        the second time a step sees the same tensors (``x``, caches, state: callers that reuse their buffers, as a decode
+        loop does) and replayed from then on: seven host calls per step (four replays, three collectives; the
+        collectives themselves are never captured)."""
+        import torch.distributed as dist
+        B, dev = x.shape[0], x.device
+        b = self._step_buffers(B, int(infer_state.max_len_in_batch), dev)
+        r2t = infer_state.req_manager.req_to_token_indexs
+        key = (x.data_ptr(), cache_k.data_ptr(), scale_k.data_ptr(), cache_v.data_ptr(), scale_v.data_ptr(),
+               infer_state.b_seq_len.data_ptr(), infer_state.b_req_idx.data_ptr(), infer_state.mem_index.data_ptr(), r2t.data_ptr(),
+               B, int(infer_state.max_len_in_batch))
+        graphs = None
+        if self.use_graphs and x.is_cuda and stages is None and timing_events is None:
+            graphs = self._graphs.get(key)
+            if graphs is None and self._seen.get(key, 0) >= 1:
+                pool = torch.cuda.graph_pool_handle()
+                graphs = []
+                for seg in self._segments(b, x, cache_k, scale_k, cache_v, scale_v, infer_state):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, pool=pool):
+                        seg()
+                    graphs.append(g)
+                self._graphs[key] = graphs
+            self._seen[key] = self._seen.get(key, 0) + 1
+        if graphs is not None:
+            run = [g.replay for g in graphs]
+        else:
+            run = self._segments(b, x, cache_k, scale_k, cache_v, scale_v, infer_state, timing_events)
+        mark = (lambda: None) if segment_events is None else (lambda: segment_events.append(_recorded_event()))
+        mark()
+        run[0]()
+        mark()
+        dist.all_reduce(b["part"], group=self.group)
+        mark()
+        run[1]()
+        mark()
+        dist.all_gather_into_tensor(b["recv"], b["send"], group=self.group)
+        mark()
+        run[2]()
+        mark()
         dist.all_reduce(b["acc"], group=self.group)
-        out = dequant_residual(b["acc"], hs, self.f_Wd_s, residual=b["y1"], out=b["out"])
+        mark()
+        run[3]()
+        mark()
         if stages is not None:
-            stages.update(xn=b["xn"], o_lat=b["o_lat"], y1=b["y1"], h_q=hq, down_acc=b["acc"], out=out)
-        return out
+            stages.update(xn=b["xn"], o_lat=b["o_lat"], y1=b["y1"], h_q=b["hq"], down_acc=b["acc"], out=b["out"])
+        return b["out"]

@@ -19,7 +19,7 @@ buffers in the GPU's own memory; no kernel here reads a peer's memory.
 """
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -122,3 +122,35 @@ def gather_hidden(h_local: torch.Tensor, info: dict, world: int, group=None, pla
         recv = h_local.new_empty(world * B, widest)            # rank r's rows at r * B ..
     dist.all_gather_into_tensor(recv, send, group=group)
     return recv.view(world, B, widest).permute(1, 0, 2).reshape(B, world * widest).index_select(1, idx)
+
+
+def tp_heads_hadamard_quant(x_local: torch.Tensor, head_ids, num_heads: int, group=None, had_K: Optional[torch.Tensor] = None,
+                            partial: Optional[torch.Tensor] = None):
+    """The Hadamard across heads + per-token int8 quantisation in front of ``o_proj`` (``ActQuantWrapper`` with
+    ``online_partial_had``, fake_quant/utils/quant_utils.py:302-322) when the heads are sharded: ``x_local
+    [rows, len(head_ids) * head_dim]`` fp16 holds this rank's heads (global indices ``head_ids``).  Every rank adds its heads'
+    terms of all ``num_heads`` output heads into an fp32 row (``lsvd_heads_hadamard_partial``), ONE all-reduce sums the
+    rows, and the quantiser rounds the sum to fp16 once.  Returns (codes int8 [rows, num_heads * head_dim], scale fp32
+    [rows], rotated fp16): the same on every rank; a row-parallel ``o_proj`` then multiplies its own columns of the codes."""
+    import ctypes as C
+    import torch.distributed as dist
+    from . import _lib
+    from .attention import _require_cuda, _stream_ptr
+    from .ffn import act_quant
+    _require_cuda(x_local)
+    n_local = len(head_ids)
+    rows, cols = x_local.shape
+    if x_local.dtype != torch.float16 or x_local.stride(1) != 1 or n_local == 0 or cols % n_local:
+        raise ValueError("x_local must be fp16 [rows, len(head_ids) * head_dim] with unit inner stride")
+    head_dim = cols // n_local
+    if partial is None:
+        partial = torch.empty(rows, num_heads * head_dim, dtype=torch.float32, device=x_local.device)
+    hk = None if had_K is None else had_K.to(device=x_local.device, dtype=torch.float16).contiguous()
+    ids = (C.c_int32 * n_local)(*[int(h) for h in head_ids])
+    _lib.check(_lib.load().lsvd_heads_hadamard_partial(x_local.data_ptr(), x_local.stride(0), ids, n_local, num_heads, head_dim,
+                                                      None if hk is None else hk.data_ptr(), partial.data_ptr(), rows,
+                                                      _stream_ptr(x_local)))
+    dist.all_reduce(partial, group=group)
+    rot = torch.empty(rows, num_heads * head_dim, dtype=torch.float16, device=x_local.device)
+    q, s, _ = act_quant(None, x_f32=partial, sum_out=rot)
+    return q, s, rot

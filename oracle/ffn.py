@@ -70,6 +70,23 @@ def partial_hadamard_heads(x16: torch.Tensor, head_dim: int) -> torch.Tensor:
     return y.transpose(1, 2).reshape(x16.shape)
 
 
+def partial_hadamard_heads_terms(x_local16: torch.Tensor, head_ids, num_heads: int, had_K=None) -> torch.Tensor:
+    """One tensor-parallel rank's terms of the Hadamard across heads (lsvd_b200.parallel.tp_heads_hadamard_quant): the rank
+    holds heads ``head_ids`` of the ``num_heads``; returns fp32 ``[rows, num_heads * head_dim]`` with
+    ``out[h', d] = sum_j S[h', head_ids[j]] x[j, d] / sqrt(num_heads)``.  The sum of all ranks' terms, rounded to fp16, is
+    ``partial_hadamard_heads`` of the whole row (the transform is linear; Sylvester signs are (-1)^popcount(h' & h))."""
+    n_local = len(head_ids)
+    rows, cols = x_local16.shape
+    hd = cols // n_local
+    if had_K is None:
+        hp = torch.arange(num_heads)
+        S = torch.tensor([[(-1.0) ** bin(int(a) & int(b)).count("1") for b in head_ids] for a in hp])
+    else:
+        S = had_K.float()[:, list(head_ids)]
+    x = x_local16.float().reshape(rows, n_local, hd)
+    return (torch.einsum("oj,rjd->rod", S, x) * (1.0 / math.sqrt(num_heads))).reshape(rows, num_heads * hd)
+
+
 def hadamard_full(x16: torch.Tensor, had_K, K: int) -> torch.Tensor:
     """(H_K kron H_{n/K}) x / sqrt(n) on the last axis, with the reference's two fp16 roundings.
 

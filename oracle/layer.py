@@ -35,7 +35,8 @@ def decoder_layer(x16, w, ffn_w, k_off, v_off, num_heads, head_dim, rank_q, cach
     xn = xn_own if xn is None else xn
     lat = linear_a8w8(xn, w["W_lat_q"], w["W_lat_s"])
     attention.cache_append(lat[:, Rq:Rq + k_off[-1]].contiguous(), mem_index, k_off, cache_k, scale_k)
-    attention.cache_append(lat[:, Rq + k_off[-1]:].contiguous(), mem_index, v_off, cache_v, scale_v)
+    if cache_v is not cache_k:                  # a shared K/V latent is cached once (svd_utils.py:1505-1507)
+        attention.cache_append(lat[:, Rq + k_off[-1]:].contiguous(), mem_index, v_off, cache_v, scale_v)
     q = lat[:, :Rq].reshape(-1, num_heads, rank_q)
     ident = torch.zeros(v_off[-1], 1, dtype=torch.float16)          # the V up-projection is folded into W_uvo
     _, o_lat = attention.decode_absorb(q, cache_k, scale_k, cache_v, scale_v, w["C"], ident, k_off, v_off,

@@ -171,3 +171,39 @@ def test_prefill_append_then_decode_attention(head_major):
     o = attend(c["q"].cuda(), st, H, D, ck, sk, cv, sv, c["up_k"].cuda(), c["up_v"].cuda(), layout=lay).cpu()
     o_ref, _ = U.run_oracle(c)
     assert rel_to_norm(o.float(), o_ref.float()) < 2e-4
+
+
+@pytest.mark.parametrize("head_major", [False, True])
+def test_shared_kv_latent_layer(head_major):
+    """One cached latent per head serving as K and as V latent (the reference's shared-``BLinear`` factors,
+    fake_quant/utils/svd_utils.py:1505-1507): the cache holds half the bytes, the append writes it once, the attention
+    reads scores and values from the same rows.  Against the oracle run with the same tensor on both sides."""
+    H, D, rq, hidden = 8, 128, 64, 1024
+    kr = synth.ragged_ranks(H, 64, seed=5)
+    lay = LatentCacheLayout(kr, shared_kv=True, head_major=head_major)
+    w = make_layer_weights(hidden, H, D, rq, kr, kr, seed=4, shared_kv=True)
+    assert w["W_lat_q"].shape[0] == H * rq + sum(kr)
+    fw = synth.ffn_weights(hidden, 12 * 64, 128, 384, seed=2, had_K=synth.sign_matrix(12, seed=1).float(), K=12, input_had=False, std=0.05)
+    B, lens = 3, [150, 33, 64]
+    c = U.build_case(B, H, D, kr, kr, lens, seed=11)
+    st = InferState(B, c["max_len"], lens, device="cuda")
+    x = torch.randn(B, hidden, generator=torch.Generator().manual_seed(3)).half()
+    dev = lambda d: {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+    layer = LSVDDecoderLayer(lay, D, rq, dev(w), HybridFFN(dev(fw)))
+    ck, sk, cv, sv = lay.alloc(c["cache_k"].shape[0])
+    assert cv is ck and sv is sk
+    if head_major:
+        a, b = lay.to_head_major(c["cache_k"], c["scale_k"], "k")
+        ck.copy_(a.cuda()); sk.copy_(b.cuda())
+    else:
+        ck.copy_(c["cache_k"].cuda()); sk.copy_(c["scale_k"].cuda())
+    stages = {}
+    out = layer(x.cuda(), ck, sk, cv, sv, st, stages=stages).cpu()
+    ck_ref, sk_ref = c["cache_k"].clone(), c["scale_k"].clone()
+    ref, rst = olayer.decoder_layer(x, w, fw, lay.k_off, lay.v_off, H, D, rq, ck_ref, sk_ref, ck_ref, sk_ref,
+                                    c["req_to_token"], c["b_req_idx"], c["b_seq_len"], st.mem_index.cpu())
+    got_k, got_s = (lay.from_head_major(ck, sk, "k") if head_major else (ck, sk))
+    assert torch.equal(stages["lat"].cpu(), rst["lat"])
+    assert torch.equal(got_k.cpu(), ck_ref) and torch.equal(got_s.cpu(), sk_ref)
+    assert rel_to_norm(stages["o_lat"].cpu().float(), rst["o_lat"].float()) < 2e-3
+    assert rel_to_norm(out.float(), ref.float()) < 2e-3

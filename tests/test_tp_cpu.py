@@ -102,3 +102,44 @@ def test_sharded_layer_matches_the_unsharded_oracle(world, H):
     for r in range(1, world):        # ranks agree bit for bit: output, int32 accumulators, quantised hidden vector
         assert torch.equal(out[0][0], out[r][0]) and torch.equal(out[0][1], out[r][1]) and torch.equal(out[0][2], out[r][2])
     assert rel_to_norm(out[0][0].float(), ref.float()) < 2e-3
+
+
+def _had_rank_main(rank, world, port, out, H, with_hadk):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import ffn as offn
+        from lsvd_b200.parallel import partition_heads
+        D = 16
+        x = torch.randn(5, H * D, generator=torch.Generator().manual_seed(4)).half()
+        heads = partition_heads([64] * H, [64] * H, world)[rank]
+        x_local = torch.cat([x[:, h * D:(h + 1) * D] for h in heads], dim=1)
+        hk = load_golden("partial_hadamard")["had28"].float() if with_hadk else None
+        terms = offn.partial_hadamard_heads_terms(x_local, heads, H, hk)
+        dist.all_reduce(terms)
+        out[rank] = terms.half()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,H,with_hadk", [(2, 32, False), (4, 32, False), (2, 28, True)])
+def test_heads_hadamard_under_head_sharding(world, H, with_hadk):
+    """The across-heads Hadamard in front of o_proj when every rank holds only its own heads: each rank's terms summed by
+    one all-reduce give the single-process rotation (fake_quant/utils/quant_utils.py:302-317)."""
+    from oracle import ffn as offn
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_had_rank_main, args=(world, port, out, H, with_hadk), nprocs=world, join=True)
+    x = torch.randn(5, H * 16, generator=torch.Generator().manual_seed(4)).half()
+    if with_hadk:
+        ref = offn.partial_hadamard_heads_hadk(x, 16, load_golden("partial_hadamard")["had28"].float())
+    else:
+        ref = offn.partial_hadamard_heads(x, 16)
+    for r in range(world):
+        assert torch.equal(out[r], out[0])
+        d = (out[r].float() - ref.float()).abs()
+        assert (d <= ref.float().abs() * 2.0 ** -10 + 1e-6).all()      # one fp16 rounding (the reference rounds twice with had_K)
+        assert (d == 0).float().mean() > (0.6 if with_hadk else 0.9)
