@@ -745,11 +745,13 @@ def run_tp(args, rank, world, local):
     kr, vr = synth.ragged_ranks(H, 64, seed=0), synth.ragged_ranks(H, 64, seed=1)
     lw_full = make_layer_weights(hid, H, D, rq, kr, vr, seed=1)                       # same seed: same weights on every rank
     fw_full = synth.ffn_weights(hid, dff, 640, dff // 2, seed=2, had_K=synth.sign_matrix(108, seed=0).float(), K=108, input_had=False)
-    lw, fw, info = shard_layer(lw_full, fw_full, kr, vr, rq, world, rank)
+    ew = args.emulate_world if (args.emulate_world > 1 and world == 1) else world
+    lw, fw, info = shard_layer(lw_full, fw_full, kr, vr, rq, ew, rank)
     del lw_full, fw_full
     to = lambda d: {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
     head_major = args.cache_layout == "head"
-    layer = TPDecoderLayer(to(lw), to(fw), info, D, rq, world, head_major=head_major)
+    layer = TPDecoderLayer(to(lw), to(fw), info, D, rq, ew, head_major=head_major)
+    layer.skip_collectives = ew != world
     lay = layer.layout
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     n_slots = B * (L + 1)
@@ -803,14 +805,16 @@ def run_tp(args, rank, world, local):
     seg_names = ("attention_block", "all_reduce_attn", "gate_up", "all_gather_h", "hadamard_down", "all_reduce_ffn", "finish")
     seg_sum = [0.0] * len(seg_names)
     barrier()
-    for i in range(args.steps):
+    all_evs = []
+    for i in range(args.steps):              # back to back, as in the timed loop: a rank that runs ahead waits in a collective
         evs = []
         x_in.copy_(xs[i % 4], non_blocking=True)
         layer(x_in, ck, sk, cv, sv, st, segment_events=evs)
-        torch.cuda.synchronize()
-        for j in range(len(seg_names)):
-            seg_sum[j] += evs[j].elapsed_time(evs[j + 1]) * 1e3 / args.steps
+        all_evs.append(evs)
     barrier()
+    for evs in all_evs[args.steps // 2:]:    # the second half: the ranks have settled into their steady offsets
+        for j in range(len(seg_names)):
+            seg_sum[j] += evs[j].elapsed_time(evs[j + 1]) * 1e3 / (args.steps - args.steps // 2)
     clocks = sampler.stop() if rank == 0 else None
     local_bytes = ck.numel() + cv.numel() + (sk.numel() + sv.numel()) * 2 + sum(
         v.numel() for v in list(lw.values()) + list(fw.values()) if isinstance(v, torch.Tensor) and v.dtype == torch.int8)
@@ -826,6 +830,7 @@ def run_tp(args, rank, world, local):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax, fp16 out", "data": "synthetic",
         "config": bench_config(args, w, B, world),
+        **({"emulated": "rank 0 of a %d-way split on one GPU, collectives left out: a profiling aid, not a result" % ew} if ew != world else {}),
         "config_detail": {"step": "RMSNorm + A8, int8 latent projection, cache append, int8 latent decode attention on the rank's "
                                   "heads, row-parallel output projection + all-reduce, column-parallel hybrid FFN gate/up, "
                                   "all-gather of the hidden vector, Hadamard 128 x 108 + A8, row-parallel int32 down projection + "
@@ -1197,6 +1202,9 @@ def main():
     ap.add_argument("--cache-layout", default="slot", choices=["head", "slot"],
                     help="latent cache stored head by head ([H][slots][r_h], the layout the streaming kernel prefers) or "
                          "slot by slot ([slots][sum r], the reference's)")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="c4_layer_tp on one GPU: run rank 0's shard of an N-way split without the collectives (for profilers, "
+                         "which take one process); the line is marked `emulated`")
     ap.add_argument("--shared-kv", action="store_true",
                     help="attention / layer workloads: one cached latent per head serving as K and V latent (half the cache)")
     args = ap.parse_args()

@@ -315,6 +315,15 @@ typedef struct lsvd_heads_hadamard_quant_args {
 } lsvd_heads_hadamard_quant_args;
 int lsvd_heads_hadamard_quant(const lsvd_heads_hadamard_quant_args* args, void* stream);
 
+/* Row-wise gather of byte segments: for every row r < rows and segment s < nseg (at most 32),
+ *   dst[r * dst_row_stride + dst_off[s] .. + len[s])  =  src[src_off[s] + r * src_row_stride[s] .. + len[s])
+ * (all in bytes, multiples of 16; the four tables are HOST arrays).  The tensor-parallel FFN uses it to lay the
+ * all-gathered [rank][token][svd slice | rtn slice] pieces of the hidden vector out in the global [SVD | RTN] channel
+ * order in one pass.  No counterpart in the reference (it has no tensor parallelism). */
+int lsvd_gather_segments(const void* src, void* dst, int64_t dst_row_stride_bytes, int32_t rows, int32_t nseg,
+                         const int64_t* src_off_bytes, const int64_t* src_row_stride_bytes, const int64_t* dst_off_bytes,
+                         const int32_t* len_bytes, void* stream);
+
 /* The same rotation when the heads are sharded over tensor-parallel ranks.  x fp16 [rows, n_local * head_dim] holds the
  * heads head_ids[0 .. n_local) (HOST array of global head indices); out fp32 [rows, heads * head_dim] (contiguous) receives
  * this rank's terms of every output head, already scaled by 1 / sqrt(heads): out[h', d] = s * sum_j S[h', head_ids[j]] x[j, d]

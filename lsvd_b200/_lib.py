@@ -202,6 +202,8 @@ SIGNATURES = {
                                         C.c_int32, C.c_void_p]),
     "lsvd_heads_hadamard_partial": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                               C.c_void_p, C.c_int32, C.c_void_p]),
+    "lsvd_gather_segments": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_int64),
+                                       C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_void_p]),
     "lsvd_per_head_up": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_int64,
                                    C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "lsvd_i8gemm_prefill": (C.c_int, [C.POINTER(I8GemmArgs), C.c_void_p]),

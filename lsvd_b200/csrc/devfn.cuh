@@ -60,13 +60,53 @@ __device__ __forceinline__ int8_t act_code(float x, float s) {
 __device__ __forceinline__ void act_quant_row(const ActQuantParams& p, int r, float* row, float* red) {
   const __half* x = p.x + r * p.x_row_stride;
   if (p.x32 != nullptr) {
-    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
-      const int64_t o = static_cast<int64_t>(r) * p.cols + i;
-      float v = __ldcg(p.x32 + o);
-      if (p.add16 != nullptr) v += __half2float(p.add16[o]);
-      const __half hv = __float2half_rn(v);
-      if (p.sum_out != nullptr) p.sum_out[o] = hv;
-      row[i] = __half2float(hv);
+    const int64_t base = static_cast<int64_t>(r) * p.cols;
+    if ((p.cols & 3) == 0) {
+      // four entries per thread and pass (rows start 16-byte aligned: contiguous tensors, cols a multiple of 4), all of a
+      // thread's loads requested before the first use
+      const int quads = p.cols >> 2;
+      for (int c0 = threadIdx.x; c0 < quads; c0 += 4 * blockDim.x) {
+        float4 xv[4];
+        uint2 av[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * blockDim.x;
+          if (c < quads) {
+            xv[u] = __ldcg(reinterpret_cast<const float4*>(p.x32 + base) + c);
+            if (p.add16 != nullptr) av[u] = __ldg(reinterpret_cast<const uint2*>(p.add16 + base) + c);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * blockDim.x;
+          if (c < quads) {
+            float v[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+            if (p.add16 != nullptr) {
+              const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&av[u].x));
+              const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&av[u].y));
+              v[0] += a0.x; v[1] += a0.y; v[2] += a1.x; v[3] += a1.y;
+            }
+            const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+            if (p.sum_out != nullptr) {
+              uint2 o;
+              o.x = *reinterpret_cast<const uint32_t*>(&h0);
+              o.y = *reinterpret_cast<const uint32_t*>(&h1);
+              reinterpret_cast<uint2*>(p.sum_out + base)[c] = o;
+            }
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+            row[4 * c] = f0.x; row[4 * c + 1] = f0.y; row[4 * c + 2] = f1.x; row[4 * c + 3] = f1.y;
+          }
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+        const int64_t o = base + i;
+        float v = __ldcg(p.x32 + o);
+        if (p.add16 != nullptr) v += __half2float(p.add16[o]);
+        const __half hv = __float2half_rn(v);
+        if (p.sum_out != nullptr) p.sum_out[o] = hv;
+        row[i] = __half2float(hv);
+      }
     }
   } else if (p.vec8) {
     // 16-byte loads, all of a thread's chunks in flight before the first use

@@ -697,6 +697,10 @@ extern "C" int lsvd_act_quant(const lsvd_act_quant_args* a, void* stream) {
   if (a->rows == 0) return LSVD_OK;
   if ((!a->x && !a->x_f32) || !a->q || !a->scale) return LSVD_ERR_INVALID_ARG;
   if (a->x_f32 != nullptr && (a->sign != nullptr || a->fwht != 0)) return LSVD_ERR_UNSUPPORTED;
+  // the fp32 rows are read four entries at a time when cols allows it: 16-byte aligned rows (8 for the fp16 companions)
+  if (a->x_f32 != nullptr && (a->cols % 4) == 0 &&
+      (!aligned(a->x_f32, 16) || (a->add != nullptr && !aligned(a->add, 8)) || (a->sum_out != nullptr && !aligned(a->sum_out, 8))))
+    return LSVD_ERR_INVALID_ARG;
   const bool rotate = a->sign != nullptr || a->fwht != 0;
   if (rotate && !is_pow2(a->cols)) return LSVD_ERR_INVALID_ARG;
   ActQuantParams p{};
@@ -930,10 +934,14 @@ extern "C" int lsvd_w8a8_gemv(const lsvd_gemv_args* a, void* stream) {
   if (a->form == 1) return a->m <= 16 ? launch_gemv_streamed(p, dual, split, st) : LSVD_ERR_UNSUPPORTED;
   if (a->form == 2) return launch_gemv_wide(p, dual, split, st);
   if (a->form != 0 && a->form != 3) return LSVD_ERR_INVALID_ARG;
-  // more than 32 tokens and a large matrix: the form that shares the token rows between a block's warps
-  // (measured: 35.6 vs 48.9 us for the 45 MB gate/up pair at 64 tokens; no gain at 32 tokens or below 16 MB)
+  // more than 32 tokens: the form that shares the token rows between a block's warps (measured: 35.6 vs 48.9 us for the
+  // 45 MB gate/up pair at 64 tokens; no gain at 32 tokens).  Its blocks split K between their warps when the matrix
+  // has few channels, which is what a tensor-parallel rank's column slice looks like (a 9.8 MB latent projection slice
+  // took 38 us in the register-fed form, more than the whole 39 MB matrix in this one); short reductions stay
+  // register-fed.
   const int64_t weight_bytes = static_cast<int64_t>(a->n) * a->k * (dual ? 2 : 1);
-  if (a->form == 0 && !fp32_form && a->out_f32 == nullptr && a->m > 32 && weight_bytes >= (16ll << 20)) return launch_gemv_wide(p, dual, split, st);
+  if (a->form == 0 && !fp32_form && a->out_f32 == nullptr && a->m > 32 && weight_bytes >= (4ll << 20) && a->k >= 2048)
+    return launch_gemv_wide(p, dual, split, st);
   if (a->m <= 8) return launch_gemv_nt<1>(p, dual, split, st);
   if (a->m <= 16) return launch_gemv_nt<2>(p, dual, split, st);
   if (a->m <= 32) return launch_gemv_nt<4>(p, dual, split, st);

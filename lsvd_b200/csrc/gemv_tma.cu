@@ -182,29 +182,37 @@ w8a8_gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 // and a stage holds 256 bytes of K of those weight rows and of ALL token rows, fetched once per block by TMA;
 // every consumer warp reads the whole token tile from shared memory and only its own weight rows, keeps complete
 // sums for its channels in registers, and stores them itself: no reduction across warps.
+// When the matrix has too few channels to give every SM a block of 64 (a tensor-parallel rank's column slice), a block
+// takes 16 or 32 channels and its four consumer warps split every stage's K instead (`kw` warps per 16-channel tile, each
+// taking every kw-th 64-byte span): a single warp's chain of dependent MMAs on one tile leaves three quarters of the SM's
+// tensor issue idle (measured: 46 us for a 2 x 1728 x 5120 pair on 108 one-warp blocks, the same as for 4 x the channels).
+// The kw partial sums of a tile meet in shared memory; each of the kw warps then finishes the token columns j = kq mod kw.
 constexpr int kWideStageK = 256;                      // bytes of K per stage: two 128-byte chunks
 constexpr int kWideMaxWarps = 4;
 
-template <int NT, bool DUAL, bool SPLIT_B>
+template <int NT, bool DUAL, bool SPLIT_B, int KW>
 __global__ void __launch_bounds__((kWideMaxWarps + 1) * 32, 1)
 w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                       const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a2,
                       const __grid_constant__ GemvParams p, const int stages, const int warps) {
   constexpr int NMAT = DUAL ? 2 : 1;
+  constexpr int kw = KW;                              // warps that share a 16-channel tile's K
   extern __shared__ uint8_t smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const int rows = warps * 16;                        // channels per block (and matrix)
+  const int rows = warps * 16;                        // channels per block (and matrix): `warps` 16-channel tiles
+  const int consumers = warps * kw;                   // kw warps share a tile's K
   const int w_bytes = 2 * rows * 128;                 // one matrix' rows of a stage: [2 chunks][rows][128]
   const int a_bytes = 2 * NT * 8 * 128;               // the token rows of a stage: [2 chunks][NT * 8][128]
   const int stage_bytes = NMAT * w_bytes + (SPLIT_B ? 2 : 1) * a_bytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * stage_bytes);
   uint64_t* empty_bar = full_bar + kTgMaxStages;
+  int* red = reinterpret_cast<int*>(empty_bar + kTgMaxStages);      // kw > 1: [consumers][NMAT * NT * 4 * 32] partial sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], warps);
+      mbar_init(&empty_bar[s], consumers);
     }
     fence_mbar_init();
   }
@@ -212,7 +220,7 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int tiles = (p.n + rows - 1) / rows;
   const int ksteps = (p.k + kWideStageK - 1) / kWideStageK;
 
-  if (warp == warps) {
+  if (warp == consumers) {
     // ================= producer =================
     if (lane == 0) {
       grid_dependency_wait();
@@ -240,10 +248,12 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
     return;
   }
-  if (warp > warps) return;
+  if (warp > consumers) return;
 
-  // ================= consumers: warp w owns channels 16 w .. 16 w + 15 of the block's tile =================
+  // ========== consumers: warp w works on channels 16 rt .. 16 rt + 15 of the block's tile, K spans kq mod kw ==========
   const int g = lane >> 2, t = lane & 3;
+  const int rt = warp / kw, kq = warp - rt * kw;
+  bool bad = false;
   int it = 0;
   for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     int acc[NMAT][NT][4];
@@ -257,15 +267,17 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       const int s = it % stages;
       if (!mbar_wait_bounded(&full_bar[s], (it / stages) & 1)) {
         report_status(p.status_word, LSVD_ERR_TIMEOUT);
-        return;
+        bad = true;
+        break;
       }
       const uint8_t* st = ring + static_cast<size_t>(s) * stage_bytes;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const uint8_t* wc = st + c * (rows * 128) + warp * (16 * 128);        // [16 rows of this warp][128], swizzled
+        const uint8_t* wc = st + c * (rows * 128) + rt * (16 * 128);          // [16 rows of this warp's tile][128], swizzled
         const uint8_t* ac = st + NMAT * w_bytes + c * (NT * 8 * 128);         // [NT * 8 tokens][128]
 #pragma unroll
         for (int sp = 0; sp < 2; ++sp) {
+          if (KW > 1 && ((2 * c + sp) % KW) != kq) continue;                  // another warp of the tile takes this span
           const int unit = ((4 * sp + t) ^ g) << 4;
           const uint4 x0 = lds_u4(wc + g * 128 + unit), x1 = lds_u4(wc + (g + 8) * 128 + unit);
           uint4 y0 = x0, y1 = x1;
@@ -290,10 +302,35 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
+    if (kw == 1) {
+      if (bad) return;
+    } else {
+      // the tile's kw partial sums meet in shared memory; this warp goes on with the token columns j = kq mod kw
+      int* mine = red + warp * (NMAT * NT * 4 * 32);
+#pragma unroll
+      for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) mine[((mtx * NT + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
+      // the barrier ORs "a wait gave up" over the consumer warps: they all stop here or none does
+      if (named_barrier_or(1, consumers * 32, bad)) return;
+#pragma unroll
+      for (int mtx = 0; mtx < NMAT; ++mtx)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            int sum = 0;
+            if ((j % kw) == kq)
+              for (int q = 0; q < kw; ++q) sum += red[(rt * kw + q) * (NMAT * NT * 4 * 32) + ((mtx * NT + j) * 4 + c) * 32 + lane];
+            acc[mtx][j][c] = sum;
+          }
+    }
     // ---- complete sums of channels (g, g + 8) x tokens (8 j + 2 t, + 1): dequantise and store ----
     // Scales and residuals are requested for all of a lane's 4 NT values before the first one is used: an
     // epilogue that waits on a global load per value costs more than the tile's whole stream.
-    const int row_base = tile * rows + warp * 16;
+    const int row_base = tile * rows + rt * 16;
     const int r0 = row_base + g, r1 = r0 + 8;
     const bool ok0 = r0 < p.n, ok1 = r1 < p.n;
     if (p.acc_out != nullptr || (DUAL && p.acc2_out != nullptr)) {
@@ -302,7 +339,7 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int row = (c >> 1) ? r1 : r0, tok = j * 8 + 2 * t + (c & 1);
-          if (row < p.n && tok < p.m) {
+          if (row < p.n && tok < p.m && (j % kw) == kq) {
             if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(tok) * p.n + row] = acc[0][j][c];
             if (DUAL && p.acc2_out != nullptr) p.acc2_out[static_cast<int64_t>(tok) * p.n + row] = acc[NMAT - 1][j][c];
           }
@@ -345,7 +382,7 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         for (int c = 0; c < 4; ++c) {
           const int hi = c >> 1, e = c & 1;
           const int row = hi ? r1 : r0, tok = j * 8 + 2 * t + e;
-          if (row >= p.n || tok >= p.m) continue;
+          if (row >= p.n || tok >= p.m || (j % kw) != kq) continue;
           const __half v0 = __float2half_rn((static_cast<float>(acc[0][j][c]) * sa[j][e]) * sw[hi]);
           __half out = v0;
           if (DUAL) {
@@ -357,6 +394,7 @@ w8a8_gemv_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           p.out[static_cast<int64_t>(tok) * p.out_row_stride + p.out_col + row] = out;
         }
     }
+    if (kw > 1) named_barrier_or(1, consumers * 32, false);      // the shares are read before the next tile overwrites them
   }
 }
 
@@ -366,6 +404,12 @@ static int launch_wide(const GemvParams& p, cudaStream_t st) {
   const int sms = std::max(1, device_sm_count());
   const int row_tiles = (p.n + 15) / 16;
   const int warps = std::max(1, std::min(kWideMaxWarps, (row_tiles + sms - 1) / sms));    // 16-channel tiles per block
+  int kw = warps == 1 ? 4 : (warps == 2 ? 2 : 1);                                          // warps that share a tile's K
+  {
+    // measurement knob: LSVD_GEMV_WIDE_KW = 1 | 2 | 4 forces the split where the block shape allows it
+    static const int forced = [] { const char* e = std::getenv("LSVD_GEMV_WIDE_KW"); return e ? std::atoi(e) : 0; }();
+    if ((forced == 1 || forced == 2 || forced == 4) && warps * forced <= kWideMaxWarps) kw = forced;
+  }
   const int rows = warps * 16;
   CUtensorMap mw, mw2, ma, ma2;
   int rc = make_map_k128(&mw, p.w, p.n, p.k, p.w_row_stride, rows);
@@ -377,7 +421,8 @@ static int launch_wide(const GemvParams& p, cudaStream_t st) {
   rc = make_map_k128(&ma2, SPLIT_B ? p.a2 : p.a, p.m, p.k, SPLIT_B ? p.a2_row_stride : p.a_row_stride, NT * 8);
   if (rc != LSVD_OK) return rc;
   const int stage_bytes = NMAT * 2 * rows * 128 + (SPLIT_B ? 2 : 1) * 2 * NT * 8 * 128;
-  const int fixed = 1024 + 2 * kTgMaxStages * 8 + 16;
+  const int red_bytes = kw > 1 ? warps * kw * NMAT * NT * 4 * 32 * 4 : 0;
+  const int fixed = 1024 + 2 * kTgMaxStages * 8 + 16 + red_bytes;
   const int budget = device_max_smem_optin() - 4096;
   const int tiles = (p.n + rows - 1) / rows;
   const int ksteps = (p.k + kWideStageK - 1) / kWideStageK;
@@ -386,7 +431,9 @@ static int launch_wide(const GemvParams& p, cudaStream_t st) {
   const int stages = std::max(1, std::min(std::min((budget - fixed) / stage_bytes, kTgMaxStages), per_block));
   if (fixed + stage_bytes > budget) return LSVD_ERR_UNSUPPORTED;
   const int smem = fixed + stages * stage_bytes;
-  auto kern = w8a8_gemv_wide_kernel<NT, DUAL, SPLIT_B>;
+  void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemvParams, int, int) =
+      kw == 4 ? w8a8_gemv_wide_kernel<NT, DUAL, SPLIT_B, 4>
+              : (kw == 2 ? w8a8_gemv_wide_kernel<NT, DUAL, SPLIT_B, 2> : w8a8_gemv_wide_kernel<NT, DUAL, SPLIT_B, 1>);
   LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
   LSVD_CUDA_TRY(launch_chained(kern, dim3(grid), dim3((kWideMaxWarps + 1) * 32), smem, st, 1, false, mw, mw2, ma, ma2, p,
                                stages, warps));

@@ -23,6 +23,7 @@ from typing import Optional
 import torch
 from torch import nn
 
+from . import _lib
 from .attention import LatentCacheLayout, cache_append, token_decode_attention_int8_latent_absorb, attn_decode_workspace_bytes
 from .ffn import HybridFFN, act_quant, w8a8_gemv, quantize_weight_rtn, i8gemm
 
@@ -155,6 +156,9 @@ class TPDecoderLayer(nn.Module):
         self._bufs = {}
         self.use_graphs = os.environ.get("LSVD_TP_GRAPHS", "1") == "1"
         self._graphs, self._seen = {}, {}
+        # profiling aid: one rank's launches of an N-way split on a single GPU, the three collectives left out (the
+        # results are then not those of the layer)
+        self.skip_collectives = False
 
     def _step_buffers(self, B: int, max_len: int, dev):
         key = (B, max_len, str(dev))
@@ -177,6 +181,20 @@ class TPDecoderLayer(nn.Module):
             send=torch.zeros(B, widest, dtype=torch.float16, device=dev), recv=e(self.world * B, widest),
             h=e(B, d_ffn), hq=e(B, d_ffn, dt=torch.int8), hs=e(B, dt=torch.float32), hloc=e(B, ns + nq, dt=torch.int8),
             acc=e(B, hidden, dt=torch.int32), out=e(B, hidden), plan=(widest, idx))
+        # the gathered pieces [rank][token][svd slice | rtn slice] -> rows in the global [SVD | RTN] order: two byte
+        # segments per rank (lsvd_gather_segments)
+        from .parallel import channel_slices
+        n_svd, n_q = self.info["n_svd"], self.info["n_q"]
+        src_off, src_stride, dst_off, length = [], [], [], []
+        for rk, (sv, rt) in enumerate(zip(channel_slices(n_svd, self.world), channel_slices(n_q, self.world))):
+            for first, (c0, c1), base in ((0, sv, 0), (sv[1] - sv[0], rt, n_svd)):
+                src_off.append((rk * B * widest + first) * 2)
+                src_stride.append(widest * 2)
+                dst_off.append((base + c0) * 2)
+                length.append((c1 - c0) * 2)
+        import ctypes as C
+        n = len(length)
+        b["segments"] = (n, (C.c_int64 * n)(*src_off), (C.c_int64 * n)(*src_stride), (C.c_int64 * n)(*dst_off), (C.c_int32 * n)(*length))
         self._bufs[key] = b
         return b
 
@@ -218,8 +236,10 @@ class TPDecoderLayer(nn.Module):
 
         def down():
             # gathered pieces -> global [SVD | RTN] order, Hadamard + A8, the rank's columns, row-parallel int32 product
-            torch.index_select(b["recv"].view(self.world, B, widest).permute(1, 0, 2).reshape(B, self.world * widest), 1, idx,
-                               out=b["h"])
+            seg = b["segments"]
+            _lib.check(_lib.load().lsvd_gather_segments(b["recv"].data_ptr(), b["h"].data_ptr(), b["h"].stride(0) * 2, B, seg[0],
+                                                       seg[1], seg[2], seg[3], seg[4],
+                                                       torch.cuda.current_stream(b["h"].device).cuda_stream))
             hadamard_quant(b["h"], self.had_K_packed, self.K, q=b["hq"], scale=b["hs"])
             s0, s1 = self.info["svd"]
             q0, q1 = self.info["rtn"]
@@ -268,15 +288,18 @@ class TPDecoderLayer(nn.Module):
         mark()
         run[0]()
         mark()
-        dist.all_reduce(b["part"], group=self.group)
+        if not self.skip_collectives:
+            dist.all_reduce(b["part"], group=self.group)
         mark()
         run[1]()
         mark()
-        dist.all_gather_into_tensor(b["recv"], b["send"], group=self.group)
+        if not self.skip_collectives:
+            dist.all_gather_into_tensor(b["recv"], b["send"], group=self.group)
         mark()
         run[2]()
         mark()
-        dist.all_reduce(b["acc"], group=self.group)
+        if not self.skip_collectives:
+            dist.all_reduce(b["acc"], group=self.group)
         mark()
         run[3]()
         mark()

@@ -292,9 +292,13 @@ def test_hadamard_across_heads_reference_fixture_and_7b_shape():
 
 @pytest.mark.parametrize("m,n,k,kind", [(17, 1024, 4096, "single"), (64, 4096, 11008, "single"), (33, 48, 1376 + 16, "single"),
                                         (64, 5504, 4096, "dual"), (40, 688, 4096, "dual"), (64, 5504, 512, "split"),
-                                        (20, 80, 48, "split"), (5, 4096, 512, "single")])
+                                        (20, 80, 48, "split"), (5, 4096, 512, "single"),
+                                        # a tensor-parallel rank's column slices at the 13B shape: few channels, so the
+                                        # block's warps split K (four warps on one 16-channel tile / two on each of two)
+                                        (64, 1728, 5120, "dual"), (64, 3456, 5120, "dual"), (64, 1920, 5120, "single"),
+                                        (64, 1280, 5120, "single"), (48, 2400, 2048 + 64, "split")])
 def test_gemv_wide_form_equals_register_form(m, n, k, kind):
-    """form 2 (token rows shared through shared memory, the default beyond 16 tokens) against form 3 (register-fed)
+    """form 2 (token rows shared through shared memory, the default beyond 32 tokens) against form 3 (register-fed)
     and the oracle: same integers, same fp16."""
     gen = torch.Generator().manual_seed(m * 13 + n + k)
     a = torch.randint(-128, 128, (m, k), generator=gen, dtype=torch.int8).cuda()
