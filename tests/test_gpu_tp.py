@@ -83,3 +83,33 @@ def test_two_gpu_layer_matches_oracle_and_ranks_agree():
     assert r0[3] and r1[3]
     assert r0[4] and r1[4]
     assert rel_to_norm(r0[0].float(), ref.float()) < 2e-3
+
+
+def test_gather_segments_lays_out_the_gathered_hidden_vector():
+    """lsvd_gather_segments on one GPU: the [rank][token][svd slice | rtn slice] pieces of a 4-way split into rows in the
+    global [SVD | RTN] order, against the index table of ``gather_plan``; and its argument checks."""
+    import ctypes as C
+    from lsvd_b200 import _lib
+    from lsvd_b200.parallel import channel_slices, gather_plan
+    world, B, n_svd, n_q = 4, 5, 6912, 6912
+    info = dict(n_svd=n_svd, n_q=n_q)
+    widest, idx = gather_plan(info, world)
+    recv = torch.randn(world * B, widest, generator=torch.Generator().manual_seed(1)).half().cuda()
+    want = recv.view(world, B, widest).permute(1, 0, 2).reshape(B, world * widest).index_select(1, idx.cuda())
+    src_off, src_stride, dst_off, length = [], [], [], []
+    for rk, (sv, rt) in enumerate(zip(channel_slices(n_svd, world), channel_slices(n_q, world))):
+        for first, (c0, c1), base in ((0, sv, 0), (sv[1] - sv[0], rt, n_svd)):
+            src_off.append((rk * B * widest + first) * 2)
+            src_stride.append(widest * 2)
+            dst_off.append((base + c0) * 2)
+            length.append((c1 - c0) * 2)
+    n = len(length)
+    out = torch.zeros(B, n_svd + n_q, dtype=torch.float16, device="cuda")
+    tabs = ((C.c_int64 * n)(*src_off), (C.c_int64 * n)(*src_stride), (C.c_int64 * n)(*dst_off), (C.c_int32 * n)(*length))
+    lib = _lib.load()
+    rc = lib.lsvd_gather_segments(recv.data_ptr(), out.data_ptr(), out.stride(0) * 2, B, n, *tabs, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(out, want)
+    bad = (C.c_int32 * n)(*([length[0] + 2] + length[1:]))           # not a multiple of 16 bytes
+    assert lib.lsvd_gather_segments(recv.data_ptr(), out.data_ptr(), out.stride(0) * 2, B, n, tabs[0], tabs[1], tabs[2], bad, None) == 1
+    assert lib.lsvd_gather_segments(recv.data_ptr(), out.data_ptr(), out.stride(0) * 2, B, 33, *tabs, None) == 1
