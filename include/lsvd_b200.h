@@ -437,7 +437,7 @@ typedef struct lsvd_ffn_decode_args {
                                  /* have been set to zero once, before its first use (it holds the barrier counters,   */
                                  /* which the kernel maintains from call to call); calls that share a workspace must   */
                                  /* be ordered on a stream.  `overlap` is ignored.  Same values as the chain; slower   */
-                                 /* than the chain on B200 at the 7B shape as measured, hence opt-in.  */
+                                 /* than the chain on B200 at the 7B shape as measured (78 against 56 us), hence opt-in.   */
 } lsvd_ffn_decode_args;
 size_t lsvd_ffn_decode_workspace_bytes(int32_t m, int32_t d_in, int32_t d_ffn, int32_t rank, int32_t d_out);
 int lsvd_ffn_decode(const lsvd_ffn_decode_args* args, void* stream);

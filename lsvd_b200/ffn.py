@@ -239,7 +239,7 @@ class HybridFFN(nn.Module):
         self._chains = {}
         self.overlap_branches = True      # RTN gate/up on a second stream beside the SVD branch (chain of launches)
         # at most 16 tokens: the whole block as ONE persistent kernel (lsvd_ffn_decode with `fused`).  Off by default:
-        # measured on B200 it is exact but slower than the chain (78 vs 56 us at the 7B shape)
+        # measured on B200 it is exact but slower than the chain (78 vs 56 us at the 7B shape: the device-wide barriers between its stages cost more than the launch gaps they replace)
         self.fused = os.environ.get("LSVD_FFN_FUSED", "0") == "1"
         self.rank = self.U_q.shape[0] // 2
         self.n_svd = self.Vg_q.shape[0]
