@@ -1213,9 +1213,10 @@ def main():
                     help="with several GPUs: N independent copies of the 1-GPU workload instead of the tensor-parallel layer")
     ap.add_argument("--tokens", type=int, default=8, help="tokens per step of the c2_ffn workload (1..64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cache-layout", default="slot", choices=["head", "slot"],
-                    help="latent cache stored head by head ([H][slots][r_h], the layout the streaming kernel prefers) or "
-                         "slot by slot ([slots][sum r], the reference's)")
+    ap.add_argument("--cache-layout", default="head", choices=["head", "slot"],
+                    help="latent cache stored head by head ([H][slots][r_h] with scales [H][slots]: the layout of the library's "
+                         "own layer and stack, whose streaming kernel then reads a step's 32 token scales as one 64-byte run) or "
+                         "slot by slot ([slots][sum r], the reference's tensors, which the drop-in functions take)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="c4_layer_tp on one GPU: run rank 0's shard of an N-way split without the collectives (for profilers, "
                          "which take one process); the line is marked `emulated`")

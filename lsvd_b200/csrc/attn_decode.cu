@@ -25,6 +25,7 @@
 // Stage 2 (flash_latent_per_head_decoding_stage2.py:7-48) is the same merge, followed here by the V
 // up-projection the reference leaves to a later GEMM (ffn_kernel/baseline_kernel.py:96-99,144-145).
 #include <algorithm>
+#include <cstdlib>
 #include <cmath>
 #include <cstring>
 #include <mutex>
@@ -317,7 +318,15 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     resolve(s0, valid, rslot);
   }
   load_k(rslot);
-  float ks = __half2float(ksc[kHeadMajor ? static_cast<int64_t>(rslot) : rslot * p.scale_k_row_stride]);
+  // The K and the V scale of a step's token are both needed by the softmax, long before the V latents are: both are
+  // requested one step ahead, with the K latents (the V scale, requested at the top of its own step, sat on the step's
+  // critical path: 8 us per call), and wait in ONE register as two fp16 bit patterns.
+  auto load_scales = [&](int rs) {
+    const uint32_t a = __half_as_ushort(ksc[kHeadMajor ? static_cast<int64_t>(rs) : rs * p.scale_k_row_stride]);
+    const uint32_t c = __half_as_ushort(vsc[kHeadMajor ? static_cast<int64_t>(rs) : rs * p.scale_v_row_stride]);
+    return a | (c << 16);
+  };
+  uint32_t kvs = load_scales(rslot);
   int slot_n1 = -1;                  // slot of "my" token of the next step (lane = token role)
   if (tok_begin + kTileTokens + lane < tok_end) slot_n1 = r2t[tok_begin + kTileTokens + lane];
 
@@ -334,7 +343,6 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
       if (v_ok0) va[i] = ldg64(row);
       if (v_ok1) vb[i] = ldg64(row + 64);
     }
-    const float vs = __half2float(vsc[kHeadMajor ? static_cast<int64_t>(rslot) : rslot * p.scale_v_row_stride]);
 
     // ---- scores ----
     float sc[4];                     // score of token g + 8j, in lanes t = 0, 1 of the quad
@@ -365,13 +373,15 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
       const float got = __shfl_sync(0xffffffffu, sc[j], (lane & 7) << 2);
       if ((lane >> 3) == j) s_raw = got;
     }
+    const float ks = __half2float(__ushort_as_half(static_cast<unsigned short>(kvs & 0xffffu)));
+    const float vs_cur = __half2float(__ushort_as_half(static_cast<unsigned short>(kvs >> 16)));
     const float s = valid ? s_raw * (ks * step) : -INFINITY;      // log2 domain
     // ---- request the K latents of the next step (their registers are free now) ----
     const bool valid_cur = valid;
     if (tb + kTileTokens < tok_end) {
       resolve(slot_n1, valid, rslot);
       load_k(rslot);
-      ks = __half2float(ksc[kHeadMajor ? static_cast<int64_t>(rslot) : rslot * p.scale_k_row_stride]);
+      kvs = load_scales(rslot);
     }
     // ---- online softmax; the running maximum is shared by the warp ----
     const float mx = fmaxf(m, warp_max_redux(s));
@@ -379,7 +389,7 @@ __device__ __forceinline__ void stream_item(const StreamParams& p, const HeadPla
     m = mx;
     const float pr = exp2f(s - mx);
     l = fmaf(l, corr, pr);
-    const float w = valid_cur ? pr * vs : 0.f;
+    const float w = valid_cur ? pr * vs_cur : 0.f;
     // ---- weights of the 32 tokens as two unsigned base-256 limbs against the step's largest weight (16 bits) ----
     const float wmax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(w)));   // w >= 0
     const float winv = wmax > 0.f ? 65535.f / wmax : 0.f;
