@@ -179,7 +179,22 @@ class MixedFFNGateUpDenseLatentFused(nn.Module):
         if x2.dtype != torch.float16 or x2.stride(1) != 1 or hid != self.hidden_size:
             raise ValueError("x must be fp16 [..., hidden] with unit inner stride")
         if m > 64:
-            raise ValueError("the decode form takes at most 64 tokens")
+            # Any number of tokens, like the reference's kernels (mix_ffn_kernel.py:1157-1232 are tiled over M): every
+            # quantity of this block is per token, so 64 tokens at a time through the decode kernels give the same values.
+            # (The weights are streamed once per 64 tokens: correct, not the fast way to run a prefill; the fp32-SwiGLU /
+            # row-maximum epilogues this structure needs are built into the weight-streaming product only.)
+            if out is None:
+                out = torch.empty(m, hid, dtype=torch.float16, device=x2.device)
+            parts = []
+            for r0 in range(0, m, 64):
+                _, st_c = self._run(x2[r0:r0 + 64], want, out=out[r0:r0 + 64])
+                parts.append(st_c)
+            st_all = {}
+            if want:
+                for key in parts[0]:
+                    vals = [pc[key] for pc in parts]
+                    st_all[key] = None if vals[0] is None else torch.cat(vals, dim=0)
+            return out, st_all
         dev, r, s, d = x2.device, self.rank, self.svd_out, self.intermediate_size
         st = {}
         amax = torch.empty(m, 4, dtype=torch.int32, device=dev)          # float bits: up latent, gate latent, low-rank mid, dense mid

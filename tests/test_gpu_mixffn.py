@@ -59,9 +59,10 @@ def test_reference_pipeline_fixture_stage_by_stage():
     assert torch.equal(y.cpu(), cpu["out"])
 
 
-@pytest.mark.parametrize("tokens", [1, 8, 33, 64])
+@pytest.mark.parametrize("tokens", [1, 8, 33, 64, 150])
 def test_seeded_module_against_the_oracle(tokens):
-    """hidden 1024, intermediate 2816 (low-rank channels 1408, rank 256; down: 512 channels, rank 192)."""
+    """hidden 1024, intermediate 2816 (low-rank channels 1408, rank 256; down: 512 channels, rank 192).  150 tokens: more
+    than one pass of the 64-token kernels (the module takes any number of tokens, like the reference's tiled kernels)."""
     gen = torch.Generator().manual_seed(100 + tokens)
     hid, d = 1024, 2816
     up = (torch.randn(d, hid, generator=gen) / hid ** 0.5).half()
@@ -117,5 +118,9 @@ def test_provider_converts_and_caches():
     w = {k: v.cpu() for k, v in conv.state_dict().items()}
     ref = omix.forward_stages(x.cpu().reshape(-1, hid), w, 1e-6)["out"]
     assert rel_to_norm(y.cpu().reshape(-1, hid).float(), ref.float()) < TOL
+    # more than 64 tokens: passes of 64 through the same kernels, the same rows
+    xl = torch.randn(130, hid, device="cuda", generator=gen).half()
+    yl = conv(xl)
+    assert torch.equal(yl[:64], conv(xl[:64])) and torch.equal(yl[128:], conv(xl[128:]))
     with pytest.raises(ValueError):
-        conv(torch.zeros(65, hid, dtype=torch.float16, device="cuda"))
+        conv(torch.zeros(3, hid + 16, dtype=torch.float16, device="cuda"))
