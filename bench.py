@@ -477,8 +477,8 @@ def run_ours(args, rank, world, local):
         "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "of": "measured" if "hbm_gbs" in peaks else "fallback",
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-                     # ncu capture summarised under profiles/ (277.7 MB + 7.3 MB); other workloads were not captured
-                     "traffic": 284952832 if (has_attn and w["batch"] == 16 and w["context"] == 4096 and w["ragged"]) else None,
+                     # ncu capture summarised under profiles/ (277.8 MB + 7.2 MB, slot-major layout at context 4097); other workloads were not captured
+                     "traffic": 284975872 if (has_attn and w["batch"] == 16 and w["context"] == 4096 and w["ragged"] and not args.shared_kv) else None,
                      "algorithmic_bytes_per_launch": abytes, "kernel_us": k_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
         "parts": {"step_us": ms_step * 1e3, "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
                   "step_algorithmic_bytes": step_bytes, "dominant_kernel_us": k_ms * 1e3,
