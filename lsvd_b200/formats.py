@@ -120,7 +120,9 @@ def _quantizer_scale(qz) -> Optional[torch.Tensor]:
 
 def load_qmodel(path: str) -> Tuple[Dict[str, torch.Tensor], Dict[str, torch.Tensor]]:
     """(state dict, {target name: per-row scales fp32}) of a ``--save_qmodel_path`` checkpoint.  The quantiser objects are
-    read without the reference's classes being importable."""
+    read without the reference's classes being importable.  The file is a pickle (the reference writes it with a plain
+    ``torch.save`` of Python objects): like ``torch.load(weights_only=False)`` this executes what the file says, so load
+    only checkpoints you made or trust."""
     blob = torch.load(path, map_location="cpu", weights_only=False, pickle_module=_tolerant_pickle)
     if "model" not in blob:
         raise KeyError("checkpoint without a 'model' state dict: %s" % path)
