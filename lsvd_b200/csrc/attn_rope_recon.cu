@@ -20,7 +20,6 @@
 // (they move a score by about 1e-5 of its value).
 #include <algorithm>
 #include <cmath>
-#include <cstdlib>
 
 #include "common.cuh"
 #include "gemv.cuh"
@@ -65,8 +64,8 @@ __global__ void rope_table_kernel(__half2* table, int max_len, int D, float thet
   table[idx] = __floats2half2_rn(cosf(ang), sinf(ang));
 }
 
-template <int D, int kParts>
-__global__ void __launch_bounds__(kRopeWarps * 32, (kParts > 1 ? 5 : 4)) rope_recon_kernel(const __grid_constant__ RopeParams p) {
+template <int D>
+__global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __grid_constant__ RopeParams p) {
   extern __shared__ __align__(16) uint8_t rope_smem[];
   constexpr int D2 = D >> 1;
   const int rk = p.rk, rv = p.rv;
@@ -138,59 +137,54 @@ __global__ void __launch_bounds__(kRopeWarps * 32, (kParts > 1 ? 5 : 4)) rope_re
     const int8_t* klo = p.cache_k + slot_lo * p.k_slot_stride + hk * p.k_head_stride + 8 * t;
     const int8_t* khi = p.cache_k + slot_hi * p.k_slot_stride + hk * p.k_head_stride + 8 * t;
 
-    // ---- K = Z W_uk and the folded rotation / dot product, in kParts passes over the rotary pairs: a pass rebuilds
-    // 8 / kParts column tiles and their partners D / 2 further on, so that only 64 / kParts accumulator registers are
-    // live at a time (the K rows are re-read from L1 in the later passes): more warps fit an SM ----
+    // ---- K = Z W_uk: acc[j] holds columns 8j + 2t, 8j + 2t + 1 of rows g (c = 0, 1) and g + 8 (c = 2, 3) ----
+    int acc[ntile][4];
+#pragma unroll
+    for (int j = 0; j < ntile; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+    for (int ks = 0; ks < rk; ks += 32) {
+      // the MMA's k index is a permutation of the 32 ranks that both operands follow:
+      // k 4t..4t+3 <-> ranks ks + 8t..8t+3, k 16+4t.. <-> ranks ks + 8t+4..8t+7
+      uint2 alo = make_uint2(0u, 0u), ahi = alo;
+      if (ks + 8 * t < rk) {
+        alo = __ldg(reinterpret_cast<const uint2*>(klo + ks));
+        ahi = __ldg(reinterpret_cast<const uint2*>(khi + ks));
+      }
+#pragma unroll
+      for (int j = 0; j < ntile; ++j) {
+        uint2 bw = make_uint2(0u, 0u);
+        if (ks + 8 * t < rk) bw = *reinterpret_cast<const uint2*>(wT + (8 * j + g) * pitch + ks + 8 * t);
+        mma_s8(acc[j], alo.x, ahi.x, alo.y, ahi.y, bw.x, bw.y);
+      }
+    }
+
+    // ---- rotation at the logical position and the dot product with the rotated query, folded (see the top) ----
     const float sk_lo = __half2float(p.scale_k[slot_lo * p.sk_slot_stride + hk]);
     const float sk_hi = __half2float(p.scale_k[slot_hi * p.sk_slot_stride + hk]);
     const __half2* tab_lo = p.table + static_cast<int64_t>(min(t0 + g, end - 1)) * D2;
     const __half2* tab_hi = p.table + static_cast<int64_t>(min(t0 + g + 8, end - 1)) * D2;
     float dot_lo = 0.f, dot_hi = 0.f;
-    constexpr int ppp = npair / kParts;                // rotary-pair tiles per pass
 #pragma unroll
-    for (int part = 0; part < kParts; ++part) {
-      int acc[2 * ppp][4];                             // [0, ppp): tiles part * ppp + jj; [ppp, 2 ppp): their partners
+    for (int j = 0; j < npair; ++j) {
+      const int c = 8 * j + 2 * t;                   // pairs c and c + 1: (cos, sin) of both in one 8-byte load
+      const uint2 raw_lo = __ldg(reinterpret_cast<const uint2*>(tab_lo + c));
+      const uint2 raw_hi = __ldg(reinterpret_cast<const uint2*>(tab_hi + c));
 #pragma unroll
-      for (int j = 0; j < 2 * ppp; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
-      for (int ks = 0; ks < rk; ks += 32) {
-        // the MMA's k index is a permutation of the 32 ranks that both operands follow:
-        // k 4t..4t+3 <-> ranks ks + 8t..8t+3, k 16+4t.. <-> ranks ks + 8t+4..8t+7
-        uint2 alo = make_uint2(0u, 0u), ahi = alo;
-        if (ks + 8 * t < rk) {
-          alo = __ldg(reinterpret_cast<const uint2*>(klo + ks));
-          ahi = __ldg(reinterpret_cast<const uint2*>(khi + ks));
+      for (int e = 0; e < 2; ++e) {
+        const float4 k4 = cst[c + e];
+        const uint32_t wl = e ? raw_lo.y : raw_lo.x, wh = e ? raw_hi.y : raw_hi.x;
+        const float2 cs_lo = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wl & 0xffffu))),
+                                         __half2float(__ushort_as_half(static_cast<unsigned short>(wl >> 16))));
+        const float2 cs_hi = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wh & 0xffffu))),
+                                         __half2float(__ushort_as_half(static_cast<unsigned short>(wh >> 16))));
+        {
+          const float a0 = static_cast<float>(acc[j][e]), a1 = static_cast<float>(acc[j + npair][e]);
+          dot_lo = fmaf(cs_lo.x, fmaf(a1, k4.y, a0 * k4.x), dot_lo);
+          dot_lo = fmaf(cs_lo.y, fmaf(-a1, k4.w, a0 * k4.z), dot_lo);
         }
-#pragma unroll
-        for (int jj = 0; jj < 2 * ppp; ++jj) {
-          const int j = (jj < ppp) ? part * ppp + jj : npair + part * ppp + (jj - ppp);
-          uint2 bw = make_uint2(0u, 0u);
-          if (ks + 8 * t < rk) bw = *reinterpret_cast<const uint2*>(wT + (8 * j + g) * pitch + ks + 8 * t);
-          mma_s8(acc[jj], alo.x, ahi.x, alo.y, ahi.y, bw.x, bw.y);
-        }
-      }
-#pragma unroll
-      for (int jj = 0; jj < ppp; ++jj) {
-        const int c = 8 * (part * ppp + jj) + 2 * t;   // pairs c and c + 1: (cos, sin) of both in one 8-byte load
-        const uint2 raw_lo = __ldg(reinterpret_cast<const uint2*>(tab_lo + c));
-        const uint2 raw_hi = __ldg(reinterpret_cast<const uint2*>(tab_hi + c));
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float4 k4 = cst[c + e];
-          const uint32_t wl = e ? raw_lo.y : raw_lo.x, wh = e ? raw_hi.y : raw_hi.x;
-          const float2 cs_lo = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wl & 0xffffu))),
-                                           __half2float(__ushort_as_half(static_cast<unsigned short>(wl >> 16))));
-          const float2 cs_hi = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wh & 0xffffu))),
-                                           __half2float(__ushort_as_half(static_cast<unsigned short>(wh >> 16))));
-          {
-            const float a0 = static_cast<float>(acc[jj][e]), a1 = static_cast<float>(acc[jj + ppp][e]);
-            dot_lo = fmaf(cs_lo.x, fmaf(a1, k4.y, a0 * k4.x), dot_lo);
-            dot_lo = fmaf(cs_lo.y, fmaf(-a1, k4.w, a0 * k4.z), dot_lo);
-          }
-          {
-            const float a0 = static_cast<float>(acc[jj][2 + e]), a1 = static_cast<float>(acc[jj + ppp][2 + e]);
-            dot_hi = fmaf(cs_hi.x, fmaf(a1, k4.y, a0 * k4.x), dot_hi);
-            dot_hi = fmaf(cs_hi.y, fmaf(-a1, k4.w, a0 * k4.z), dot_hi);
-          }
+        {
+          const float a0 = static_cast<float>(acc[j][2 + e]), a1 = static_cast<float>(acc[j + npair][2 + e]);
+          dot_hi = fmaf(cs_hi.x, fmaf(a1, k4.y, a0 * k4.x), dot_hi);
+          dot_hi = fmaf(cs_hi.y, fmaf(-a1, k4.w, a0 * k4.z), dot_hi);
         }
       }
     }
@@ -371,12 +365,8 @@ extern "C" int lsvd_attn_decode_rope(const lsvd_attn_rope_args* a, void* stream)
                                  a->max_len_in_batch, a->head_dim, p.theta));
     const int pitch = a->rank_k + 16;
     const int smem = ((a->head_dim * pitch + 15) & ~15) + (2 * a->head_dim + 2 * a->head_dim + kRopeWarps * (2 + 128)) * 4;
-    // head_dim 128 and a grid of several waves: the two-pass form (96 registers, five blocks per SM: 394 -> 374 us at
-    // batch 16 x 4096 tokens; four passes with six blocks per SM: 437 us); a small grid keeps the one-pass form (a single
-    // request: 37 against 43 us)
-    const int64_t blocks = static_cast<int64_t>(p.nsplit) * a->num_q_heads * a->batch;
-    void (*kern)(RopeParams) = a->head_dim == 128 ? (blocks >= 148 * 5 ? rope_recon_kernel<128, 2> : rope_recon_kernel<128, 1>)
-                               : (a->head_dim == 64 ? rope_recon_kernel<64, 1> : rope_recon_kernel<32, 1>);
+    void (*kern)(RopeParams) = a->head_dim == 128 ? rope_recon_kernel<128>
+                               : (a->head_dim == 64 ? rope_recon_kernel<64> : rope_recon_kernel<32>);
     if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
     LSVD_CUDA_TRY(launch_chained(kern, dim3(p.nsplit, a->num_q_heads, a->batch), dim3(kRopeWarps * 32), smem, st, 1, true, p));
   }
