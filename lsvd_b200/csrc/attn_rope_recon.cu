@@ -64,11 +64,13 @@ __global__ void rope_table_kernel(__half2* table, int max_len, int D, float thet
   table[idx] = __floats2half2_rn(cosf(ang), sinf(ang));
 }
 
-template <int D>
+// RK, RV: the K and V ranks when known at compile time (0: read from the parameters).  With the ranks fixed the rank loop
+// unrolls, its bounds checks fold away and the shared-memory offsets of the W_uk fragments become immediates.
+template <int D, int RK, int RV>
 __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __grid_constant__ RopeParams p) {
   extern __shared__ __align__(16) uint8_t rope_smem[];
   constexpr int D2 = D >> 1;
-  const int rk = p.rk, rv = p.rv;
+  const int rk = RK ? RK : p.rk, rv = RV ? RV : p.rv;
   const int pitch = rk + 16;                                   // bytes per column of the transposed W_uk slice
   int8_t* wT = reinterpret_cast<int8_t*>(rope_smem);           // [D][pitch]: column c of the head, ranks contiguous
   float* sw = reinterpret_cast<float*>(rope_smem + ((D * pitch + 15) & ~15));     // [D] column scales
@@ -141,7 +143,9 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
     int acc[ntile][4];
 #pragma unroll
     for (int j = 0; j < ntile; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
-    for (int ks = 0; ks < rk; ks += 32) {
+#pragma unroll
+    for (int ks = 0; ks < (RK ? RK : LSVD_MAX_RANK); ks += 32) {
+      if (!RK && ks >= rk) break;
       // the MMA's k index is a permutation of the 32 ranks that both operands follow:
       // k 4t..4t+3 <-> ranks ks + 8t..8t+3, k 16+4t.. <-> ranks ks + 8t+4..8t+7
       uint2 alo = make_uint2(0u, 0u), ahi = alo;
@@ -365,8 +369,10 @@ extern "C" int lsvd_attn_decode_rope(const lsvd_attn_rope_args* a, void* stream)
                                  a->max_len_in_batch, a->head_dim, p.theta));
     const int pitch = a->rank_k + 16;
     const int smem = ((a->head_dim * pitch + 15) & ~15) + (2 * a->head_dim + 2 * a->head_dim + kRopeWarps * (2 + 128)) * 4;
-    void (*kern)(RopeParams) = a->head_dim == 128 ? rope_recon_kernel<128>
-                               : (a->head_dim == 64 ? rope_recon_kernel<64> : rope_recon_kernel<32>);
+    void (*kern)(RopeParams) = a->head_dim == 128 ? rope_recon_kernel<128, 0, 0>
+                               : (a->head_dim == 64 ? rope_recon_kernel<64, 0, 0> : rope_recon_kernel<32, 0, 0>);
+    if (a->head_dim == 128 && a->rank_k == 64 && a->rank_v == 64) kern = rope_recon_kernel<128, 64, 64>;
+    if (a->head_dim == 128 && a->rank_k == 128 && a->rank_v == 128) kern = rope_recon_kernel<128, 128, 128>;
     if (smem > 48 * 1024) LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
     LSVD_CUDA_TRY(launch_chained(kern, dim3(p.nsplit, a->num_q_heads, a->batch), dim3(kRopeWarps * 32), smem, st, 1, true, p));
   }
