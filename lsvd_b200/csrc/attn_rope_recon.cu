@@ -116,6 +116,12 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
   constexpr int ntile = D >> 3;        // 8-column MMA tiles of the head
   constexpr int npair = ntile >> 1;    // tile j pairs with tile j + npair (columns c and c + D/2)
+  // Which columns of the head an MMA tile holds is free; they are chosen so that a lane's accumulators cover FOUR
+  // consecutive rotary pairs per two tiles (one 16-byte piece of a cos/sin row, which then needs 2 * D / 32 loads per
+  // tile and row instead of D / 8 eight-byte ones that each touched eight rows): column n of tile j = 2 i + u is head
+  // column 16 i + u + 2 n, so lane (g, t) holds pairs 16 i + 4 t + u + 2 e in acc[j][e].  The stride of two columns
+  // between lanes also spreads the W_uk fragment reads of a half-warp over all banks (pitch rk + 16).
+  auto tile_col = [](int j) { return (j >= npair ? D2 : 0) + 16 * ((j % npair) >> 1) + (j & 1); };
   float m = -INFINITY, l = 0.f;
   // value latents: lane (tg = lane / 8, ch = lane % 8) adds tokens 4 i + tg of a tile into ranks 8 ch .. 8 ch + 7 and
   // 64 + 8 ch .. 64 + 8 ch + 7; the four token groups are summed once, after the loop
@@ -139,7 +145,7 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
     const int8_t* klo = p.cache_k + slot_lo * p.k_slot_stride + hk * p.k_head_stride + 8 * t;
     const int8_t* khi = p.cache_k + slot_hi * p.k_slot_stride + hk * p.k_head_stride + 8 * t;
 
-    // ---- K = Z W_uk: acc[j] holds columns 8j + 2t, 8j + 2t + 1 of rows g (c = 0, 1) and g + 8 (c = 2, 3) ----
+    // ---- K = Z W_uk: acc[j] holds columns tile_col(j) + 4t, + 4t + 2 of rows g (c = 0, 1) and g + 8 (c = 2, 3) ----
     int acc[ntile][4];
 #pragma unroll
     for (int j = 0; j < ntile; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
@@ -156,7 +162,7 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
 #pragma unroll
       for (int j = 0; j < ntile; ++j) {
         uint2 bw = make_uint2(0u, 0u);
-        if (ks + 8 * t < rk) bw = *reinterpret_cast<const uint2*>(wT + (8 * j + g) * pitch + ks + 8 * t);
+        if (ks + 8 * t < rk) bw = *reinterpret_cast<const uint2*>(wT + (tile_col(j) + 2 * g) * pitch + ks + 8 * t);
         mma_s8(acc[j], alo.x, ahi.x, alo.y, ahi.y, bw.x, bw.y);
       }
     }
@@ -168,27 +174,32 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
     const __half2* tab_hi = p.table + static_cast<int64_t>(min(t0 + g + 8, end - 1)) * D2;
     float dot_lo = 0.f, dot_hi = 0.f;
 #pragma unroll
-    for (int j = 0; j < npair; ++j) {
-      const int c = 8 * j + 2 * t;                   // pairs c and c + 1: (cos, sin) of both in one 8-byte load
-      const uint2 raw_lo = __ldg(reinterpret_cast<const uint2*>(tab_lo + c));
-      const uint2 raw_hi = __ldg(reinterpret_cast<const uint2*>(tab_hi + c));
+    for (int i = 0; i < npair / 2; ++i) {
+      // this lane's four rotary pairs 16 i + 4 t .. + 3 of both rows: (cos, sin) of all four in one 16-byte load
+      const uint4 raw_lo = __ldg(reinterpret_cast<const uint4*>(tab_lo + 16 * i + 4 * t));
+      const uint4 raw_hi = __ldg(reinterpret_cast<const uint4*>(tab_hi + 16 * i + 4 * t));
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float4 k4 = cst[c + e];
-        const uint32_t wl = e ? raw_lo.y : raw_lo.x, wh = e ? raw_hi.y : raw_hi.x;
-        const float2 cs_lo = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wl & 0xffffu))),
-                                         __half2float(__ushort_as_half(static_cast<unsigned short>(wl >> 16))));
-        const float2 cs_hi = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wh & 0xffffu))),
-                                         __half2float(__ushort_as_half(static_cast<unsigned short>(wh >> 16))));
-        {
-          const float a0 = static_cast<float>(acc[j][e]), a1 = static_cast<float>(acc[j + npair][e]);
-          dot_lo = fmaf(cs_lo.x, fmaf(a1, k4.y, a0 * k4.x), dot_lo);
-          dot_lo = fmaf(cs_lo.y, fmaf(-a1, k4.w, a0 * k4.z), dot_lo);
-        }
-        {
-          const float a0 = static_cast<float>(acc[j][2 + e]), a1 = static_cast<float>(acc[j + npair][2 + e]);
-          dot_hi = fmaf(cs_hi.x, fmaf(a1, k4.y, a0 * k4.x), dot_hi);
-          dot_hi = fmaf(cs_hi.y, fmaf(-a1, k4.w, a0 * k4.z), dot_hi);
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = 2 * i + u;
+          const float4 k4 = cst[16 * i + 4 * t + u + 2 * e];
+          const uint32_t wl = e ? (u ? raw_lo.w : raw_lo.z) : (u ? raw_lo.y : raw_lo.x);
+          const uint32_t wh = e ? (u ? raw_hi.w : raw_hi.z) : (u ? raw_hi.y : raw_hi.x);
+          const float2 cs_lo = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wl & 0xffffu))),
+                                           __half2float(__ushort_as_half(static_cast<unsigned short>(wl >> 16))));
+          const float2 cs_hi = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wh & 0xffffu))),
+                                           __half2float(__ushort_as_half(static_cast<unsigned short>(wh >> 16))));
+          {
+            const float a0 = static_cast<float>(acc[j][e]), a1 = static_cast<float>(acc[j + npair][e]);
+            dot_lo = fmaf(cs_lo.x, fmaf(a1, k4.y, a0 * k4.x), dot_lo);
+            dot_lo = fmaf(cs_lo.y, fmaf(-a1, k4.w, a0 * k4.z), dot_lo);
+          }
+          {
+            const float a0 = static_cast<float>(acc[j][2 + e]), a1 = static_cast<float>(acc[j + npair][2 + e]);
+            dot_hi = fmaf(cs_hi.x, fmaf(a1, k4.y, a0 * k4.x), dot_hi);
+            dot_hi = fmaf(cs_hi.y, fmaf(-a1, k4.w, a0 * k4.z), dot_hi);
+          }
         }
       }
     }
