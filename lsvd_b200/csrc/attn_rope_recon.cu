@@ -109,8 +109,9 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
     }
   }
   __syncthreads();
+  // pair c = 16 i + 4 t + m is stored at 16 i + 4 m + t: the four lanes of a quad then read one 64-byte run per load
   for (int i = threadIdx.x; i < D2; i += blockDim.x)
-    cst[i] = make_float4(sw[i] * qrot[i], sw[i + D2] * qrot[i + D2], sw[i] * qrot[i + D2], sw[i + D2] * qrot[i]);
+    cst[(i & ~15) | ((i & 3) << 2) | ((i >> 2) & 3)] = make_float4(sw[i] * qrot[i], sw[i + D2] * qrot[i + D2], sw[i] * qrot[i + D2], sw[i + D2] * qrot[i]);
   __syncthreads();
 
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) rope_recon_kernel(const __
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int j = 2 * i + u;
-          const float4 k4 = cst[16 * i + 4 * t + u + 2 * e];
+          const float4 k4 = cst[16 * i + 4 * (u + 2 * e) + t];
           const uint32_t wl = e ? (u ? raw_lo.w : raw_lo.z) : (u ? raw_lo.y : raw_lo.x);
           const uint32_t wh = e ? (u ? raw_hi.w : raw_hi.z) : (u ? raw_hi.y : raw_hi.x);
           const float2 cs_lo = make_float2(__half2float(__ushort_as_half(static_cast<unsigned short>(wl & 0xffffu))),
