@@ -133,6 +133,36 @@ def test_head_major_cache_layout_same_bits(shuffle):
     assert torch.equal(U.run_gpu(c, want="latent", head_major=True), U.run_gpu(c, want="latent"))
 
 
+_RING_CHILD = """
+import sys, torch
+sys.path.insert(0, {tests!r}); sys.path.insert(0, {root!r})
+import gpu_util as U
+from lsvd_b200 import synth
+for shuffle in (False, True):
+    kr = synth.ragged_ranks(32, 64, seed=3); vr = synth.ragged_ranks(32, 64, seed=4)
+    c = U.build_case(4, 32, 128, kr, vr, [700, 1, 33, 1024], seed=12, shuffle=shuffle, extra_slots=50 if shuffle else 0)
+    assert torch.equal(U.run_gpu(c, head_major=True), U.run_gpu(c)), shuffle
+    assert torch.equal(U.run_gpu(c, want="latent", head_major=True), U.run_gpu(c, want="latent")), shuffle
+c = U.build_case(3, 8, 128, [128] * 8, [128] * 8, [513, 64, 2000], seed=5)
+assert torch.equal(U.run_gpu(c, head_major=True), U.run_gpu(c))
+print("ring ok")
+"""
+
+
+def test_ring_form_same_bits():
+    """The shared-memory ring form of the streaming kernel (head-major cache, LSVD_STREAM_RING=1: bulk copies of a
+    step's rows when its slots are consecutive, one copy per row otherwise) gives the same bits as the register-fed
+    kernel on the slot-major cache.  The switch is read once per process, hence the child process."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, LSVD_STREAM_RING="1")
+    r = subprocess.run([sys.executable, "-c", _RING_CHILD.format(tests=here, root=os.path.dirname(here))],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ring ok" in r.stdout, r.stdout + r.stderr
+
+
 def _adversarial(c, kind):
     """Put the case into a corner of the value range; the cache is re-quantised by the oracle."""
     from oracle import quant
