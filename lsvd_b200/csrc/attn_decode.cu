@@ -510,6 +510,14 @@ constexpr int kRingMaxStages = 4;
 __device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ uint2 lds64(const uint8_t* p) { return *reinterpret_cast<const uint2*>(p); }
 
+// Two 16 x 16 byte matrices (rows given by lanes 0..15 and 16..31, 16 bytes each) transposed into registers: lane (g, t)
+// receives, per matrix, bytes [4t..4t+3][g] and [4t..4t+3][g + 8] (layout measured on B200).
+__device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const uint8_t* row) {
+  asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(smem_u32(row)));
+}
+
 __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const HeadPlan& H, int b, int h, int rem, int k,
                                                  int len, int t0, int t1, uint4* scratch, uint8_t* wlimb, uint8_t* ring,
                                                  uint64_t* bars, uint32_t& phases, int lane) {
@@ -521,7 +529,6 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
   const int S = min(kRingMaxStages, kRingBytesPerWarp / stage_bytes);       // >= 2: a stage is at most 8 KB
   const int8_t* kbase = p.cache_k + static_cast<int64_t>(H.k_col) * p.num_slots;
   const int8_t* vbase = p.cache_v + static_cast<int64_t>(H.v_col) * p.num_slots;
-  const bool v_ok0 = g * 8 < nv * 16, v_ok1 = 64 + g * 8 < nv * 16;
   const __half* ksc = p.scale_k + static_cast<int64_t>(h) * p.num_slots;
   const __half* vsc = p.scale_v + static_cast<int64_t>(h) * p.num_slots;
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
@@ -555,6 +562,7 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
 #pragma unroll
     for (int r = 0; r < 4; ++r) acc[gi][r][0] = acc[gi][r][1] = 0.f;
 
+  const int koff0 = t4 < nk ? 16 * t4 : 0, koff1 = 4 + t4 < nk ? 64 + 16 * t4 : 0;
   const int tok_begin = t0 * kTileTokens, tok_end = min(len, t1 * kTileTokens);
   const int nsteps = (tok_end - tok_begin + kTileTokens - 1) / kTileTokens;
   auto slot_of = [&](int j) {        // slot of this lane's token of step j (-1: no token)
@@ -634,22 +642,15 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
     float sc[4];                     // score of token g + 8j, in lanes t = 0, 1 of the quad
 #pragma unroll
     for (int rt = 0; rt < 2; ++rt) {
-      const uint8_t* r0 = kst + (g + 16 * rt) * rkb + 16 * t4;
+      // a 16-byte piece past the head's rank meets zero query limbs: it is read from piece 0 instead (any bytes do)
+      const uint8_t* r0 = kst + (g + 16 * rt) * rkb;
       const uint8_t* r1 = r0 + 8 * rkb;
-      uint4 a0 = make_uint4(0u, 0u, 0u, 0u), a1 = a0;
-      if (t4 < nk) {
-        a0 = lds128(r0);
-        a1 = lds128(r1);
-      }
+      const uint4 a0 = lds128(r0 + koff0), a1 = lds128(r1 + koff0);
       int d[4];
       mma_s8_16x8x32_zero(d, a0.x, a1.x, a0.y, a1.y, limb_b0[0], limb_b1[0]);
       mma_s8_16x8x32(d, a0.z, a1.z, a0.w, a1.w, limb_b0[1], limb_b1[1]);
       if (nk > 4) {
-        uint4 c0 = make_uint4(0u, 0u, 0u, 0u), c1 = c0;
-        if (4 + t4 < nk) {
-          c0 = lds128(r0 + 64);
-          c1 = lds128(r1 + 64);
-        }
+        const uint4 c0 = lds128(r0 + koff1), c1 = lds128(r1 + koff1);
         mma_s8_16x8x32(d, c0.x, c1.x, c0.y, c1.y, limb_b0[2], limb_b1[2]);
         mma_s8_16x8x32(d, c0.z, c1.z, c0.w, c1.w, limb_b0[3], limb_b1[3]);
       }
@@ -691,37 +692,31 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
       wlimb[32 + lane] = static_cast<uint8_t>(Q >> 8);
       __syncwarp();
     }
-    uint32_t wb0 = 0u, wb1 = 0u;     // B operand: k 4t..4t+3 <-> tokens 8t..8t+3, k 16+4t.. <-> tokens 8t+4..8t+7
+    uint32_t wb0 = 0u, wb1 = 0u;     // B operand: k 4t..4t+3 <-> tokens 4t..4t+3, k 16+4t.. <-> tokens 16+4t..16+4t+3
     if (g < 2) {                     // column 0: low limb, column 1: high limb; both land in lane t = 0 of a quad
-      const uint32_t* wl = reinterpret_cast<const uint32_t*>(wlimb + g * 32 + t4 * 8);
+      const uint32_t* wl = reinterpret_cast<const uint32_t*>(wlimb + g * 32 + t4 * 4);
       wb0 = wl[0];
-      wb1 = wl[1];
+      wb1 = wl[4];
     }
-    // ---- values: token 8t + i, ranks 8g..8g+7 of a 64-rank group, transposed 4 x 4 in registers ----
+    // ---- values: A = V transposed (rows = 16 ranks, k = the step's 32 tokens), fetched in fragment order by
+    // ldmatrix.trans on bytes: lane l gives the address of token l's 16 ranks; registers 0, 1 = tokens 0..15 at ranks
+    // g and g + 8, registers 2, 3 = tokens 16..31 -- the four A registers of the MMA, in order ----
+    const uint8_t* vlane = vst + lane * rvb;
 #pragma unroll
     for (int gi = 0; gi < 2; ++gi) {
       if (gi < nvg) {
-        const bool ok = gi == 0 ? v_ok0 : v_ok1;
-        const uint8_t* vrow = vst + (8 * t4) * rvb + 64 * gi + 8 * g;
-        uint2 va[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          va[i] = make_uint2(0u, 0u);
-          if (ok) va[i] = lds64(vrow + i * rvb);
-        }
-        uint32_t x0[4], y0[4], x1[4], y1[4];
-        transpose4x4_bytes(va[0].x, va[1].x, va[2].x, va[3].x, x0);
-        transpose4x4_bytes(va[0].y, va[1].y, va[2].y, va[3].y, y0);
-        transpose4x4_bytes(va[4].x, va[5].x, va[6].x, va[7].x, x1);
-        transpose4x4_bytes(va[4].y, va[5].y, va[6].y, va[7].y, y1);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          int d[4];
-          mma_s8u8_16x8x32_zero(d, x0[r], y0[r], x1[r], y1[r], wb0, wb1);
-          // lane t = 0 holds both limb columns; the other lanes of the quad compute on zero columns
-          const float lo = static_cast<float>(d[0] + d[1] * 256), hi = static_cast<float>(d[2] + d[3] * 256);
-          acc[gi][r][0] = fmaf(acc[gi][r][0], corr, wsc * lo);
-          acc[gi][r][1] = fmaf(acc[gi][r][1], corr, wsc * hi);
+          if (gi * 4 + r < nv) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x2_trans_b8(a0, a1, a2, a3, vlane + 64 * gi + 16 * r);
+            int d[4];
+            mma_s8u8_16x8x32_zero(d, a0, a1, a2, a3, wb0, wb1);
+            // lane t = 0 holds both limb columns; the other lanes of the quad compute on zero columns
+            const float lo = static_cast<float>(d[0] + d[1] * 256), hi = static_cast<float>(d[2] + d[3] * 256);
+            acc[gi][r][0] = fmaf(acc[gi][r][0], corr, wsc * lo);      // rank 64 gi + 16 r + g
+            acc[gi][r][1] = fmaf(acc[gi][r][1], corr, wsc * hi);      // rank 64 gi + 16 r + g + 8
+          }
         }
       }
     }
@@ -742,19 +737,15 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
     ml[1] = lsum;
   }
   float* pa = p.part_acc + static_cast<int64_t>(b) * p.acc_per_request + H.acc_off + k * nv * 16;
+  if (t4 == 0) {                       // complete in lane t = 0 of each quad
 #pragma unroll
-  for (int gi = 0; gi < 2; ++gi) {
-    float v[8];
+    for (int gi = 0; gi < 2; ++gi)
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      v[r] = acc[gi][r][0];            // complete in lane t = 0 of each quad
-      v[4 + r] = acc[gi][r][1];
-    }
-    if (t4 == 0 && gi * 64 + g * 8 < nv * 16) {
-      float4* dst = reinterpret_cast<float4*>(pa + gi * 64 + g * 8);     // ranks 8g .. 8g+7 of the group
-      dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-      dst[1] = make_float4(v[4], v[5], v[6], v[7]);
-    }
+      for (int r = 0; r < 4; ++r)
+        if (gi * 4 + r < nv) {
+          pa[64 * gi + 16 * r + g] = acc[gi][r][0];
+          pa[64 * gi + 16 * r + g + 8] = acc[gi][r][1];
+        }
   }
   return true;
 }
@@ -1105,11 +1096,11 @@ int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
   sp.head_major = a->cache_layout == LSVD_CACHE_HEAD_MAJOR ? 1 : 0;
   for (int h = 0; h < a->num_heads; ++h) sp.head[h] = hp.head[h];
   if (a->ev_stream_begin) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_begin), st));
-  // head-major cache: LSVD_STREAM_RING=1 selects the shared-memory ring form (same bits; within 1 us of the
-  // register-fed form on B200, which stays the default)
+  // head-major cache: the shared-memory ring form (same bits as the register-fed one, 61 against 67 us on config 3);
+  // LSVD_STREAM_RING=0 selects the register-fed kernel, for measurements
   static const bool use_ring = [] {
     const char* e = std::getenv("LSVD_STREAM_RING");
-    return e != nullptr && std::atoi(e) != 0;
+    return e == nullptr || std::atoi(e) != 0;
   }();
   if (sp.head_major && use_ring) {
     const int smem = kRingWarps * kRingBytesPerWarp;

@@ -149,15 +149,17 @@ print("ring ok")
 """
 
 
-def test_ring_form_same_bits():
-    """The shared-memory ring form of the streaming kernel (head-major cache, LSVD_STREAM_RING=1: bulk copies of a
-    step's rows when its slots are consecutive, one copy per row otherwise) gives the same bits as the register-fed
-    kernel on the slot-major cache.  The switch is read once per process, hence the child process."""
+@pytest.mark.parametrize("ring", ["1", "0"])
+def test_ring_and_register_forms_same_bits(ring):
+    """On the head-major cache the streaming kernel has two forms: the shared-memory ring (the default: bulk copies
+    of a step's rows when its slots are consecutive, one copy per row otherwise, `ldmatrix` transposes) and the
+    register-fed one (LSVD_STREAM_RING=0).  Both give the same bits as the kernel on the slot-major cache.  The
+    switch is read once per process, hence the child process."""
     import os
     import subprocess
     import sys
     here = os.path.dirname(os.path.abspath(__file__))
-    env = dict(os.environ, LSVD_STREAM_RING="1")
+    env = dict(os.environ, LSVD_STREAM_RING=ring)
     r = subprocess.run([sys.executable, "-c", _RING_CHILD.format(tests=here, root=os.path.dirname(here))],
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "ring ok" in r.stdout, r.stdout + r.stderr
