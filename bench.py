@@ -444,7 +444,8 @@ def run_ours(args, rank, world, local):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     k_ms = statistics.mean(kernel_ms)
     if has_attn:
-        abytes, kname = algorithmic_bytes(wl), "latent_stream_kernel"
+        abytes = algorithmic_bytes(wl)
+        kname = "latent_stream_ring_kernel" if args.cache_layout == "head" else "latent_stream_kernel"
     else:
         abytes, kname = FFN_RTN_PAIR_BYTES + B * 4096 + 2 * 5504 * 4, "w8a8_gemv_kernel (RTN gate/up pair)"
     achieved = abytes / (k_ms * 1e-3) / 1e9
@@ -477,8 +478,12 @@ def run_ours(args, rank, world, local):
         "roofline": {"kernel": kname, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "of": "measured" if "hbm_gbs" in peaks else "fallback",
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-                     # ncu capture summarised under profiles/ (277.8 MB + 7.2 MB, slot-major layout at context 4097); other workloads were not captured
-                     "traffic": 284975872 if (has_attn and w["batch"] == 16 and w["context"] == 4096 and w["ragged"] and not args.shared_kv) else None,
+                     # ncu captures summarised under profiles/ (context 4097: 278.4 MB + 4.8 MB for the ring kernel on the
+                     # head-major cache, 277.8 MB + 7.2 MB for the register-fed kernel on the slot-major one); other
+                     # workloads were not captured
+                     "traffic": ((283184384 if args.cache_layout == "head" else 284975872)
+                                 if (has_attn and w["batch"] == 16 and w["context"] == 4096 and w["ragged"] and not args.shared_kv)
+                                 else None),
                      "algorithmic_bytes_per_launch": abytes, "kernel_us": k_ms * 1e3, "frac_of_8TBs": achieved / 8000.0},
         "parts": {"step_us": ms_step * 1e3, "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
                   "step_algorithmic_bytes": step_bytes, "dominant_kernel_us": k_ms * 1e3,
@@ -856,7 +861,7 @@ def run_tp(args, rank, world, local):
         "e2e": {"value": B / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": x_in.numel() * 2,
                 "d2h_bytes_per_step": host_out.numel() * 2},
         "gpu_launches": 19 * args.steps,
-        "roofline": {"kernel": "latent_stream_kernel (slowest rank's share of the cache)", "bound": "hbm", "achieved": achieved,
+        "roofline": {"kernel": "latent_stream_ring_kernel (slowest rank's share of the cache)", "bound": "hbm", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "of": "measured" if peaks else "fallback",
                      "traffic": None, "algorithmic_bytes_per_launch": stream_bytes, "kernel_us": k_ms * 1e3},
         "parts": {"step_us": ms_step * 1e3, "bytes_per_gpu_per_step": local_bytes,

@@ -497,10 +497,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const 
 // 32 V rows are ONE bulk copy each (cp.async.bulk, no tensor map, no multicast) when the page table maps the step's
 // tokens to consecutive slots -- checked per step by the warp -- and one copy per row and lane otherwise.  The copies
 // land in a per-warp ring of up to four steps and complete on a per-stage mbarrier, so a warp keeps several steps of
-// latents in flight without holding them in registers, and the MMA fragments come from shared memory with constant
-// offsets: 80 registers instead of 127, so 24 warps per SM instead of 16.  Measured on B200 (batch 16 x 4097 tokens,
-// ragged ranks): 12 / 16 / 20 / 24 warps take 90.6 / 77.4 / 72.3 / 69.3 us against 70.3 us for the register-fed kernel
-// with the same items -- what bounds both is a warp's own instruction stream per step, not the bytes it has in flight.
+// latents in flight without holding them in registers, the K fragments come from shared memory with constant offsets
+// and the V fragments by ldmatrix.trans on bytes (no byte transposes in registers): 78 registers instead of 127, so 24
+// warps per SM instead of 16.  Measured on B200 (batch 16 x 4097 tokens, ragged ranks): 61.4 us against 66.7 us for the
+// register-fed kernel; at batch 64 x 8192 tokens, 40 heads: 0.97 of the measured HBM bandwidth against 0.79.  With
+// byte transposes in registers as above, 12 / 16 / 20 / 24 warps took 90.6 / 77.4 / 72.3 / 69.3 us: what bounds both
+// forms at the smaller size is a warp's own instruction stream per step, which more resident warps hide better.
+// When the page table has no runs (or on the slot-major cache) a step costs 64 small copies and this form loses
+// (116.5 against 80 us): LSVD_STREAM_RING=0 selects the register-fed kernel.
 // Waits are bounded: a wait that runs out reports LSVD_ERR_TIMEOUT and the warp stops taking items.
 constexpr int kRingWarps = 24;
 constexpr int kRingThreads = kRingWarps * 32;
@@ -518,6 +522,7 @@ __device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t& r0, uint32_t& r1,
                : "r"(smem_u32(row)));
 }
 
+template <bool kHeadMajor>
 __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const HeadPlan& H, int b, int h, int rem, int k,
                                                  int len, int t0, int t1, uint4* scratch, uint8_t* wlimb, uint8_t* ring,
                                                  uint64_t* bars, uint32_t& phases, int lane) {
@@ -527,10 +532,13 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
   const int rkb = nk * 16, rvb = nv * 16;        // bytes of a K / V row of this head
   const int stage_bytes = kTileTokens * (rkb + rvb);
   const int S = min(kRingMaxStages, kRingBytesPerWarp / stage_bytes);       // >= 2: a stage is at most 8 KB
-  const int8_t* kbase = p.cache_k + static_cast<int64_t>(H.k_col) * p.num_slots;
-  const int8_t* vbase = p.cache_v + static_cast<int64_t>(H.v_col) * p.num_slots;
-  const __half* ksc = p.scale_k + static_cast<int64_t>(h) * p.num_slots;
-  const __half* vsc = p.scale_v + static_cast<int64_t>(h) * p.num_slots;
+  // head-major: a head's rows of consecutive slots are contiguous (r_h bytes apart), and so are its scales;
+  // slot-major: a row sits at slot * row stride + the head's column, every row is its own copy
+  const int8_t* kbase = p.cache_k + (kHeadMajor ? static_cast<int64_t>(H.k_col) * p.num_slots : H.k_col);
+  const int8_t* vbase = p.cache_v + (kHeadMajor ? static_cast<int64_t>(H.v_col) * p.num_slots : H.v_col);
+  const int64_t kstride = kHeadMajor ? rkb : p.cache_k_row_stride, vstride = kHeadMajor ? rvb : p.cache_v_row_stride;
+  const __half* ksc = kHeadMajor ? p.scale_k + static_cast<int64_t>(h) * p.num_slots : p.scale_k + h;
+  const __half* vsc = kHeadMajor ? p.scale_v + static_cast<int64_t>(h) * p.num_slots : p.scale_v + h;
   const int32_t* r2t = p.req_to_token + static_cast<int64_t>(p.b_req_idx[b]) * p.req_to_token_stride;
   const float step = p.qstep[b * p.num_heads + h];
 
@@ -581,7 +589,7 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
     const uint32_t mask = __ballot_sync(0xffffffffu, valid);
     const int n = __popc(mask);
     const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
-    const bool run = mask == (n == 32 ? 0xffffffffu : ((1u << n) - 1u)) &&
+    const bool run = kHeadMajor && mask == (n == 32 ? 0xffffffffu : ((1u << n) - 1u)) &&
                      __all_sync(0xffffffffu, !valid || slot == slot0 + lane);
     uint8_t* kst = ring + ist * stage_bytes;
     uint8_t* vst = kst + kTileTokens * rkb;
@@ -594,13 +602,13 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
         bulk_g2s(vst, vbase + static_cast<int64_t>(slot0) * rvb, static_cast<uint32_t>(n * rvb), bar);
       }
     } else if (valid) {
-      bulk_g2s(kst + lane * rkb, kbase + static_cast<int64_t>(slot) * rkb, static_cast<uint32_t>(rkb), bar);
-      bulk_g2s(vst + lane * rvb, vbase + static_cast<int64_t>(slot) * rvb, static_cast<uint32_t>(rvb), bar);
+      bulk_g2s(kst + lane * rkb, kbase + static_cast<int64_t>(slot) * kstride, static_cast<uint32_t>(rkb), bar);
+      bulk_g2s(vst + lane * rvb, vbase + static_cast<int64_t>(slot) * vstride, static_cast<uint32_t>(rvb), bar);
     }
     uint32_t sc = 0u;
     if (valid) {
-      const uint32_t a = __half_as_ushort(ksc[slot]);
-      const uint32_t c = __half_as_ushort(vsc[slot]);
+      const uint32_t a = __half_as_ushort(ksc[kHeadMajor ? static_cast<int64_t>(slot) : slot * p.scale_k_row_stride]);
+      const uint32_t c = __half_as_ushort(vsc[kHeadMajor ? static_cast<int64_t>(slot) : slot * p.scale_v_row_stride]);
       sc = a | (c << 16);
     }
     if (inflight == 0) q0 = sc;
@@ -750,6 +758,7 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
   return true;
 }
 
+template <bool kHeadMajor>
 __global__ void __launch_bounds__(kRingThreads, 1) latent_stream_ring_kernel(const __grid_constant__ StreamParams p) {
   extern __shared__ __align__(128) uint8_t ring_smem[];                   // [kRingWarps][kRingBytesPerWarp]
   __shared__ uint4 limb_scratch[kRingWarps][8 * 3];
@@ -782,7 +791,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) latent_stream_ring_kernel(con
     const int t0 = k * H.chunk_tiles;
     const int t1 = min(ntiles, t0 + H.chunk_tiles);
     if (t0 >= t1) continue;
-    if (!stream_item_ring(p, H, b, h, rem, k, len, t0, t1, limb_scratch[warp], weight_limbs[warp],
+    if (!stream_item_ring<kHeadMajor>(p, H, b, h, rem, k, len, t0, t1, limb_scratch[warp], weight_limbs[warp],
                           ring_smem + warp * kRingBytesPerWarp, bars[warp], phases, lane))
       break;
   }
@@ -1102,10 +1111,20 @@ int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
     const char* e = std::getenv("LSVD_STREAM_RING");
     return e == nullptr || std::atoi(e) != 0;
   }();
-  if (sp.head_major && use_ring) {
-    const int smem = kRingWarps * kRingBytesPerWarp;
-    LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(latent_stream_ring_kernel), smem));
-    LSVD_CUDA_TRY(launch_chained(latent_stream_ring_kernel, dim3(hp.num_blocks), dim3(kRingThreads), smem, st, 1, true, sp));
+  // The ring form pays off where a step's rows arrive as one bulk copy: on the head-major cache.  On the slot-major
+  // cache every row is its own copy (64 small bulk copies per step): 116.5 us against 80 us register-fed on config 3,
+  // so that layout keeps the register-fed kernel unless LSVD_STREAM_RING=2 asks for the ring form (same bits).
+  static const bool ring_slot_major = [] {
+    const char* e = std::getenv("LSVD_STREAM_RING");
+    return e != nullptr && std::atoi(e) == 2;
+  }();
+  const int ring_smem = kRingWarps * kRingBytesPerWarp;
+  if (use_ring && sp.head_major) {
+    LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(latent_stream_ring_kernel<true>), ring_smem));
+    LSVD_CUDA_TRY(launch_chained(latent_stream_ring_kernel<true>, dim3(hp.num_blocks), dim3(kRingThreads), ring_smem, st, 1, true, sp));
+  } else if (ring_slot_major && !sp.head_major) {
+    LSVD_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(latent_stream_ring_kernel<false>), ring_smem));
+    LSVD_CUDA_TRY(launch_chained(latent_stream_ring_kernel<false>, dim3(hp.num_blocks), dim3(kRingThreads), ring_smem, st, 1, true, sp));
   } else if (sp.head_major) LSVD_CUDA_TRY(launch_chained(latent_stream_kernel<true>, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
   else LSVD_CUDA_TRY(launch_chained(latent_stream_kernel<false>, dim3(hp.num_blocks), dim3(kStreamThreads), 0, st, 1, true, sp));
   if (a->ev_stream_end) LSVD_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_stream_end), st));
