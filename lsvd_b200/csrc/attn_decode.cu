@@ -495,7 +495,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const 
 // ----------------------------------------------------------------------------------------------
 // In the head-major layout the rows of a head for consecutive slots are one contiguous run, so a step's 32 K rows and
 // 32 V rows are ONE bulk copy each (cp.async.bulk, no tensor map, no multicast) when the page table maps the step's
-// tokens to consecutive slots -- checked per step by the warp -- and one copy per row and lane otherwise.  The copies
+// tokens to consecutive slots -- checked per step by the warp -- and gathered 16-byte cp.async copies otherwise.  The rows
 // land in a per-warp ring of up to four steps and complete on a per-stage mbarrier, so a warp keeps several steps of
 // latents in flight without holding them in registers, the K fragments come from shared memory with constant offsets
 // and the V fragments by ldmatrix.trans on bytes (no byte transposes in registers): 78 registers instead of 127, so 24
@@ -503,8 +503,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) latent_stream_kernel(const 
 // register-fed kernel; at batch 64 x 8192 tokens, 40 heads: 0.97 of the measured HBM bandwidth against 0.79.  With
 // byte transposes in registers as above, 12 / 16 / 20 / 24 warps took 90.6 / 77.4 / 72.3 / 69.3 us: what bounds both
 // forms at the smaller size is a warp's own instruction stream per step, which more resident warps hide better.
-// When the page table has no runs (or on the slot-major cache) a step costs 64 small copies and this form loses
-// (116.5 against 80 us): LSVD_STREAM_RING=0 selects the register-fed kernel.
+// A step whose slots are not one run (always, on the slot-major cache) is gathered with 16-byte cp.async copies in
+// commit groups instead (one bulk copy per row, 64 per step, took 116.5 us): 87 us against 80 us for the register-fed
+// kernel, which LSVD_STREAM_RING=0 selects.
 // Waits are bounded: a wait that runs out reports LSVD_ERR_TIMEOUT and the warp stops taking items.
 constexpr int kRingWarps = 24;
 constexpr int kRingThreads = kRingWarps * 32;
@@ -512,6 +513,20 @@ constexpr int kRingBytesPerWarp = 9088;              // two steps of a 64 + 64-r
 constexpr int kRingMaxStages = 4;
 
 __device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+// 16 bytes global -> shared without a register in between; a thread's copies complete in commit groups.
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most `newer` of this thread's commit groups are still in flight (newer = 0..3).
+__device__ __forceinline__ void cp_async_wait_newer(int newer) {
+  switch (newer) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+  }
+}
 __device__ __forceinline__ uint2 lds64(const uint8_t* p) { return *reinterpret_cast<const uint2*>(p); }
 
 // Two 16 x 16 byte matrices (rows given by lanes 0..15 and 16..31, 16 bytes each) transposed into registers: lane (g, t)
@@ -520,6 +535,20 @@ __device__ __forceinline__ void ldmatrix_x2_trans_b8(uint32_t& r0, uint32_t& r1,
   asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                : "r"(smem_u32(row)));
+}
+
+// A tile's 32 gathered rows of n 16-byte pieces into dst[32][n * 16]: consecutive lanes copy consecutive pieces (piece q
+// belongs to row q / n), rows of lanes without a token are skipped.  Not inlined: it runs only for steps whose slots
+// are not one run, and must not cost the streaming loop registers.
+__device__ __noinline__ void ring_gather_rows(uint8_t* dst, const int8_t* base, int64_t row_stride, int n, int slot,
+                                              uint32_t valid_mask, int lane) {
+  const int inv = (65536 + n - 1) / n;           // q / n = (q * inv) >> 16 for q < 256
+  for (int q0 = 0; q0 < kTileTokens * n; q0 += 32) {
+    const int q = q0 + lane;
+    const int row = (q * inv) >> 16, col = q - row * n;
+    const int rslot = __shfl_sync(0xffffffffu, slot, row);
+    if ((valid_mask >> row) & 1u) cp_async16(dst + q * 16, base + static_cast<int64_t>(rslot) * row_stride + col * 16);
+  }
 }
 
 template <bool kHeadMajor>
@@ -571,6 +600,9 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
     for (int r = 0; r < 4; ++r) acc[gi][r][0] = acc[gi][r][1] = 0.f;
 
   const int koff0 = t4 < nk ? 16 * t4 : 0, koff1 = 4 + t4 < nk ? 64 + 16 * t4 : 0;
+  // stages filled by gathered cp.async copies: a bit per stage, the commit-group number of each (8 bits per stage) and
+  // the number of groups committed so far
+  uint32_t gather_mask = 0u, gather_seq_of = 0u, gather_seq = 0u;
   const int tok_begin = t0 * kTileTokens, tok_end = min(len, t1 * kTileTokens);
   const int nsteps = (tok_end - tok_begin + kTileTokens - 1) / kTileTokens;
   auto slot_of = [&](int j) {        // slot of this lane's token of step j (-1: no token)
@@ -594,16 +626,27 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
     uint8_t* kst = ring + ist * stage_bytes;
     uint8_t* vst = kst + kTileTokens * rkb;
     uint64_t* bar = bars + ist;
-    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n * (rkb + rvb)));
-    __syncwarp();
     if (run) {
-      if (lane == 0 && n > 0) {
-        bulk_g2s(kst, kbase + static_cast<int64_t>(slot0) * rkb, static_cast<uint32_t>(n * rkb), bar);
-        bulk_g2s(vst, vbase + static_cast<int64_t>(slot0) * rvb, static_cast<uint32_t>(n * rvb), bar);
+      // one bulk copy per tile, counted in bytes on the stage's barrier
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n * (rkb + rvb)));
+        if (n > 0) {
+          bulk_g2s(kst, kbase + static_cast<int64_t>(slot0) * rkb, static_cast<uint32_t>(n * rkb), bar);
+          bulk_g2s(vst, vbase + static_cast<int64_t>(slot0) * rvb, static_cast<uint32_t>(n * rvb), bar);
+        }
       }
-    } else if (valid) {
-      bulk_g2s(kst + lane * rkb, kbase + static_cast<int64_t>(slot) * kstride, static_cast<uint32_t>(rkb), bar);
-      bulk_g2s(vst + lane * rvb, vbase + static_cast<int64_t>(slot) * vstride, static_cast<uint32_t>(rvb), bar);
+      gather_mask &= ~(1u << ist);
+    } else {
+      // gathered rows (64 bulk copies of one row each cost more than they bring): consecutive lanes copy consecutive
+      // 16-byte pieces with cp.async (piece q of a tile = row q / pieces-per-row), one commit group per lane and step;
+      // the barrier's phase is completed at once and the consumer waits for the group instead
+      if (lane == 0) mbar_arrive(bar);
+      ring_gather_rows(kst, kbase, kstride, nk, slot, mask, lane);
+      ring_gather_rows(vst, vbase, vstride, nv, slot, mask, lane);
+      cp_async_commit();
+      gather_mask |= 1u << ist;
+      gather_seq_of = (gather_seq_of & ~(0xffu << (8 * ist))) | ((gather_seq & 0xffu) << (8 * ist));
+      ++gather_seq;
     }
     uint32_t sc = 0u;
     if (valid) {
@@ -638,6 +681,10 @@ __device__ __forceinline__ bool stream_item_ring(const StreamParams& p, const He
       return false;
     }
     phases ^= 1u << cst;
+    if ((gather_mask >> cst) & 1u) {
+      cp_async_wait_newer(static_cast<int>((gather_seq - 1u - (gather_seq_of >> (8 * cst))) & 0xffu));
+      __syncwarp();
+    }
     const uint8_t* kst = ring + cst * stage_bytes;
     const uint8_t* vst = kst + kTileTokens * rkb;
     const bool valid = (vbits & 1u) != 0u;
@@ -1112,8 +1159,8 @@ int attn_launch_stream(const lsvd_attn_decode_args* a, const AttnLaunch& L, cuda
     return e == nullptr || std::atoi(e) != 0;
   }();
   // The ring form pays off where a step's rows arrive as one bulk copy: on the head-major cache.  On the slot-major
-  // cache every row is its own copy (64 small bulk copies per step): 116.5 us against 80 us register-fed on config 3,
-  // so that layout keeps the register-fed kernel unless LSVD_STREAM_RING=2 asks for the ring form (same bits).
+  // cache every step is gathered piece by piece: 87 us against 80 us register-fed on config 3, so that layout keeps
+  // the register-fed kernel unless LSVD_STREAM_RING=2 asks for the ring form (same bits).
   static const bool ring_slot_major = [] {
     const char* e = std::getenv("LSVD_STREAM_RING");
     return e != nullptr && std::atoi(e) == 2;

@@ -152,9 +152,9 @@ print("ring ok")
 @pytest.mark.parametrize("ring", ["1", "0", "2"])
 def test_ring_and_register_forms_same_bits(ring):
     """On the head-major cache the streaming kernel has two forms: the shared-memory ring (the default: bulk copies
-    of a step's rows when its slots are consecutive, one copy per row otherwise, `ldmatrix` transposes) and the
-    register-fed one (LSVD_STREAM_RING=0); LSVD_STREAM_RING=2 runs the ring form on the slot-major cache too (one copy
-    per row).  All give the same bits.  The
+    of a step's rows when its slots are consecutive, gathered `cp.async` pieces otherwise, `ldmatrix` transposes) and the
+    register-fed one (LSVD_STREAM_RING=0); LSVD_STREAM_RING=2 runs the ring form on the slot-major cache too (every
+    step gathered).  All give the same bits.  The
     switch is read once per process, hence the child process."""
     import os
     import subprocess
