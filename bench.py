@@ -319,8 +319,9 @@ def run_ours(args, rank, world, local):
         if full:
             # the layer step, then one token further on the device: lengths + 1, the new token's slot looked up; after
             # DECODE_TOKENS steps the requests start over at the initial context (the slots reserved for them are reused)
-            layer(inputs[0], wl["ck"], wl["sk"], wl["cv"], wl["sv"], st, out=ffn_out, timing_events=ev)
-            decode_advance(st, base_len=wl["seq"], period=DECODE_TOKENS, status_word=status)
+            # (the move runs beside the output projection and the FFN, which no longer read the state)
+            layer(inputs[0], wl["ck"], wl["sk"], wl["cv"], wl["sv"], st, out=ffn_out, timing_events=ev,
+                  after_attention=lambda: decode_advance(st, base_len=wl["seq"], period=DECODE_TOKENS, status_word=status))
             return
         if has_attn:
             q, lk, lv = inputs

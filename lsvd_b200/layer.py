@@ -39,13 +39,16 @@ class LSVDDecoderLayer(nn.Module):
         self.hidden = self.ln1.shape[0]
         self.Rq = layout.num_heads * rank_q
         self._ws = None
+        self._side = None
 
     @torch.no_grad()
     def forward(self, x, cache_k, scale_k, cache_v, scale_v, infer_state, stages: Optional[dict] = None, out=None,
-                timing_events=None):
+                timing_events=None, after_attention=None):
         """x [B, hidden] fp16 (one token per request).  Mutates the cache rows ``infer_state.mem_index`` in place.
         ``out`` receives the result if given; ``timing_events`` (a CUDA event pair) is recorded around the attention's
-        streaming kernel."""
+        streaming kernel.  ``after_attention`` (a callable) is run on a side stream as soon as the attention has read
+        ``infer_state`` for the last time, beside the output projection and the FFN, and joined before the step ends:
+        the place for the device-side move to the next token (``decode_advance``) of a decode loop."""
         lay, H, B = self.layout, self.layout.num_heads, x.shape[0]
         xq, xs, xn = act_quant(x, want_rotated=True, norm_weight=self.ln1, norm_eps=1e-5)
         lat, _, _ = w8a8_gemv(xq, xs, self.W_lat_q, self.W_lat_s)
@@ -60,9 +63,19 @@ class LSVDDecoderLayer(nn.Module):
         token_decode_attention_int8_latent_absorb(q, infer_state, H, self.rank_q, cache_k, scale_k, cache_v, scale_v,
                                                   self.C, None, layout=lay, out_latent=o_lat, workspace=self._ws,
                                                   sm_scale=1.0 / math.sqrt(self.head_dim), timing_events=timing_events)
+        side = None
+        if after_attention is not None:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=x.device)
+            side, cur = self._side, torch.cuda.current_stream(x.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                after_attention()
         oq, os_, _ = act_quant(o_lat)
         y1, _, _ = w8a8_gemv(oq, os_, self.W_uvo_q, self.W_uvo_s, residual=xn)
         out = self.ffn(y1, out=out, norm_weight=self.ln2, norm_eps=1e-6, residual=y1)
+        if side is not None:
+            torch.cuda.current_stream(x.device).wait_stream(side)
         if stages is not None:
             stages.update(xn=xn, lat=lat, o_lat=o_lat, y1=y1, out=out)
         return out

@@ -55,9 +55,12 @@ class LSVDModel(nn.Module):
         return x
 
     @torch.no_grad()
-    def decode_step(self, x: torch.Tensor, state: InferState) -> torch.Tensor:
-        for layer, (ck, sk, cv, sv) in zip(self.layers, self.caches):
-            x = layer(x, ck, sk, cv, sv, state)
+    def decode_step(self, x: torch.Tensor, state: InferState, after_last_attention=None) -> torch.Tensor:
+        """One token per request through every layer.  ``after_last_attention`` (a callable) runs on a side stream once
+        the last layer's attention has read ``state``, beside that layer's output projection and FFN."""
+        last = len(self.layers) - 1
+        for i, (layer, (ck, sk, cv, sv)) in enumerate(zip(self.layers, self.caches)):
+            x = layer(x, ck, sk, cv, sv, state, after_attention=after_last_attention if i == last else None)
         return x
 
     @torch.no_grad()
@@ -76,9 +79,8 @@ class LSVDModel(nn.Module):
         torch.cuda.current_stream(x.device).wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            out = self.decode_step(x, state)
-            if advance is not None:
-                decode_advance(state, **advance)
+            out = self.decode_step(x, state, after_last_attention=(
+                None if advance is None else (lambda: decode_advance(state, **advance))))
         return graph, out
 
 
